@@ -1,0 +1,120 @@
+// Shared device/host helpers for the flat k-NN kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/b200_flat.h"
+
+namespace b200f {
+
+constexpr int kNumSMsDefault = 148;
+constexpr float kHostInf = __builtin_huge_valf();
+
+// Bits OR-ed into the device status word (B200FSearchArgs::status[0]).
+constexpr int kDevErrBarrierWait = 1;   // a bounded mbarrier wait ran out
+constexpr int kDevErrSmemAlign = 2;     // dynamic shared memory base not 1024-byte aligned
+constexpr int kDevErrOverflow = 4;      // a candidate buffer overflowed (never expected)
+
+#define B200F_CUDA_TRY(expr)                         \
+    do {                                             \
+        cudaError_t _e = (expr);                     \
+        if (_e != cudaSuccess) {                     \
+            (void)cudaGetLastError();                \
+            return B200F_ERR_CUDA;                   \
+        }                                            \
+    } while (0)
+
+#define B200F_LAUNCH_CHECK()                         \
+    do {                                             \
+        cudaError_t _e = cudaGetLastError();         \
+        if (_e != cudaSuccess) return B200F_ERR_CUDA; \
+    } while (0)
+
+__host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ inline int64_t round_up64(int64_t a, int64_t b) { return ceil_div64(a, b) * b; }
+
+// Monotone map float -> uint32 (ascending float order == ascending unsigned order;
+// NaN sorts after +INF).
+__device__ __forceinline__ uint32_t float_to_ordered(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_to_float(uint32_t u) {
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Launchers implemented in the other translation units ------------------------
+
+// rows.cu: queries fp32 [nq][d] -> A planes (16-bit, [npl][nq][d_pad]) + squared norms.
+int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,
+                           int64_t a_pitch, int64_t a_plane_stride, float* qnorm,
+                           cudaStream_t stream);
+
+// scan.cu: streaming search for small nq, k <= 32.  Writes P = *out_P partial lists.
+struct ScanPlan {
+    int grid;        // CTAs == number of partial lists per query
+    int threads;
+};
+ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count);
+int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part_key,
+                     int32_t* part_idx, cudaStream_t stream);
+// Scan that stores keys (smaller = better) to a matrix [nq][ld] for columns [col0, col0+ncols).
+int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, float* out,
+                      int64_t ld, int sm_count, cudaStream_t stream);
+
+// gemm_topk.cu
+struct GemmPlan {
+    int nqb;             // query blocks of 128 rows
+    int64_t ntiles;      // column tiles of 256 rows in the launch
+    int P;               // column ranges == partial lists per query
+    int64_t tiles_per_range;
+    int grid;
+};
+GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count);
+struct GemmOperands {
+    const uint16_t* a_planes;  // [npl][nq][a_pitch]
+    int64_t a_pitch, a_plane_stride;
+    const uint16_t* b_planes;  // [npl][nb][b_pitch]
+    int64_t b_pitch, b_plane_stride;
+    int npl;                   // 1 (fp16 / bf16 storage) or 3 (fp32 storage split)
+    int is_bf16;               // element format of both operands
+    int64_t nq, nb;
+    int d_pad;                 // K extent (multiple of 8)
+};
+// Fused top-k (k <= 32): partial lists part_key/part_idx [nq][P][k].
+int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
+                     float alpha, const float* bias, int k, float* part_key, int32_t* part_idx,
+                     int32_t* status, cudaStream_t stream);
+// Store mode: out[row*ld + (col-col0)] = sign*(alpha*dot + bias[col]) + rowadd[row].
+int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
+                      float alpha, const float* bias, float sign, const float* rowadd, float* out,
+                      int64_t ld, int32_t* status, cudaStream_t stream);
+
+// select.cu
+// Merge P sorted partial lists (key smaller=better, int32 local ids; -1 = empty) per
+// query and finalise: L2 dist = max(key + qnorm, 0), IP dist = -key; labels = id + base.
+int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
+                          int metric, const float* qnorm, int64_t label_base, float* out_dist,
+                          int64_t* out_labels, cudaStream_t stream);
+// Running top-k over a key matrix chunk: run lists [nq][k] (key, int32 id) are read
+// (if has_prev) and rewritten with the best k of (previous list U chunk columns).
+int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int64_t col0,
+                        int k, int has_prev, float* run_key, int32_t* run_idx, int32_t* status,
+                        cudaStream_t stream);
+int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t nq, int k,
+                          int metric, const float* qnorm, int64_t label_base, float* out_dist,
+                          int64_t* out_labels, cudaStream_t stream);
+
+int cached_sm_count();
+
+}  // namespace b200f

@@ -1,0 +1,643 @@
+// Distance GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), operands
+// staged by TMA, with the top-k selection fused into the epilogue so that the
+// nq x nb score matrix is never written to HBM.
+//
+// Replaces the reference's simdgroup_gemm_* kernels (shaders/simdgroup_gemm.metal:26-481,
+// shaders/simdgroup_gemm_bf16.metal:23-242, shaders/simdgroup_gemm_family9.metal:27-470),
+// their host dispatch (src/MetalDistance.mm:225-323) and, through the fused
+// epilogue, fused_l2_topk_* (shaders/fused_l2_topk.metal:19-444).
+//
+// Shape of one CTA (192 threads, one CTA per SM, persistent over work items):
+//   warp 0     TMA producer: Q tile (128 x 64) and X tile (256 x 64) per k-block,
+//              128-byte swizzle, 4-stage mbarrier ring
+//   warp 1     MMA issuer: tcgen05.mma kind::f16, M=128 N=256 K=16, fp32 accumulators
+//              in TMEM, two accumulator buffers (2 x 256 columns)
+//   warps 2-5  epilogue: tcgen05.ld (thread t owns query row t of the tile),
+//              key = bias[col] + alpha * dot, threshold filter against the row's
+//              current k-th best, sorted insertion into a per-row list in shared memory
+// A work item is (query block, column range); every item yields one sorted
+// partial list per query row, merged afterwards by merge_partials.
+//
+// FP32 storage: both operands are split into three bf16 planes
+// (x = x0 + x1 + x2 exactly to 24 bits) and six plane products
+// (0,0) (0,1) (1,0) (0,2) (2,0) (1,1) are accumulated in the same fp32 TMEM
+// accumulator; the dropped products are below 2^-24 relative.
+//
+// Every wait on an mbarrier is bounded: after ~1 s of clock the waiting thread
+// records kDevErrBarrierWait in the status word, raises the CTA abort flag and
+// all roles drain out, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200f {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;  // 16-bit elements: 128 bytes = one swizzle row
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int KMAX = B200F_FUSED_MAX_K;
+constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_THREADS = 128;
+constexpr int TMEM_COLS = 512;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+
+// shared memory map (bytes from the 1024-aligned dynamic base)
+constexpr int SM_A = 0;
+constexpr int SM_B = SM_A + STAGES * A_STAGE_BYTES;
+constexpr int SM_LKEY = SM_B + STAGES * B_STAGE_BYTES;
+constexpr int SM_LIDX = SM_LKEY + KMAX * BM * 4;
+constexpr int SM_BIAS = SM_LIDX + KMAX * BM * 4;
+constexpr int SM_BAR = SM_BIAS + 2 * BN * 4;
+// barriers: full[4] empty[4] tfull[2] tempty[2] bias[2]  = 14 x 8 bytes
+constexpr int SM_TMEMPTR = SM_BAR + 14 * 8;
+constexpr int SM_ABORT = SM_TMEMPTR + 4;
+constexpr int SMEM_BYTES = SM_ABORT + 4 + 8;
+
+enum { MODE_TOPK = 0, MODE_STORE = 1 };
+
+struct GemmParams {
+    int64_t nq;
+    int64_t col0;        // first global column (row of X) of this launch
+    int64_t ncols_end;   // one past the last valid global column of this launch
+    int64_t ntiles;      // column tiles in this launch
+    int64_t tiles_per_range;
+    int nqb;
+    int P;
+    int kb_per_pass;     // k-blocks of 64 per plane product
+    int npass;
+    uint32_t pass_a;     // 4 bits per pass: plane index of A
+    uint32_t pass_b;
+    uint32_t idesc;
+    int mode;
+    int k;
+    float alpha;
+    const float* bias;   // per global column, may be null (0)
+    float sign;
+    const float* rowadd; // per query row, may be null (0)
+    float* part_key;
+    int32_t* part_idx;
+    float* out;
+    int64_t ld;
+    int32_t* status;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+    return done;
+}
+
+// Bounded wait.  Returns false when the wait ran out or another thread of the CTA
+// already aborted; the caller must then leave its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    int spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 255) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status) atomicOr(status, kDevErrBarrierWait);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+    asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+            : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(d_tmem),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+              "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+              "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address
+    desc |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle)
+    desc |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+    desc |= (uint64_t)1 << 46;                    // descriptor version (sm_100)
+    desc |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return desc;
+}
+
+// Sorted insertion into the thread's own row list (column `row` of lkey/lidx).
+// Precondition: s < current k-th key.  Equal keys keep arrival order (ids ascend).
+__device__ __noinline__ float list_insert(float* lkey, int32_t* lidx, int row, int k, float s,
+                                          int32_t id) {
+    int j = k - 1;
+    while (j > 0) {
+        float prev = lkey[(j - 1) * BM + row];
+        if (!(prev > s)) break;
+        lkey[j * BM + row] = prev;
+        lidx[j * BM + row] = lidx[(j - 1) * BM + row];
+        j--;
+    }
+    lkey[j * BM + row] = s;
+    lidx[j * BM + row] = id;
+    return lkey[(k - 1) * BM + row];
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    float* lkey = reinterpret_cast<float*>(smem + SM_LKEY);
+    int32_t* lidx = reinterpret_cast<int32_t*>(smem + SM_LIDX);
+    float* sbias = reinterpret_cast<float*>(smem + SM_BIAS);
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + SM_TMEMPTR);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_ABORT);
+
+    const uint32_t bar_full = sbase + SM_BAR;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_tfull = bar_empty + STAGES * 8;
+    const uint32_t bar_tempty = bar_tfull + 2 * 8;
+    const uint32_t bar_bias = bar_tempty + 2 * 8;
+
+    if ((sbase & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
+        if (threadIdx.x == 0 && p.status) atomicOr(p.status, kDevErrSmemAlign);
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(bar_tfull + s * 8, 1);
+            mbar_init(bar_tempty + s * 8, 4);
+            mbar_init(bar_bias + s * 8, NUM_EPI_THREADS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             sbase + SM_TMEMPTR),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    const int64_t nitems = (int64_t)p.nqb * p.P;
+    const int kb_total = p.kb_per_pass * p.npass;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+                const int qb = (int)(item % p.nqb);
+                const int64_t xr = item / p.nqb;
+                const int64_t t0 = xr * p.tiles_per_range;
+                const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
+                for (int64_t t = t0; t < t1 && ok; t++) {
+                    const int xrow = (int)(p.col0 + t * BN);
+                    for (int kb = 0; kb < kb_total; kb++) {
+                        if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status)) {
+                            ok = false;
+                            break;
+                        }
+                        const int pass = kb / p.kb_per_pass;
+                        const int kk = (kb - pass * p.kb_per_pass) * BK;
+                        const int pa = (p.pass_a >> (4 * pass)) & 15;
+                        const int pb = (p.pass_b >> (4 * pass)) & 15;
+                        mbar_arrive_expect_tx(bar_full + stage * 8, A_STAGE_BYTES + B_STAGE_BYTES);
+                        tma_load_3d(sbase + SM_A + stage * A_STAGE_BYTES, &tmap_a,
+                                    bar_full + stage * 8, kk, qb * BM, pa);
+                        tma_load_3d(sbase + SM_B + stage * B_STAGE_BYTES, &tmap_b,
+                                    bar_full + stage * 8, kk, xrow, pb);
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                    }
+                }
+            }
+            // Let every copy this thread issued land before the CTA's shared memory goes
+            // away: wait (bounded) until the consumer released, or the data arrived in,
+            // each stage that is still in flight.
+            if (!ok) {
+                long long t0 = clock64();
+                while (clock64() - t0 < 2000000LL) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+                const int64_t xr = item / p.nqb;
+                const int64_t t0 = xr * p.tiles_per_range;
+                const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
+                for (int64_t t = t0; t < t1 && ok; t++) {
+                    if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1, abort_flag, p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    for (int kb = 0; kb < kb_total; kb++) {
+                        if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, p.status)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint64_t da = make_smem_desc(sbase + SM_A + stage * A_STAGE_BYTES);
+                        const uint64_t db = make_smem_desc(sbase + SM_B + stage * B_STAGE_BYTES);
+#pragma unroll
+                        for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                            // advance 32 bytes (16 elements) along K inside the swizzle row
+                            tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
+                                       p.idesc, (kb | k4) != 0 ? 1u : 0u);
+                        }
+                        tc_commit(bar_empty + stage * 8);  // frees the stage when the MMAs retire
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(bar_tfull + acc * 8);  // accumulator complete
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue -----------------------------------
+        const int ew = warp & 3;              // TMEM lane quarter this warp may read
+        const int row = ew * 32 + lane;       // row of the tile owned by this thread
+        const int et = threadIdx.x - 64;      // 0..127
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const int k = p.k;
+        for (int64_t item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+            const int qb = (int)(item % p.nqb);
+            const int64_t xr = item / p.nqb;
+            const int64_t t0 = xr * p.tiles_per_range;
+            const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
+            const int64_t grow = (int64_t)qb * BM + row;
+            const bool row_live = grow < p.nq;
+            float thr = CUDART_INF_F;
+            float radd = 0.f;
+            if (p.mode == MODE_TOPK) {
+                for (int j = 0; j < k; j++) {
+                    lkey[j * BM + row] = CUDART_INF_F;
+                    lidx[j * BM + row] = -1;
+                }
+            } else if (row_live && p.rowadd) {
+                radd = p.rowadd[grow];
+            }
+            for (int64_t t = t0; t < t1 && ok; t++) {
+                const int64_t c_tile = p.col0 + t * BN;
+                // stage the per-column bias of this tile (+INF beyond the last valid column)
+                {
+                    float* bs = sbias + acc * BN;
+                    for (int c = et; c < BN; c += NUM_EPI_THREADS) {
+                        const int64_t gc = c_tile + c;
+                        float b = CUDART_INF_F;
+                        if (gc < p.ncols_end) b = p.bias ? __ldg(p.bias + gc) : 0.f;
+                        bs[c] = b;
+                    }
+                    mbar_arrive(bar_bias + acc * 8);
+                    const bool w = mbar_wait(bar_bias + acc * 8, acc_phase, abort_flag, p.status);
+                    if (!__all_sync(0xffffffffu, w)) {  // keep the warp converged for tcgen05.ld
+                        ok = false;
+                        break;
+                    }
+                }
+                {
+                    const bool w = mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag, p.status);
+                    if (!__all_sync(0xffffffffu, w)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                tc_fence_after();
+                const float* bs = sbias + acc * BN;
+                const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN;
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ch++) {
+                    uint32_t r[32];
+                    tc_ld32(taddr + ch * 32, r);
+                    tc_wait_ld();
+                    if (p.mode == MODE_TOPK) {
+                        uint32_t hits = 0;
+#pragma unroll
+                        for (int c = 0; c < 32; c++) {
+                            const float s = fmaf(p.alpha, __uint_as_float(r[c]), bs[ch * 32 + c]);
+                            r[c] = __float_as_uint(s);
+                            hits |= (s < thr ? 1u : 0u) << c;
+                        }
+                        if (hits != 0 && row_live) {
+                            const int32_t id0 = (int32_t)(c_tile + ch * 32);
+#pragma unroll
+                            for (int c = 0; c < 32; c++) {
+                                const float s = __uint_as_float(r[c]);
+                                if (((hits >> c) & 1u) && s < thr)
+                                    thr = list_insert(lkey, lidx, row, k, s, id0 + c);
+                            }
+                        }
+                    } else {
+                        if (row_live) {
+                            const int64_t cbase = c_tile + ch * 32;
+                            float* orow = p.out + grow * p.ld + (cbase - p.col0);
+#pragma unroll
+                            for (int c = 0; c < 32; c++) {
+                                if (cbase + c < p.ncols_end) {
+                                    const float s =
+                                            fmaf(p.alpha, __uint_as_float(r[c]), bs[ch * 32 + c]);
+                                    orow[c] = fmaf(p.sign, s, radd);
+                                }
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + acc * 8);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+            if (p.mode == MODE_TOPK && row_live && ok) {
+                float* ok_ = p.part_key + (grow * p.P + xr) * k;
+                int32_t* oi_ = p.part_idx + (grow * p.P + xr) * k;
+                for (int j = 0; j < k; j++) {
+                    ok_[j] = lkey[j * BM + row];
+                    oi_[j] = lidx[j * BM + row];
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+                    cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+// 3-D map {k, row, plane} over a [planes][rows][pitch] 16-bit array; box {64, box_rows, 1}.
+int make_operand_map(CUtensorMap* map, const uint16_t* base, int is_bf16, int64_t k_extent,
+                     int64_t rows, int64_t pitch, int planes, int64_t plane_stride, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return B200F_ERR_CUDA;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch % 8) != 0 ||
+        (planes > 1 && (plane_stride % 8) != 0))
+        return B200F_ERR_BAD_ARG;
+    cuuint64_t dims[3] = {(cuuint64_t)k_extent, (cuuint64_t)rows, (cuuint64_t)planes};
+    cuuint64_t pstride = (planes > 1) ? (cuuint64_t)plane_stride * 2 : (cuuint64_t)pitch * 2 * (cuuint64_t)(rows > 0 ? rows : 1);
+    cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, pstride};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                    3, const_cast<uint16_t*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? B200F_OK : B200F_ERR_CUDA;
+}
+
+int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, int64_t col0,
+                  int64_t ncols, cudaStream_t stream) {
+    if (op.nq <= 0 || ncols <= 0) return B200F_OK;
+    if (col0 + ncols > op.nb || op.nb > 0x7fffffffLL) return B200F_ERR_BAD_ARG;
+    CUtensorMap ma, mb;
+    int rc = make_operand_map(&ma, op.a_planes, op.is_bf16, op.d_pad, op.nq, op.a_pitch, op.npl,
+                              op.a_plane_stride, BM);
+    if (rc != B200F_OK) return rc;
+    rc = make_operand_map(&mb, op.b_planes, op.is_bf16, op.d_pad, op.nb, op.b_pitch, op.npl,
+                          op.b_plane_stride, BN);
+    if (rc != B200F_OK) return rc;
+
+    p.nq = op.nq;
+    p.col0 = col0;
+    p.ncols_end = col0 + ncols;
+    p.ntiles = plan.ntiles;
+    p.tiles_per_range = plan.tiles_per_range;
+    p.nqb = plan.nqb;
+    p.P = plan.P;
+    p.kb_per_pass = (int)ceil_div64(op.d_pad, BK);
+    if (op.npl == 1) {
+        p.npass = 1;
+        p.pass_a = 0;
+        p.pass_b = 0;
+    } else {
+        // smallest products first: (1,1) (0,2) (2,0) (0,1) (1,0) (0,0)
+        p.npass = 6;
+        p.pass_a = 0x010201u;  // nibble i = plane of A in pass i (pass 0 is the lowest nibble)
+        p.pass_b = 0x001021u;
+    }
+    const uint32_t fmt = op.is_bf16 ? 1u : 0u;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+              ((uint32_t)(BM >> 4) << 24);
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        B200F_CUDA_TRY(cudaFuncSetAttribute(gemm_topk_kernel,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set = true;
+    }
+    gemm_topk_kernel<<<plan.grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+}  // namespace
+
+GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
+    GemmPlan g;
+    g.nqb = (int)ceil_div64(nq, BM);
+    g.ntiles = ceil_div64(ncols, BN);
+    if (g.nqb <= 0 || g.ntiles <= 0) {
+        g.nqb = 0; g.ntiles = 0; g.P = 0; g.tiles_per_range = 0; g.grid = 0;
+        return g;
+    }
+    // Number of column ranges: make nqb * P a multiple of the SM count when there is
+    // enough work, keep at least ~32 tiles per range so list warm-up stays cheap.
+    auto gcd = [](int64_t a, int64_t b) { while (b) { int64_t t = a % b; a = b; b = t; } return a; };
+    int64_t P0 = sm_count / gcd(sm_count, g.nqb);
+    int64_t P;
+    if (P0 >= g.ntiles) {
+        P = g.ntiles;
+    } else {
+        int64_t max_mult = g.ntiles / (P0 * 32);
+        int64_t want_waves = 8;
+        int64_t mult = (want_waves * sm_count) / (P0 * g.nqb);
+        if (mult < 1) mult = 1;
+        if (max_mult < 1) max_mult = 1;
+        if (mult > max_mult) mult = max_mult;
+        P = P0 * mult;
+    }
+    if (P > 4096) P = 4096;
+    g.tiles_per_range = ceil_div64(g.ntiles, P);
+    g.P = (int)ceil_div64(g.ntiles, g.tiles_per_range);
+    int64_t items = (int64_t)g.nqb * g.P;
+    g.grid = (int)(items < sm_count ? items : sm_count);
+    return g;
+}
+
+int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
+                     float alpha, const float* bias, int k, float* part_key, int32_t* part_idx,
+                     int32_t* status, cudaStream_t stream) {
+    if (k <= 0 || k > KMAX) return B200F_ERR_UNSUPPORTED;
+    GemmParams p{};
+    p.mode = MODE_TOPK;
+    p.k = k;
+    p.alpha = alpha;
+    p.bias = bias;
+    p.sign = 1.f;
+    p.rowadd = nullptr;
+    p.part_key = part_key;
+    p.part_idx = part_idx;
+    p.out = nullptr;
+    p.ld = 0;
+    p.status = status;
+    return launch_common(op, plan, p, col0, ncols, stream);
+}
+
+int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
+                      float alpha, const float* bias, float sign, const float* rowadd, float* out,
+                      int64_t ld, int32_t* status, cudaStream_t stream) {
+    GemmParams p{};
+    p.mode = MODE_STORE;
+    p.k = 0;
+    p.alpha = alpha;
+    p.bias = bias;
+    p.sign = sign;
+    p.rowadd = rowadd;
+    p.part_key = nullptr;
+    p.part_idx = nullptr;
+    p.out = out;
+    p.ld = ld;
+    p.status = status;
+    return launch_common(op, plan, p, col0, ncols, stream);
+}
+
+}  // namespace b200f

@@ -1,0 +1,377 @@
+// Row-wise kernels: squared norms, append-time conversion, reconstruction,
+// query preparation and the synthetic-data generator.
+//
+// Replaces l2_norm / l2_norm_large / l2_norm_f16 / l2_norm_f16_large
+// (shaders/l2_norm.metal:7-66, shaders/l2_norm_f16.metal:10-67), their dispatch
+// (src/MetalL2Norm.mm:42-89) and the host conversion loops of MetalIndexFlat::add
+// (src/MetalIndexFlat.mm:224-255).  One warp owns one row; lanes read 128-bit
+// vectors and reduce with shuffles.  Squares are formed in fp32 (the reference's
+// "f16" norm kernels square in half precision, which is not reproduced).
+#include "common.cuh"
+
+namespace b200f {
+
+namespace {
+
+constexpr int ROW_THREADS = 256;  // 8 warps = 8 rows per CTA pass
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
+    return __uint_as_float((uint32_t)b << 16);
+}
+// fp32 -> bf16 bits, round to nearest even (src/MetalIndexFlat.mm:231-234)
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ uint16_t float_to_fp16_bits(float f) {
+    return __half_as_ushort(__float2half_rn(f));
+}
+__device__ __forceinline__ float fp16_bits_to_float(uint16_t b) {
+    return __half2float(__ushort_as_half(b));
+}
+
+template <int STORAGE>
+__device__ __forceinline__ float load_elem(const void* rows, int64_t off) {
+    if (STORAGE == B200F_STORAGE_F32) return reinterpret_cast<const float*>(rows)[off];
+    uint16_t b = reinterpret_cast<const uint16_t*>(rows)[off];
+    return STORAGE == B200F_STORAGE_F16 ? fp16_bits_to_float(b) : bf16_bits_to_float(b);
+}
+
+// ---- norms -----------------------------------------------------------------------------
+template <int STORAGE>
+__global__ void row_norms_kernel(const void* __restrict__ rows, int64_t n, int d, int64_t pitch,
+                                 float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
+         r += warps_total) {
+        float s = 0.f;
+        if (STORAGE == B200F_STORAGE_F32) {
+            const float* row = reinterpret_cast<const float*>(rows) + r * pitch;
+            if ((pitch & 3) == 0 && ((uintptr_t)rows & 15) == 0) {
+                const int d4 = d >> 2;
+                const float4* row4 = reinterpret_cast<const float4*>(row);
+                for (int j = lane; j < d4; j += 32) {
+                    float4 v = __ldg(row4 + j);
+                    s = fmaf(v.x, v.x, s);
+                    s = fmaf(v.y, v.y, s);
+                    s = fmaf(v.z, v.z, s);
+                    s = fmaf(v.w, v.w, s);
+                }
+                for (int j = (d4 << 2) + lane; j < d; j += 32) s = fmaf(row[j], row[j], s);
+            } else {
+                for (int j = lane; j < d; j += 32) s = fmaf(row[j], row[j], s);
+            }
+        } else {
+            const uint16_t* row = reinterpret_cast<const uint16_t*>(rows) + r * pitch;
+            if ((pitch & 7) == 0 && ((uintptr_t)rows & 15) == 0) {
+                const int d8 = d >> 3;
+                const uint4* row8 = reinterpret_cast<const uint4*>(row);
+                for (int j = lane; j < d8; j += 32) {
+                    uint4 v = __ldg(row8 + j);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int t = 0; t < 4; t++) {
+                        float a, b;
+                        if (STORAGE == B200F_STORAGE_F16) {
+                            a = fp16_bits_to_float((uint16_t)(w[t] & 0xffffu));
+                            b = fp16_bits_to_float((uint16_t)(w[t] >> 16));
+                        } else {
+                            a = __uint_as_float(w[t] << 16);
+                            b = __uint_as_float(w[t] & 0xffff0000u);
+                        }
+                        s = fmaf(a, a, s);
+                        s = fmaf(b, b, s);
+                    }
+                }
+                for (int j = (d8 << 3) + lane; j < d; j += 32) {
+                    float a = load_elem<STORAGE>(row, j);
+                    s = fmaf(a, a, s);
+                }
+            } else {
+                for (int j = lane; j < d; j += 32) {
+                    float a = load_elem<STORAGE>(row, j);
+                    s = fmaf(a, a, s);
+                }
+            }
+        }
+        s = warp_sum(s);
+        if (lane == 0) out[r] = s;
+    }
+}
+
+// ---- append-time conversion -----------------------------------------------------------
+// One warp per row.  Writes the stored row (pad columns zeroed), the squared norm of
+// the stored values and, for fp32 storage, the three bf16 split planes.
+template <int STORAGE>
+__global__ void store_rows_kernel(const float* __restrict__ src, int64_t n, int d,
+                                  void* __restrict__ dst, int64_t dst_pitch,
+                                  uint16_t* __restrict__ planes, int64_t plane_pitch,
+                                  int64_t plane_stride, float* __restrict__ norms) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
+         r += warps_total) {
+        const float* row = src + r * (int64_t)d;
+        float s = 0.f;
+        if (STORAGE == B200F_STORAGE_F32) {
+            float* out = reinterpret_cast<float*>(dst) + r * dst_pitch;
+            for (int j = lane; j < dst_pitch; j += 32) {
+                float v = (j < d) ? row[j] : 0.f;
+                out[j] = v;
+                s = fmaf(v, v, s);
+            }
+            if (planes) {
+                uint16_t* p0 = planes + r * plane_pitch;
+                uint16_t* p1 = p0 + plane_stride;
+                uint16_t* p2 = p1 + plane_stride;
+                for (int j = lane; j < plane_pitch; j += 32) {
+                    float v = (j < d) ? row[j] : 0.f;
+                    uint16_t b0 = float_to_bf16_bits(v);
+                    float r1 = v - bf16_bits_to_float(b0);
+                    uint16_t b1 = float_to_bf16_bits(r1);
+                    float r2 = r1 - bf16_bits_to_float(b1);
+                    uint16_t b2 = float_to_bf16_bits(r2);
+                    p0[j] = b0;
+                    p1[j] = b1;
+                    p2[j] = b2;
+                }
+            }
+        } else {
+            uint16_t* out = reinterpret_cast<uint16_t*>(dst) + r * dst_pitch;
+            for (int j = lane; j < dst_pitch; j += 32) {
+                float v = (j < d) ? row[j] : 0.f;
+                uint16_t b;
+                float back;
+                if (STORAGE == B200F_STORAGE_F16) {
+                    b = float_to_fp16_bits(v);
+                    back = fp16_bits_to_float(b);
+                } else {
+                    b = float_to_bf16_bits(v);
+                    back = bf16_bits_to_float(b);
+                }
+                out[j] = b;
+                s = fmaf(back, back, s);
+            }
+        }
+        if (norms) {
+            s = warp_sum(s);
+            if (lane == 0) norms[r] = s;
+        }
+    }
+}
+
+template <int STORAGE>
+__global__ void load_rows_kernel(const void* __restrict__ rows, int64_t n, int d, int64_t pitch,
+                                 float* __restrict__ dst) {
+    const int64_t total = n * (int64_t)d;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / d;
+        const int j = (int)(i - r * d);
+        dst[i] = load_elem<STORAGE>(rows, r * pitch + j);
+    }
+}
+
+// ---- query preparation -------------------------------------------------------------------
+// fp32 queries -> operand planes of the tensor path (+ exact fp32 squared norms).
+// npl == 1: one plane in the storage format (fp16 or bf16); npl == 3: bf16 split planes.
+__global__ void prepare_queries_kernel(const float* __restrict__ q, int64_t nq, int d, int storage,
+                                       uint16_t* __restrict__ a, int64_t a_pitch,
+                                       int64_t a_plane_stride, float* __restrict__ qnorm) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nq;
+         r += warps_total) {
+        const float* row = q + r * (int64_t)d;
+        float s = 0.f;
+        for (int j = lane; j < a_pitch || j < d; j += 32) {
+            float v = (j < d) ? row[j] : 0.f;
+            s = fmaf(v, v, s);
+            if (a && j < a_pitch) {
+                uint16_t* p0 = a + r * a_pitch + j;
+                if (storage == B200F_STORAGE_F16) {
+                    *p0 = float_to_fp16_bits(v);
+                } else if (storage == B200F_STORAGE_BF16) {
+                    *p0 = float_to_bf16_bits(v);
+                } else {
+                    uint16_t b0 = float_to_bf16_bits(v);
+                    float r1 = v - bf16_bits_to_float(b0);
+                    uint16_t b1 = float_to_bf16_bits(r1);
+                    float r2 = r1 - bf16_bits_to_float(b1);
+                    p0[0] = b0;
+                    p0[a_plane_stride] = b1;
+                    p0[2 * a_plane_stride] = float_to_bf16_bits(r2);
+                }
+            }
+        }
+        if (qnorm) {
+            s = warp_sum(s);
+            if (lane == 0) qnorm[r] = s;
+        }
+    }
+}
+
+// ---- synthetic generator -------------------------------------------------------------------
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+    return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ float synth_value(uint64_t seed, int64_t row, int col, int dist) {
+    uint64_t h = mix64(seed * 0x9e3779b97f4a7c15ULL + (uint64_t)row * 0xd1342543de82ef95ULL +
+                       (uint64_t)col + 1);
+    h = mix64(h);
+    const float u1 = ((uint32_t)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
+    if (dist == 0) return ((uint32_t)(h >> 40)) * (1.0f / 16777216.0f);   // [0,1)
+    const float u2 = ((uint32_t)(h & 0xffffffu)) * (1.0f / 16777216.0f);
+    return sqrtf(-2.f * logf(u1)) * cospif(2.f * u2);
+}
+
+__global__ void fill_synthetic_kernel(float* __restrict__ dst, int64_t n, int d, int64_t row0,
+                                      uint64_t seed, int dist, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
+         r += warps_total) {
+        float* row = dst + r * (int64_t)d;
+        if (dist == 2) {
+            float s = 0.f;
+            for (int j = lane; j < d; j += 32) {
+                float v = synth_value(seed, row0 + r, j, 1);
+                s = fmaf(v, v, s);
+            }
+            s = warp_sum(s);
+            const float inv = s > 0.f ? rsqrtf(s) : 0.f;
+            for (int j = lane; j < d; j += 32) row[j] = synth_value(seed, row0 + r, j, 1) * inv;
+        } else {
+            for (int j = lane; j < d; j += 32)
+                row[j] = synth_value(seed, row0 + r, j, dist) * (dist == 1 ? scale : 1.f);
+        }
+    }
+}
+
+int grid_for_rows(int64_t n) {
+    int64_t g = ceil_div64(n, ROW_THREADS / 32);
+    int64_t cap = (int64_t)cached_sm_count() * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+}  // namespace
+
+int cached_sm_count() {
+    static int sm = 0;
+    if (sm == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm <= 0) {
+            (void)cudaGetLastError();
+            sm = 0;
+            return kNumSMsDefault;
+        }
+    }
+    return sm;
+}
+
+int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,
+                           int64_t a_pitch, int64_t a_plane_stride, float* qnorm,
+                           cudaStream_t stream) {
+    if (nq <= 0) return B200F_OK;
+    prepare_queries_kernel<<<grid_for_rows(nq), ROW_THREADS, 0, stream>>>(
+            q, nq, d, storage, a_planes, a_pitch, a_plane_stride, qnorm);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+}  // namespace b200f
+
+using namespace b200f;
+
+extern "C" int b200f_row_norms(const void* rows, int storage, int64_t n, int d, int64_t pitch_elems,
+                               float* out, void* stream) {
+    if (n < 0 || d <= 0 || pitch_elems < d || (n > 0 && (!rows || !out))) return B200F_ERR_BAD_ARG;
+    if (n == 0) return B200F_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int g = grid_for_rows(n);
+    switch (storage) {
+        case B200F_STORAGE_F32:
+            row_norms_kernel<B200F_STORAGE_F32><<<g, ROW_THREADS, 0, st>>>(rows, n, d, pitch_elems, out);
+            break;
+        case B200F_STORAGE_F16:
+            row_norms_kernel<B200F_STORAGE_F16><<<g, ROW_THREADS, 0, st>>>(rows, n, d, pitch_elems, out);
+            break;
+        case B200F_STORAGE_BF16:
+            row_norms_kernel<B200F_STORAGE_BF16><<<g, ROW_THREADS, 0, st>>>(rows, n, d, pitch_elems, out);
+            break;
+        default:
+            return B200F_ERR_BAD_ARG;
+    }
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+extern "C" int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
+                                int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
+                                int64_t plane_stride, float* norms_or_null, void* stream) {
+    if (n < 0 || d <= 0 || dst_pitch < d || (n > 0 && (!src || !dst_rows))) return B200F_ERR_BAD_ARG;
+    if (planes && (plane_pitch < d || plane_stride < plane_pitch)) return B200F_ERR_BAD_ARG;
+    if (n == 0) return B200F_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int g = grid_for_rows(n);
+    switch (storage) {
+        case B200F_STORAGE_F32:
+            store_rows_kernel<B200F_STORAGE_F32><<<g, ROW_THREADS, 0, st>>>(
+                    src, n, d, dst_rows, dst_pitch, planes, plane_pitch, plane_stride, norms_or_null);
+            break;
+        case B200F_STORAGE_F16:
+            store_rows_kernel<B200F_STORAGE_F16><<<g, ROW_THREADS, 0, st>>>(
+                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null);
+            break;
+        case B200F_STORAGE_BF16:
+            store_rows_kernel<B200F_STORAGE_BF16><<<g, ROW_THREADS, 0, st>>>(
+                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null);
+            break;
+        default:
+            return B200F_ERR_BAD_ARG;
+    }
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+extern "C" int b200f_load_rows(const void* rows, int storage, int64_t n, int d, int64_t pitch_elems,
+                               float* dst, void* stream) {
+    if (n < 0 || d <= 0 || pitch_elems < d || (n > 0 && (!rows || !dst))) return B200F_ERR_BAD_ARG;
+    if (n == 0) return B200F_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int64_t total = n * (int64_t)d;
+    int64_t g = ceil_div64(total, 256);
+    int64_t cap = (int64_t)cached_sm_count() * 32;
+    if (g > cap) g = cap;
+    switch (storage) {
+        case B200F_STORAGE_F32:
+            load_rows_kernel<B200F_STORAGE_F32><<<(int)g, 256, 0, st>>>(rows, n, d, pitch_elems, dst);
+            break;
+        case B200F_STORAGE_F16:
+            load_rows_kernel<B200F_STORAGE_F16><<<(int)g, 256, 0, st>>>(rows, n, d, pitch_elems, dst);
+            break;
+        case B200F_STORAGE_BF16:
+            load_rows_kernel<B200F_STORAGE_BF16><<<(int)g, 256, 0, st>>>(rows, n, d, pitch_elems, dst);
+            break;
+        default:
+            return B200F_ERR_BAD_ARG;
+    }
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+extern "C" int b200f_fill_synthetic(float* dst, int64_t n, int d, int64_t row0, uint64_t seed,
+                                    int dist, float scale, void* stream) {
+    if (n < 0 || d <= 0 || dist < 0 || dist > 2 || (n > 0 && !dst)) return B200F_ERR_BAD_ARG;
+    if (n == 0) return B200F_OK;
+    fill_synthetic_kernel<<<grid_for_rows(n), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+            dst, n, d, row0, seed, dist, scale);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}

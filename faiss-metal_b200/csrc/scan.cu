@@ -1,0 +1,379 @@
+// Streaming search for small query batches (nq <= 4): HBM-bound, CUDA cores only.
+//
+// Replaces fused_l2_topk_min / fused_ip_topk_max and their f16storage variants
+// (shaders/fused_l2_topk.metal:19-444, gate in src/MetalDistance.mm:341-354) and the
+// tiny-database direct kernels l2_distance_direct_f16[storage]
+// (shaders/l2_norm_f16.metal:74-123).  Differences by design: every lane streams
+// 128-bit pieces of consecutive rows (the reference walks one whole row per lane),
+// the dot product is fp32, BF16 rows are handled natively, and the per-warp top-k is
+// a sorted warp list (one slot per lane) updated by ballot + shuffle insertion so no
+// candidate is dropped.
+//
+// Work layout: a row of C 16-byte pieces is covered by LPR = min(32, pow2(C)) lanes
+// (ITERS = ceil(C / LPR) pieces per lane); a warp therefore covers 32 / LPR rows per
+// step and U steps per block, keeping U independent 16-byte loads in flight per lane.
+#include "common.cuh"
+
+namespace b200f {
+
+namespace {
+
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_WARPS = SCAN_THREADS / 32;
+constexpr int SCAN_U = 8;
+constexpr unsigned FULL = 0xffffffffu;
+
+struct ScanParams {
+    const float* queries;   // [nq][d]
+    const void* rows;
+    int64_t pitch_bytes;
+    const float* norms;     // null for inner product
+    int64_t nb;
+    int64_t col0, col1;     // rows [col0, col1) are scanned
+    int d;
+    int nq;
+    int k;
+    int metric;
+    int C;                  // 16-byte pieces per row
+    int lpr;                // lanes per row (power of two)
+    int iters;              // pieces per lane
+    int qstride;            // floats per query in shared memory (C * E)
+    float* part_key;        // top-k mode: [nq][P][k]
+    int32_t* part_idx;
+    float* out;             // store mode: [nq][ld]
+    int64_t ld;
+};
+
+template <int STORAGE>
+struct Piece {
+    static constexpr int E = (STORAGE == B200F_STORAGE_F32) ? 4 : 8;
+};
+
+template <int STORAGE>
+__device__ __forceinline__ void unpack(const uint4& v, float (&x)[Piece<STORAGE>::E]) {
+    if (STORAGE == B200F_STORAGE_F32) {
+        x[0] = __uint_as_float(v.x);
+        x[1] = __uint_as_float(v.y);
+        x[2] = __uint_as_float(v.z);
+        x[3] = __uint_as_float(v.w);
+    } else if (STORAGE == B200F_STORAGE_BF16) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            x[2 * t] = __uint_as_float(w[t] << 16);
+            x[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u);
+        }
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+            x[2 * t] = f.x;
+            x[2 * t + 1] = f.y;
+        }
+    }
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// (key, id) lexicographic "a before b"
+__device__ __forceinline__ bool before(float ka, int ia, float kb, int ib) {
+    return (ka < kb) || (ka == kb && (unsigned)ia < (unsigned)ib);
+}
+
+// Sorted warp list: lane j holds rank j.  All 32 lanes call this together.
+__device__ __forceinline__ void warp_insert(float& lk, int& li, float s, int id, int lane) {
+    const bool stays = before(lk, li, s, id);
+    const int pos = __popc(__ballot_sync(FULL, stays));
+    const float upk = __shfl_up_sync(FULL, lk, 1);
+    const int upi = __shfl_up_sync(FULL, li, 1);
+    if (lane == pos) {
+        lk = s;
+        li = id;
+    } else if (lane > pos) {
+        lk = upk;
+        li = upi;
+    }
+}
+
+template <int STORAGE, int NQ, bool STORE>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_kernel(const ScanParams p) {
+    constexpr int E = Piece<STORAGE>::E;
+    extern __shared__ __align__(16) float sq[];  // [NQ][qstride] queries, then merge area
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+
+    // stage the queries (zero padded to whole pieces)
+    for (int i = threadIdx.x; i < NQ * p.qstride; i += SCAN_THREADS) {
+        const int qi = i / p.qstride;
+        const int j = i - qi * p.qstride;
+        sq[i] = (qi < p.nq && j < p.d) ? p.queries[(int64_t)qi * p.d + j] : 0.f;
+    }
+    __syncthreads();
+
+    const int lpr = p.lpr;
+    const int rps = 32 / lpr;            // rows per warp step
+    const int cl = lane & (lpr - 1);     // piece lane inside the row
+    const int sub = lane / lpr;          // which of the rps rows
+    const int rows_per_block = rps * SCAN_U;
+    const int64_t nrows = p.col1 - p.col0;
+    const int64_t nblocks = ceil_div64(nrows, rows_per_block);
+    const int64_t gw = (int64_t)blockIdx.x * SCAN_WARPS + warp;
+    const int64_t total_warps = (int64_t)gridDim.x * SCAN_WARPS;
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(p.rows);
+    const bool l2 = p.metric == B200F_METRIC_L2;
+
+    float lk[NQ];
+    int li[NQ];
+    float thr[NQ];
+    int thr_id[NQ];
+#pragma unroll
+    for (int qi = 0; qi < NQ; qi++) {
+        lk[qi] = CUDART_INF_F;
+        li[qi] = -1;
+        thr[qi] = CUDART_INF_F;
+        thr_id[qi] = -1;
+    }
+
+    for (int64_t blk = gw; blk < nblocks; blk += total_warps) {
+        const int64_t row_base = p.col0 + blk * rows_per_block;
+        float acc[SCAN_U][NQ];
+#pragma unroll
+        for (int u = 0; u < SCAN_U; u++)
+#pragma unroll
+            for (int qi = 0; qi < NQ; qi++) acc[u][qi] = 0.f;
+
+        for (int it = 0; it < p.iters; it++) {
+            const int piece = it * lpr + cl;
+            const bool pv = piece < p.C;
+            uint4 v[SCAN_U];
+#pragma unroll
+            for (int u = 0; u < SCAN_U; u++) {
+                const int64_t row = row_base + u * rps + sub;
+                if (pv && row < p.col1)
+                    v[u] = ldg_stream(base + row * p.pitch_bytes + (int64_t)piece * 16);
+                else
+                    v[u] = make_uint4(0, 0, 0, 0);
+            }
+            float qf[NQ][E];
+#pragma unroll
+            for (int qi = 0; qi < NQ; qi++) {
+                const float4* src = reinterpret_cast<const float4*>(sq + qi * p.qstride + (pv ? piece : 0) * E);
+#pragma unroll
+                for (int e4 = 0; e4 < E / 4; e4++) {
+                    const float4 f = src[e4];
+                    qf[qi][4 * e4] = f.x;
+                    qf[qi][4 * e4 + 1] = f.y;
+                    qf[qi][4 * e4 + 2] = f.z;
+                    qf[qi][4 * e4 + 3] = f.w;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < SCAN_U; u++) {
+                float x[E];
+                unpack<STORAGE>(v[u], x);
+#pragma unroll
+                for (int qi = 0; qi < NQ; qi++)
+#pragma unroll
+                    for (int e = 0; e < E; e++) acc[u][qi] = fmaf(qf[qi][e], x[e], acc[u][qi]);
+            }
+        }
+        // reduce the partial dot products over the lpr lanes of each row
+        for (int o = lpr >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < SCAN_U; u++)
+#pragma unroll
+                for (int qi = 0; qi < NQ; qi++)
+                    acc[u][qi] += __shfl_xor_sync(FULL, acc[u][qi], o);
+        }
+        // lane cl == 0 of each row group owns the row's candidates
+#pragma unroll
+        for (int u = 0; u < SCAN_U; u++) {
+            const int64_t row = row_base + u * rps + sub;
+            const bool owner = (cl == 0) && row < p.col1;
+            float nrm = 0.f;
+            if (owner && l2) nrm = __ldg(p.norms + row);
+#pragma unroll
+            for (int qi = 0; qi < NQ; qi++) {
+                const float key = l2 ? fmaf(-2.f, acc[u][qi], nrm) : -acc[u][qi];
+                if (STORE) {
+                    if (owner && qi < p.nq) p.out[(int64_t)qi * p.ld + (row - p.col0)] = key;
+                } else {
+                    const bool hit = owner && before(key, (int)row, thr[qi], thr_id[qi]);
+                    unsigned m = __ballot_sync(FULL, hit);
+                    while (m) {
+                        const int src = __ffs(m) - 1;
+                        m &= m - 1;
+                        const float s = __shfl_sync(FULL, key, src);
+                        const int id = __shfl_sync(FULL, (int)row, src);
+                        if (before(s, id, thr[qi], thr_id[qi])) {
+                            warp_insert(lk[qi], li[qi], s, id, lane);
+                            thr[qi] = __shfl_sync(FULL, lk[qi], p.k - 1);
+                            thr_id[qi] = __shfl_sync(FULL, li[qi], p.k - 1);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    if (STORE) return;
+
+    // CTA merge: every warp publishes its lists, warp qi folds them for query qi.
+    __syncthreads();  // queries in shared memory are no longer needed
+    float* mk = sq;                                                  // [SCAN_WARPS][NQ][32]
+    int* mi = reinterpret_cast<int*>(sq + SCAN_WARPS * NQ * 32);
+#pragma unroll
+    for (int qi = 0; qi < NQ; qi++) {
+        mk[(warp * NQ + qi) * 32 + lane] = lk[qi];
+        mi[(warp * NQ + qi) * 32 + lane] = li[qi];
+    }
+    __syncthreads();
+    if (warp < NQ && warp < p.nq) {
+        const int qi = warp;
+        float k0 = mk[(0 * NQ + qi) * 32 + lane];
+        int i0 = mi[(0 * NQ + qi) * 32 + lane];
+        float t = __shfl_sync(FULL, k0, p.k - 1);
+        int tid = __shfl_sync(FULL, i0, p.k - 1);
+        for (int w = 1; w < SCAN_WARPS; w++) {
+            for (int j = 0; j < p.k; j++) {
+                const float s = mk[(w * NQ + qi) * 32 + j];
+                const int id = mi[(w * NQ + qi) * 32 + j];
+                if (id < 0) break;  // sorted: the rest of this list is empty
+                if (before(s, id, t, tid)) {
+                    warp_insert(k0, i0, s, id, lane);
+                    t = __shfl_sync(FULL, k0, p.k - 1);
+                    tid = __shfl_sync(FULL, i0, p.k - 1);
+                } else {
+                    break;  // sorted: nothing later in this list can enter either
+                }
+            }
+        }
+        if (lane < p.k) {
+            const int64_t o = ((int64_t)qi * gridDim.x + blockIdx.x) * p.k + lane;
+            p.part_key[o] = k0;
+            p.part_idx[o] = i0;
+        }
+    }
+}
+
+size_t scan_smem_bytes(int nq_t, int qstride) {
+    size_t a = (size_t)nq_t * qstride * 4;
+    size_t b = (size_t)SCAN_WARPS * nq_t * 32 * 8;
+    return a > b ? a : b;
+}
+
+void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch) {
+    const int E = storage == B200F_STORAGE_F32 ? 4 : 8;
+    const int es = storage == B200F_STORAGE_F32 ? 4 : 2;
+    p.pitch_bytes = row_pitch * es;
+    p.C = (d + E - 1) / E;
+    int lpr = 1;
+    while (lpr < p.C && lpr < 32) lpr <<= 1;
+    p.lpr = lpr;
+    p.iters = (p.C + lpr - 1) / lpr;
+    p.qstride = p.C * E;
+}
+
+template <int STORAGE, bool STORE>
+int launch_nq(const ScanParams& p, int grid, size_t smem, cudaStream_t stream) {
+#define B200F_SCAN_CASE(NQ)                                                                      \
+    {                                                                                            \
+        if (smem > 48 * 1024)                                                                    \
+            B200F_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<STORAGE, NQ, STORE>,                 \
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                                (int)smem));                                     \
+        scan_kernel<STORAGE, NQ, STORE><<<grid, SCAN_THREADS, smem, stream>>>(p);                \
+    }
+    if (p.nq == 1) B200F_SCAN_CASE(1)
+    else if (p.nq == 2) B200F_SCAN_CASE(2)
+    else B200F_SCAN_CASE(4)
+#undef B200F_SCAN_CASE
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+template <bool STORE>
+int launch_storage(const ScanParams& p, int storage, int grid, cudaStream_t stream) {
+    const int nq_t = p.nq == 1 ? 1 : (p.nq == 2 ? 2 : 4);
+    const size_t smem = scan_smem_bytes(nq_t, p.qstride);
+    if (smem > 200 * 1024) return B200F_ERR_UNSUPPORTED;
+    switch (storage) {
+        case B200F_STORAGE_F32: return launch_nq<B200F_STORAGE_F32, STORE>(p, grid, smem, stream);
+        case B200F_STORAGE_F16: return launch_nq<B200F_STORAGE_F16, STORE>(p, grid, smem, stream);
+        case B200F_STORAGE_BF16: return launch_nq<B200F_STORAGE_BF16, STORE>(p, grid, smem, stream);
+    }
+    return B200F_ERR_BAD_ARG;
+}
+
+int scan_grid(int64_t nrows, int d, int storage, int sm_count) {
+    ScanParams t{};
+    fill_geometry(t, storage, d, d);
+    const int rows_per_block = (32 / t.lpr) * SCAN_U;
+    const int64_t nblocks = ceil_div64(nrows, rows_per_block);
+    int64_t g = ceil_div64(nblocks, SCAN_WARPS);
+    const int64_t cap = (int64_t)sm_count * 4;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+}  // namespace
+
+ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count) {
+    (void)nq;
+    ScanPlan s;
+    s.grid = scan_grid(nb, d, storage, sm_count);
+    s.threads = SCAN_THREADS;
+    return s;
+}
+
+int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part_key,
+                     int32_t* part_idx, cudaStream_t stream) {
+    if (a.nq < 1 || a.nq > 4 || a.k < 1 || a.k > 32) return B200F_ERR_UNSUPPORTED;
+    ScanParams p{};
+    fill_geometry(p, a.storage, a.d, a.row_pitch);
+    p.queries = a.queries;
+    p.rows = a.rows;
+    p.norms = a.norms;
+    p.nb = a.nb;
+    p.col0 = 0;
+    p.col1 = a.nb;
+    p.d = a.d;
+    p.nq = (int)a.nq;
+    p.k = a.k;
+    p.metric = a.metric;
+    p.part_key = part_key;
+    p.part_idx = part_idx;
+    return launch_storage<false>(p, a.storage, plan.grid, stream);
+}
+
+int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, float* out, int64_t ld,
+                      int sm_count, cudaStream_t stream) {
+    if (a.nq < 1 || a.nq > 4) return B200F_ERR_UNSUPPORTED;
+    if (ncols <= 0) return B200F_OK;
+    ScanParams p{};
+    fill_geometry(p, a.storage, a.d, a.row_pitch);
+    p.queries = a.queries;
+    p.rows = a.rows;
+    p.norms = a.norms;
+    p.nb = a.nb;
+    p.col0 = col0;
+    p.col1 = col0 + ncols;
+    p.d = a.d;
+    p.nq = (int)a.nq;
+    p.k = 1;
+    p.metric = a.metric;
+    p.out = out;
+    p.ld = ld;
+    return launch_storage<true>(p, a.storage, scan_grid(ncols, a.d, a.storage, sm_count), stream);
+}
+
+}  // namespace b200f

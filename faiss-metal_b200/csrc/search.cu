@@ -1,0 +1,369 @@
+// Shard-local search driver: path choice, scratch layout, kernel sequencing.
+//
+// Replaces the encode sequence of MetalIndexFlat::search (src/MetalIndexFlat.mm:358-378)
+// and the path selection of MetalDistance / MetalSelect (src/MetalDistance.mm:107-128,
+// 327-363; src/MetalSelect.mm:34-89).  Paths here depend on (nq, k) only:
+//   nq <= 4            streaming scan (scan.cu)
+//   nq  > 4            tensor-core GEMM (gemm_topk.cu)
+//   k  <= 32           top-k fused into the distance kernel, partial lists merged after
+//   k   > 32           distance keys written per column chunk, running sort-select
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace b200f {
+
+namespace {
+
+constexpr int64_t MATRIX_BUDGET_BYTES = 512ll << 20;
+constexpr int SCAN_GROUP = 4;
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct SearchPlan {
+    int path;         // B200F_PATH_SCAN or B200F_PATH_TENSOR
+    bool fused;       // k <= 32
+    int npl;
+    int64_t a_pitch, a_plane_stride;
+    GemmPlan gemm;    // tensor path (fused: whole shard; chunked: per chunk)
+    ScanPlan scan;
+    int64_t chunk_cols;
+    int64_t ngroups;  // scan path: query groups of SCAN_GROUP
+    size_t off_qnorm, off_a, off_part_key, off_part_idx, off_matrix, off_run_key, off_run_idx;
+    size_t total;
+};
+
+bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool pairwise,
+               SearchPlan& pl) {
+    if (nq < 0 || nb < 0 || d <= 0 || k <= 0 || storage < 0 || storage > 2) return false;
+    const int sm = cached_sm_count();
+    pl = SearchPlan{};
+    pl.path = path;
+    if (path == B200F_PATH_AUTO) pl.path = (nq <= SCAN_GROUP) ? B200F_PATH_SCAN : B200F_PATH_TENSOR;
+    pl.fused = (k <= B200F_FUSED_MAX_K) && !pairwise;
+    pl.npl = (storage == B200F_STORAGE_F32) ? 3 : 1;
+    pl.a_pitch = round_up64(d, 8);
+    pl.a_plane_stride = round_up64((nq > 0 ? nq : 1) * pl.a_pitch, 128);
+    pl.ngroups = ceil_div64(nq, SCAN_GROUP);
+    size_t off = 0;
+    pl.off_qnorm = off;
+    off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+    if (pl.path == B200F_PATH_TENSOR) {
+        pl.off_a = off;
+        off += align256((size_t)pl.npl * pl.a_plane_stride * 2);
+    }
+    if (pairwise) {
+        pl.gemm = plan_gemm(nq, nb, sm);
+        pl.total = off;
+        return true;
+    }
+    if (pl.fused) {
+        int64_t P;
+        if (pl.path == B200F_PATH_TENSOR) {
+            pl.gemm = plan_gemm(nq, nb, sm);
+            P = pl.gemm.P;
+        } else {
+            pl.scan = plan_scan(nq, nb, d, storage, sm);
+            P = pl.scan.grid;
+        }
+        if (P < 1) P = 1;
+        pl.off_part_key = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * P * k * 4);
+        pl.off_part_idx = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * P * k * 4);
+    } else {
+        int64_t cols = MATRIX_BUDGET_BYTES / (4 * (nq > 0 ? nq : 1));
+        cols &= ~(int64_t)255;
+        if (cols < 1024) cols = 1024;
+        const int64_t nb_pad = round_up64(nb > 0 ? nb : 1, 256);
+        if (cols > nb_pad) cols = nb_pad;
+        pl.chunk_cols = cols;
+        pl.gemm = plan_gemm(nq, cols, sm);
+        pl.off_matrix = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * cols * 4);
+        pl.off_run_key = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * k * 4);
+        pl.off_run_idx = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * k * 4);
+    }
+    pl.total = off;
+    return true;
+}
+
+__global__ void fill_pad_kernel(float* dist, int64_t* labels, int64_t n, float pad) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        dist[i] = pad;
+        labels[i] = -1;
+    }
+}
+
+// scan path of b200f_pairwise: keys -> scores
+__global__ void finish_matrix_kernel(float* m, int64_t nq, int64_t ncols, int64_t ld, float sign,
+                                     const float* qnorm) {
+    const int64_t total = nq * ncols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t q = i / ncols;
+        const int64_t c = i - q * ncols;
+        m[q * ld + c] = sign * m[q * ld + c] + (qnorm ? qnorm[q] : 0.f);
+    }
+}
+
+int validate(const B200FSearchArgs* a, bool pairwise) {
+    if (!a) return B200F_ERR_BAD_ARG;
+    if (a->nq < 0 || a->nb < 0 || a->d <= 0) return B200F_ERR_BAD_ARG;
+    if (a->storage < 0 || a->storage > 2) return B200F_ERR_BAD_ARG;
+    if (a->metric != B200F_METRIC_L2 && a->metric != B200F_METRIC_INNER_PRODUCT)
+        return B200F_ERR_BAD_ARG;
+    if (!pairwise && a->k <= 0) return B200F_ERR_BAD_ARG;
+    if (!pairwise && a->k > B200F_MAX_K) return B200F_ERR_UNSUPPORTED;
+    if (a->nb > 0x7fffffffLL) return B200F_ERR_UNSUPPORTED;  // int32 row numbers inside a shard
+    if (a->path < B200F_PATH_AUTO || a->path > B200F_PATH_TENSOR) return B200F_ERR_BAD_ARG;
+    if (a->nq > 0 && !a->queries) return B200F_ERR_BAD_ARG;
+    if (!pairwise && a->nq > 0 && (!a->out_dist || !a->out_labels)) return B200F_ERR_BAD_ARG;
+    if (a->nb > 0) {
+        if (!a->rows) return B200F_ERR_BAD_ARG;
+        const int e = a->storage == B200F_STORAGE_F32 ? 4 : 8;
+        if (a->row_pitch < a->d || (a->row_pitch % e) != 0 ||
+            (reinterpret_cast<uintptr_t>(a->rows) & 15) != 0)
+            return B200F_ERR_BAD_ARG;
+        if (a->metric == B200F_METRIC_L2 && !a->norms) return B200F_ERR_BAD_ARG;
+    }
+    if ((reinterpret_cast<uintptr_t>(a->scratch) & 255) != 0) return B200F_ERR_BAD_ARG;
+    return B200F_OK;
+}
+
+int fill_operands(const B200FSearchArgs& a, const SearchPlan& pl, uint8_t* scratch,
+                  GemmOperands& op) {
+    op.a_planes = reinterpret_cast<const uint16_t*>(scratch + pl.off_a);
+    op.a_pitch = pl.a_pitch;
+    op.a_plane_stride = pl.a_plane_stride;
+    op.npl = pl.npl;
+    op.nq = a.nq;
+    op.nb = a.nb;
+    op.d_pad = (int)round_up64(a.d, 8);
+    if (a.storage == B200F_STORAGE_F32) {
+        if (!a.planes || a.plane_pitch < op.d_pad || (a.plane_pitch % 8) != 0 ||
+            (a.plane_stride % 8) != 0)
+            return B200F_ERR_BAD_ARG;
+        op.b_planes = a.planes;
+        op.b_pitch = a.plane_pitch;
+        op.b_plane_stride = a.plane_stride;
+        op.is_bf16 = 1;
+    } else {
+        if (a.row_pitch < op.d_pad) return B200F_ERR_BAD_ARG;
+        op.b_planes = reinterpret_cast<const uint16_t*>(a.rows);
+        op.b_pitch = a.row_pitch;
+        op.b_plane_stride = 0;
+        op.is_bf16 = a.storage == B200F_STORAGE_BF16;
+    }
+    return B200F_OK;
+}
+
+}  // namespace
+
+}  // namespace b200f
+
+using namespace b200f;
+
+extern "C" const char* b200f_status_string(int status) {
+    switch (status) {
+        case B200F_OK: return "ok";
+        case B200F_ERR_BAD_ARG: return "bad argument";
+        case B200F_ERR_UNSUPPORTED: return "unsupported size (k > 4096 or more than 2^31-1 rows in a shard)";
+        case B200F_ERR_SCRATCH: return "scratch buffer too small";
+        case B200F_ERR_CUDA: return "CUDA call failed";
+        case B200F_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+        case B200F_ERR_NO_DEVICE: return "no sm_100 device (there is no CPU fallback)";
+        case B200F_ERR_OOM: return "out of device or pinned host memory";
+        case B200F_ERR_RANGE: return "key out of range";
+        case B200F_ERR_STATE: return "token already consumed";
+    }
+    return "unknown status";
+}
+
+extern "C" int b200f_device_count(int* count) {
+    if (!count) return B200F_ERR_BAD_ARG;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        *count = 0;
+        return B200F_ERR_NO_DEVICE;
+    }
+    *count = n;
+    return B200F_OK;
+}
+
+extern "C" int b200f_device_caps(int device, B200FCaps* caps) {
+    if (!caps) return B200F_ERR_BAD_ARG;
+    std::memset(caps, 0, sizeof(*caps));
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        (void)cudaGetLastError();
+        return B200F_ERR_NO_DEVICE;
+    }
+    if (device < 0) {
+        if (cudaGetDevice(&device) != cudaSuccess) return B200F_ERR_CUDA;
+    }
+    if (device >= n) return B200F_ERR_BAD_ARG;
+    cudaDeviceProp prop;
+    B200F_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    caps->device = device;
+    caps->cc_major = prop.major;
+    caps->cc_minor = prop.minor;
+    caps->sm_count = prop.multiProcessorCount;
+    caps->max_smem_per_block = (int32_t)prop.sharedMemPerBlockOptin;
+    caps->l2_bytes = prop.l2CacheSize;
+    caps->hbm_bytes = (int64_t)prop.totalGlobalMem;
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, device) == cudaSuccess) caps->sm_clock_khz = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, device) == cudaSuccess) caps->mem_clock_khz = v;
+    (void)cudaGetLastError();
+    caps->supported = (prop.major == 10) ? 1 : 0;
+    std::snprintf(caps->name, sizeof(caps->name), "%s", prop.name);
+    return B200F_OK;
+}
+
+extern "C" size_t b200f_search_scratch_bytes(int64_t nq, int64_t nb, int d, int k, int storage,
+                                             int path) {
+    SearchPlan pl;
+    if (!make_plan(nq, nb, d, k, storage, path, false, pl)) return 0;
+    return pl.total + 256;
+}
+
+extern "C" int b200f_search(const B200FSearchArgs* a) {
+    int rc = validate(a, false);
+    if (rc != B200F_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    if (a->nq == 0) return B200F_OK;
+    if (a->status) B200F_CUDA_TRY(cudaMemsetAsync(a->status, 0, 4 * sizeof(int32_t), st));
+    const bool l2 = a->metric == B200F_METRIC_L2;
+    if (a->nb == 0) {
+        const int64_t n = a->nq * a->k;
+        fill_pad_kernel<<<(int)(ceil_div64(n, 256) < 1024 ? ceil_div64(n, 256) : 1024), 256, 0, st>>>(
+                a->out_dist, a->out_labels, n, l2 ? kHostInf : -kHostInf);
+        B200F_LAUNCH_CHECK();
+        return B200F_OK;
+    }
+    SearchPlan pl;
+    if (!make_plan(a->nq, a->nb, a->d, a->k, a->storage, a->path, false, pl)) return B200F_ERR_BAD_ARG;
+    if (!a->scratch || a->scratch_bytes < pl.total) return B200F_ERR_SCRATCH;
+    uint8_t* scratch = static_cast<uint8_t*>(a->scratch);
+    float* qnorm = reinterpret_cast<float*>(scratch + pl.off_qnorm);
+    const int sm = cached_sm_count();
+    const float alpha = l2 ? -2.f : -1.f;
+    const float* bias = l2 ? a->norms : nullptr;
+
+    GemmOperands op{};
+    if (pl.path == B200F_PATH_TENSOR) {
+        rc = fill_operands(*a, pl, scratch, op);
+        if (rc != B200F_OK) return rc;
+        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage,
+                                    reinterpret_cast<uint16_t*>(scratch + pl.off_a), pl.a_pitch,
+                                    pl.a_plane_stride, qnorm, st);
+    } else {
+        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, st);
+    }
+    if (rc != B200F_OK) return rc;
+
+    if (pl.fused) {
+        float* part_key = reinterpret_cast<float*>(scratch + pl.off_part_key);
+        int32_t* part_idx = reinterpret_cast<int32_t*>(scratch + pl.off_part_idx);
+        int P;
+        if (pl.path == B200F_PATH_TENSOR) {
+            P = pl.gemm.P;
+            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, alpha, bias, a->k, part_key, part_idx,
+                                  a->status, st);
+            if (rc != B200F_OK) return rc;
+        } else {
+            P = pl.scan.grid;
+            for (int64_t g = 0; g < pl.ngroups; g++) {
+                B200FSearchArgs sub = *a;
+                sub.queries = a->queries + g * SCAN_GROUP * (int64_t)a->d;
+                sub.nq = (a->nq - g * SCAN_GROUP) < SCAN_GROUP ? (a->nq - g * SCAN_GROUP) : SCAN_GROUP;
+                rc = launch_scan_topk(sub, pl.scan, part_key + g * SCAN_GROUP * (int64_t)P * a->k,
+                                      part_idx + g * SCAN_GROUP * (int64_t)P * a->k, st);
+                if (rc != B200F_OK) return rc;
+            }
+        }
+        return launch_merge_partials(part_key, part_idx, P, a->nq, a->k, a->metric, qnorm,
+                                     a->label_base, a->out_dist, a->out_labels, st);
+    }
+
+    // k > 32: distance keys per column chunk + running selection
+    float* matrix = reinterpret_cast<float*>(scratch + pl.off_matrix);
+    float* run_key = reinterpret_cast<float*>(scratch + pl.off_run_key);
+    int32_t* run_idx = reinterpret_cast<int32_t*>(scratch + pl.off_run_idx);
+    int has_prev = 0;
+    for (int64_t c0 = 0; c0 < a->nb; c0 += pl.chunk_cols) {
+        const int64_t nc = (a->nb - c0) < pl.chunk_cols ? (a->nb - c0) : pl.chunk_cols;
+        if (pl.path == B200F_PATH_TENSOR) {
+            GemmPlan g = plan_gemm(a->nq, nc, sm);
+            rc = launch_gemm_store(op, g, c0, nc, alpha, bias, 1.f, nullptr, matrix, pl.chunk_cols,
+                                   a->status, st);
+            if (rc != B200F_OK) return rc;
+        } else {
+            for (int64_t g = 0; g < pl.ngroups; g++) {
+                B200FSearchArgs sub = *a;
+                sub.queries = a->queries + g * SCAN_GROUP * (int64_t)a->d;
+                sub.nq = (a->nq - g * SCAN_GROUP) < SCAN_GROUP ? (a->nq - g * SCAN_GROUP) : SCAN_GROUP;
+                rc = launch_scan_store(sub, c0, nc, matrix + g * SCAN_GROUP * pl.chunk_cols,
+                                       pl.chunk_cols, sm, st);
+                if (rc != B200F_OK) return rc;
+            }
+        }
+        rc = launch_select_chunk(matrix, a->nq, nc, pl.chunk_cols, c0, a->k, has_prev, run_key,
+                                 run_idx, a->status, st);
+        if (rc != B200F_OK) return rc;
+        has_prev = 1;
+    }
+    return launch_finalize_lists(run_key, run_idx, a->nq, a->k, a->metric, qnorm, a->label_base,
+                                 a->out_dist, a->out_labels, st);
+}
+
+extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64_t ld_out) {
+    int rc = validate(a, true);
+    if (rc != B200F_OK) return rc;
+    if (a->nq == 0 || a->nb == 0) return B200F_OK;
+    if (!out_matrix || ld_out < a->nb) return B200F_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    if (a->status) B200F_CUDA_TRY(cudaMemsetAsync(a->status, 0, 4 * sizeof(int32_t), st));
+    SearchPlan pl;
+    if (!make_plan(a->nq, a->nb, a->d, 1, a->storage, a->path, true, pl)) return B200F_ERR_BAD_ARG;
+    if (!a->scratch || a->scratch_bytes < pl.total) return B200F_ERR_SCRATCH;
+    uint8_t* scratch = static_cast<uint8_t*>(a->scratch);
+    float* qnorm = reinterpret_cast<float*>(scratch + pl.off_qnorm);
+    const bool l2 = a->metric == B200F_METRIC_L2;
+    const float alpha = l2 ? -2.f : -1.f;
+    const float* bias = l2 ? a->norms : nullptr;
+    const int sm = cached_sm_count();
+    if (pl.path == B200F_PATH_TENSOR) {
+        GemmOperands op{};
+        rc = fill_operands(*a, pl, scratch, op);
+        if (rc != B200F_OK) return rc;
+        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage,
+                                    reinterpret_cast<uint16_t*>(scratch + pl.off_a), pl.a_pitch,
+                                    pl.a_plane_stride, qnorm, st);
+        if (rc != B200F_OK) return rc;
+        return launch_gemm_store(op, pl.gemm, 0, a->nb, alpha, bias, l2 ? 1.f : -1.f,
+                                 l2 ? qnorm : nullptr, out_matrix, ld_out, a->status, st);
+    }
+    rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, st);
+    if (rc != B200F_OK) return rc;
+    for (int64_t g = 0; g < pl.ngroups; g++) {
+        B200FSearchArgs sub = *a;
+        sub.queries = a->queries + g * SCAN_GROUP * (int64_t)a->d;
+        sub.nq = (a->nq - g * SCAN_GROUP) < SCAN_GROUP ? (a->nq - g * SCAN_GROUP) : SCAN_GROUP;
+        rc = launch_scan_store(sub, 0, a->nb, out_matrix + g * SCAN_GROUP * ld_out, ld_out, sm, st);
+        if (rc != B200F_OK) return rc;
+    }
+    const int64_t total = a->nq * a->nb;
+    int64_t g = ceil_div64(total, 256);
+    if (g > (int64_t)sm * 16) g = (int64_t)sm * 16;
+    finish_matrix_kernel<<<(int)g, 256, 0, st>>>(out_matrix, a->nq, a->nb, ld_out, l2 ? 1.f : -1.f,
+                                                 l2 ? qnorm : nullptr);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}

@@ -1,0 +1,529 @@
+// Selection and merge kernels.
+//
+// Replaces warp_select_min/max (shaders/warp_select.metal:11-114), block_select_min/max
+// (shaders/block_select.metal:111-274), their dispatch (src/MetalSelect.mm:34-108) and the
+// final list merge inside the fused kernels (shaders/fused_l2_topk.metal:88-131).
+//
+// Two building blocks:
+//  * merge_small: k <= 32.  One CTA per query; each warp folds a subset of sorted input
+//    lists into a sorted warp list (lane j = rank j) by ballot + shuffle insertion with
+//    early exit, then warp 0 folds the warp lists.
+//  * sort_select: any k <= 4096.  One CTA per query streams candidates, keeps those under
+//    the current k-th best in a shared-memory buffer of 8192 packed (key, payload) words
+//    and compacts with a bitonic sort whenever the buffer could overflow.  Results are
+//    exact for every k (the reference's block_select keeps only 8 real results per row).
+//
+// Keys are "smaller is better" everywhere: L2 key = distance, inner product key = -dot.
+// Ties go to the lower id.
+#include "common.cuh"
+
+namespace b200f {
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+// ---------------------------------------------------------------------------------------
+// merge_small
+// ---------------------------------------------------------------------------------------
+constexpr int MS_THREADS = 256;
+constexpr int MS_WARPS = MS_THREADS / 32;
+
+template <typename IdT>
+__device__ __forceinline__ bool before_id(float ka, IdT ia, float kb, IdT ib) {
+    // negative ids are empty slots and sort last among equal keys
+    typedef typename std::conditional<sizeof(IdT) == 8, unsigned long long, unsigned>::type U;
+    return (ka < kb) || (ka == kb && (U)ia < (U)ib);
+}
+
+template <typename IdT>
+__device__ __forceinline__ IdT shfl_id(IdT v, int src) {
+    if (sizeof(IdT) == 8) {
+        unsigned long long u = (unsigned long long)v;
+        unsigned lo = __shfl_sync(FULL, (unsigned)u, src);
+        unsigned hi = __shfl_sync(FULL, (unsigned)(u >> 32), src);
+        return (IdT)(((unsigned long long)hi << 32) | lo);
+    } else {
+        return (IdT)__shfl_sync(FULL, (int)v, src);
+    }
+}
+template <typename IdT>
+__device__ __forceinline__ IdT shfl_up_id(IdT v) {
+    if (sizeof(IdT) == 8) {
+        unsigned long long u = (unsigned long long)v;
+        unsigned lo = __shfl_up_sync(FULL, (unsigned)u, 1);
+        unsigned hi = __shfl_up_sync(FULL, (unsigned)(u >> 32), 1);
+        return (IdT)(((unsigned long long)hi << 32) | lo);
+    } else {
+        return (IdT)__shfl_up_sync(FULL, (int)v, 1);
+    }
+}
+
+template <typename IdT>
+__device__ __forceinline__ void warp_insert_id(float& lk, IdT& li, float s, IdT id, int lane) {
+    const bool stays = before_id<IdT>(lk, li, s, id);
+    const int pos = __popc(__ballot_sync(FULL, stays));
+    const float upk = __shfl_up_sync(FULL, lk, 1);
+    const IdT upi = shfl_up_id<IdT>(li);
+    if (lane == pos) {
+        lk = s;
+        li = id;
+    } else if (lane > pos) {
+        lk = upk;
+        li = upi;
+    }
+}
+
+// Input list p of query q lives at in_key/in_id + (q*q_stride + p*p_stride) (k entries).
+// key = key_sign * in_key.  Output: dist = out_sign * key + qnorm[q] (clamped at 0 when
+// clamp), label = id + label_base; empty slots give (pad, -1).
+template <typename IdT>
+struct MergeSmallParams {
+    const float* in_key;
+    const IdT* in_id;
+    int64_t q_stride, p_stride;
+    int P;
+    int64_t nq;
+    int k;
+    float key_sign;
+    float out_sign;
+    const float* qnorm;
+    int clamp;
+    float pad;
+    int64_t label_base;
+    float* out_dist;
+    int64_t* out_labels;
+};
+
+template <typename IdT>
+__global__ void __launch_bounds__(MS_THREADS) merge_small_kernel(const MergeSmallParams<IdT> p) {
+    __shared__ float sk[MS_WARPS][32];
+    __shared__ IdT si[MS_WARPS][32];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    for (int64_t q = blockIdx.x; q < p.nq; q += gridDim.x) {
+        float lk = CUDART_INF_F;
+        IdT li = (IdT)-1;
+        float thr = CUDART_INF_F;
+        IdT thr_id = (IdT)-1;
+        for (int l = warp; l < p.P; l += MS_WARPS) {
+            const float* lkey = p.in_key + q * p.q_stride + (int64_t)l * p.p_stride;
+            const IdT* lid = p.in_id + q * p.q_stride + (int64_t)l * p.p_stride;
+            // lane j prefetches entry j, entries are then consumed in order
+            float myk = CUDART_INF_F;
+            IdT myi = (IdT)-1;
+            if (lane < p.k) {
+                myk = p.key_sign * lkey[lane];
+                myi = lid[lane];
+            }
+            for (int j = 0; j < p.k; j++) {
+                const float s = __shfl_sync(FULL, myk, j);
+                const IdT id = shfl_id<IdT>(myi, j);
+                if (id < 0 || !before_id<IdT>(s, id, thr, thr_id)) break;
+                warp_insert_id<IdT>(lk, li, s, id, lane);
+                thr = __shfl_sync(FULL, lk, p.k - 1);
+                thr_id = shfl_id<IdT>(li, p.k - 1);
+            }
+        }
+        __syncthreads();  // previous query's shared lists fully consumed
+        sk[warp][lane] = lk;
+        si[warp][lane] = li;
+        __syncthreads();
+        if (warp == 0) {
+            for (int w = 1; w < MS_WARPS; w++) {
+                for (int j = 0; j < p.k; j++) {
+                    const float s = sk[w][j];
+                    const IdT id = si[w][j];
+                    if (id < 0 || !before_id<IdT>(s, id, thr, thr_id)) break;
+                    warp_insert_id<IdT>(lk, li, s, id, lane);
+                    thr = __shfl_sync(FULL, lk, p.k - 1);
+                    thr_id = shfl_id<IdT>(li, p.k - 1);
+                }
+            }
+            if (lane < p.k) {
+                float dist = p.pad;
+                int64_t label = -1;
+                if (li >= 0) {
+                    dist = p.out_sign * lk + (p.qnorm ? p.qnorm[q] : 0.f);
+                    if (p.clamp && dist < 0.f) dist = 0.f;
+                    label = (int64_t)li + p.label_base;
+                }
+                p.out_dist[q * p.k + lane] = dist;
+                p.out_labels[q * p.k + lane] = label;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// sort_select
+// ---------------------------------------------------------------------------------------
+constexpr int SS_THREADS = 1024;
+constexpr int SS_CAP = 8192;
+constexpr int SS_ITEMS = 4;
+constexpr int SS_BATCH = SS_THREADS * SS_ITEMS;  // 4096 candidates per batch
+constexpr uint64_t SS_EMPTY = ~0ull;
+
+enum { SRC_MATRIX = 0, SRC_LISTS = 1 };
+
+struct SortSelectParams {
+    // SRC_MATRIX: keys[q*ld + c], c in [0, ncand); payload = col0 + c
+    // SRC_LISTS : keys[(l*nq + q)*k + j] over l in [0, P); payload = l*k + j; labels != -1 live
+    const float* keys;
+    const int64_t* labels;
+    int64_t ld;
+    int64_t ncand;
+    int64_t col0;
+    int P;
+    int64_t nq;
+    int k;
+    float key_sign;       // key = key_sign * input
+    int has_prev;
+    float* run_key;       // [nq][k] in/out running lists (may be null when finalising directly)
+    int32_t* run_idx;
+    // finalisation (out_dist != null): dist = out_sign*key + qnorm[q]
+    float out_sign;
+    const float* qnorm;
+    int clamp;
+    float pad;
+    int64_t label_base;
+    float* out_dist;
+    int64_t* out_labels;
+};
+
+__device__ __forceinline__ uint64_t pack(float key, uint32_t payload) {
+    return ((uint64_t)float_to_ordered(key) << 32) | payload;
+}
+
+// ascending bitonic sort of buf[0..n), n a power of two, all threads of the CTA
+__device__ void bitonic_sort(uint64_t* buf, int n) {
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < (n >> 1); i += blockDim.x) {
+                const int pos = 2 * i - (i & (stride - 1));
+                const uint64_t a = buf[pos];
+                const uint64_t b = buf[pos + stride];
+                const bool up = (pos & size) == 0;
+                if ((a > b) == up) {
+                    buf[pos] = b;
+                    buf[pos + stride] = a;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+template <int SRC>
+__global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelectParams p) {
+    extern __shared__ __align__(16) uint64_t buf[];  // SS_CAP entries
+    __shared__ int s_count;
+    __shared__ uint64_t s_thr;
+    const int tid = threadIdx.x;
+
+    for (int64_t q = blockIdx.x; q < p.nq; q += gridDim.x) {
+        __syncthreads();
+        for (int i = tid; i < SS_CAP; i += SS_THREADS) buf[i] = SS_EMPTY;
+        if (tid == 0) {
+            s_count = 0;
+            s_thr = SS_EMPTY;
+        }
+        __syncthreads();
+        if (p.has_prev) {
+            for (int j = tid; j < p.k; j += SS_THREADS) {
+                const int32_t id = p.run_idx[q * p.k + j];
+                if (id >= 0) buf[j] = pack(p.run_key[q * p.k + j], (uint32_t)id);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                // live entries form a prefix of the sorted previous list
+                int c = 0;
+                // binary search for the first empty slot
+                int lo = 0, hi = p.k;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (buf[mid] != SS_EMPTY) lo = mid + 1; else hi = mid;
+                }
+                c = lo;
+                s_count = c;
+                s_thr = (c >= p.k) ? buf[p.k - 1] : SS_EMPTY;
+            }
+            __syncthreads();
+        }
+
+        const int64_t total = (SRC == SRC_MATRIX) ? p.ncand : (int64_t)p.P * p.k;
+        for (int64_t b0 = 0; b0 < total; b0 += SS_BATCH) {
+            // make room: after compaction at most k <= 4096 entries remain
+            if (s_count > SS_CAP - SS_BATCH) {
+                bitonic_sort(buf, SS_CAP);
+                for (int i = p.k + tid; i < SS_CAP; i += SS_THREADS) buf[i] = SS_EMPTY;
+                if (tid == 0) {
+                    s_count = p.k;
+                    s_thr = buf[p.k - 1];
+                }
+                __syncthreads();
+            }
+            const uint64_t thr = s_thr;
+#pragma unroll
+            for (int it = 0; it < SS_ITEMS; it++) {
+                const int64_t c = b0 + (int64_t)it * SS_THREADS + tid;
+                if (c < total) {
+                    float key;
+                    uint32_t payload;
+                    bool live = true;
+                    if (SRC == SRC_MATRIX) {
+                        key = p.key_sign * __ldg(p.keys + q * p.ld + c);
+                        payload = (uint32_t)(p.col0 + c);
+                    } else {
+                        const int64_t l = c / p.k;
+                        const int64_t j = c - l * p.k;
+                        const int64_t off = (l * p.nq + q) * p.k + j;
+                        key = p.key_sign * __ldg(p.keys + off);
+                        live = __ldg(p.labels + off) >= 0;
+                        payload = (uint32_t)c;
+                    }
+                    const uint64_t w = pack(key, payload);
+                    if (live && w < thr) {
+                        const int pos = atomicAdd(&s_count, 1);
+                        buf[pos] = w;  // pos < SS_CAP by construction
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        // final ordering
+        {
+            const int cnt = s_count;
+            int n = 64;
+            while (n < cnt) n <<= 1;
+            bitonic_sort(buf, n);
+        }
+        for (int j = tid; j < p.k; j += SS_THREADS) {
+            const uint64_t w = buf[j];
+            const bool live = (w != SS_EMPTY) && j < s_count;
+            const float key = ordered_to_float((uint32_t)(w >> 32));
+            const uint32_t payload = (uint32_t)w;
+            if (p.out_dist) {
+                float dist = p.pad;
+                int64_t label = -1;
+                if (live) {
+                    dist = p.out_sign * key + (p.qnorm ? p.qnorm[q] : 0.f);
+                    if (p.clamp && dist < 0.f) dist = 0.f;
+                    if (SRC == SRC_MATRIX) {
+                        label = (int64_t)payload + p.label_base;
+                    } else {
+                        const int64_t l = payload / p.k;
+                        const int64_t jj = payload - l * p.k;
+                        label = p.labels[(l * p.nq + q) * p.k + jj];
+                    }
+                }
+                p.out_dist[q * p.k + j] = dist;
+                p.out_labels[q * p.k + j] = label;
+            } else {
+                p.run_key[q * p.k + j] = live ? key : CUDART_INF_F;
+                p.run_idx[q * p.k + j] = live ? (int32_t)payload : -1;
+            }
+        }
+    }
+}
+
+template <int SRC>
+int launch_sort_select(const SortSelectParams& p, cudaStream_t stream) {
+    if (p.nq <= 0) return B200F_OK;
+    if (p.k < 1 || p.k > B200F_MAX_K) return B200F_ERR_UNSUPPORTED;
+    const int smem = SS_CAP * 8;
+    static bool attr_set = false;
+    if (!attr_set) {
+        B200F_CUDA_TRY(cudaFuncSetAttribute(sort_select_kernel<SRC>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set = true;
+    }
+    int64_t g = p.nq;
+    const int64_t cap = (int64_t)cached_sm_count() * 2 * 8;
+    if (g > cap) g = cap;
+    sort_select_kernel<SRC><<<(int)g, SS_THREADS, smem, stream>>>(p);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+__global__ void finalize_lists_kernel(const float* __restrict__ run_key,
+                                      const int32_t* __restrict__ run_idx, int64_t nq, int k,
+                                      float out_sign, const float* __restrict__ qnorm, int clamp,
+                                      float pad, int64_t label_base, float* __restrict__ out_dist,
+                                      int64_t* __restrict__ out_labels) {
+    const int64_t total = nq * k;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t q = i / k;
+        const int32_t id = run_idx[i];
+        float dist = pad;
+        int64_t label = -1;
+        if (id >= 0) {
+            dist = out_sign * run_key[i] + (qnorm ? qnorm[q] : 0.f);
+            if (clamp && dist < 0.f) dist = 0.f;
+            label = (int64_t)id + label_base;
+        }
+        out_dist[i] = dist;
+        out_labels[i] = label;
+    }
+}
+
+}  // namespace
+
+int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
+                          int metric, const float* qnorm, int64_t label_base, float* out_dist,
+                          int64_t* out_labels, cudaStream_t stream) {
+    if (nq <= 0) return B200F_OK;
+    if (k < 1 || k > 32 || P < 1) return B200F_ERR_UNSUPPORTED;
+    MergeSmallParams<int32_t> p{};
+    p.in_key = part_key;
+    p.in_id = part_idx;
+    p.q_stride = (int64_t)P * k;
+    p.p_stride = k;
+    p.P = P;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = 1.f;
+    const bool l2 = metric == B200F_METRIC_L2;
+    p.out_sign = l2 ? 1.f : -1.f;
+    p.qnorm = l2 ? qnorm : nullptr;
+    p.clamp = l2 ? 1 : 0;
+    p.pad = l2 ? kHostInf : -kHostInf;
+    p.label_base = label_base;
+    p.out_dist = out_dist;
+    p.out_labels = out_labels;
+    int64_t g = nq;
+    const int64_t cap = (int64_t)cached_sm_count() * 32;
+    if (g > cap) g = cap;
+    merge_small_kernel<int32_t><<<(int)g, MS_THREADS, 0, stream>>>(p);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int64_t col0,
+                        int k, int has_prev, float* run_key, int32_t* run_idx, int32_t* status,
+                        cudaStream_t stream) {
+    (void)status;
+    SortSelectParams p{};
+    p.keys = keys;
+    p.ld = ld;
+    p.ncand = ncols;
+    p.col0 = col0;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = 1.f;
+    p.has_prev = has_prev;
+    p.run_key = run_key;
+    p.run_idx = run_idx;
+    p.out_dist = nullptr;
+    return launch_sort_select<SRC_MATRIX>(p, stream);
+}
+
+int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t nq, int k,
+                          int metric, const float* qnorm, int64_t label_base, float* out_dist,
+                          int64_t* out_labels, cudaStream_t stream) {
+    if (nq <= 0) return B200F_OK;
+    const bool l2 = metric == B200F_METRIC_L2;
+    int64_t g = ceil_div64(nq * k, 256);
+    const int64_t cap = (int64_t)cached_sm_count() * 16;
+    if (g > cap) g = cap;
+    finalize_lists_kernel<<<(int)g, 256, 0, stream>>>(run_key, run_idx, nq, k, l2 ? 1.f : -1.f,
+                                                      l2 ? qnorm : nullptr, l2 ? 1 : 0,
+                                                      l2 ? kHostInf : -kHostInf, label_base,
+                                                      out_dist, out_labels);
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+}  // namespace b200f
+
+using namespace b200f;
+
+extern "C" size_t b200f_select_scratch_bytes(int64_t nq, int k) {
+    (void)nq;
+    (void)k;
+    return 256;  // the selection kernel keeps all of its state in shared memory
+}
+
+extern "C" int b200f_select_rows(const float* scores, int64_t nq, int64_t ncols, int64_t ld,
+                                 int metric, int k, float* out_dist, int64_t* out_labels,
+                                 void* scratch, size_t scratch_bytes, void* stream) {
+    (void)scratch;
+    (void)scratch_bytes;
+    if (nq < 0 || ncols < 0 || ld < ncols || k <= 0 ||
+        (metric != B200F_METRIC_L2 && metric != B200F_METRIC_INNER_PRODUCT))
+        return B200F_ERR_BAD_ARG;
+    if (k > B200F_MAX_K || ncols > 0x7fffffffLL) return B200F_ERR_UNSUPPORTED;
+    if (nq == 0) return B200F_OK;
+    if (!scores || !out_dist || !out_labels) return B200F_ERR_BAD_ARG;
+    const bool l2 = metric == B200F_METRIC_L2;
+    SortSelectParams p{};
+    p.keys = scores;
+    p.ld = ld;
+    p.ncand = ncols;
+    p.col0 = 0;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = l2 ? 1.f : -1.f;
+    p.has_prev = 0;
+    p.out_sign = l2 ? 1.f : -1.f;
+    p.qnorm = nullptr;
+    p.clamp = 0;
+    p.pad = l2 ? kHostInf : -kHostInf;
+    p.label_base = 0;
+    p.out_dist = out_dist;
+    p.out_labels = out_labels;
+    return launch_sort_select<SRC_MATRIX>(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P, int64_t nq, int k,
+                                 int metric, float* out_dist, int64_t* out_labels, void* stream) {
+    if (P <= 0 || nq < 0 || k <= 0 ||
+        (metric != B200F_METRIC_L2 && metric != B200F_METRIC_INNER_PRODUCT))
+        return B200F_ERR_BAD_ARG;
+    if (k > B200F_MAX_K || (int64_t)P * k > 0x7fffffffLL) return B200F_ERR_UNSUPPORTED;
+    if (nq == 0) return B200F_OK;
+    if (!dist || !labels || !out_dist || !out_labels) return B200F_ERR_BAD_ARG;
+    const bool l2 = metric == B200F_METRIC_L2;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (k <= 32) {
+        MergeSmallParams<int64_t> p{};
+        p.in_key = dist;
+        p.in_id = labels;
+        p.q_stride = k;
+        p.p_stride = nq * (int64_t)k;
+        p.P = P;
+        p.nq = nq;
+        p.k = k;
+        p.key_sign = l2 ? 1.f : -1.f;
+        p.out_sign = l2 ? 1.f : -1.f;
+        p.qnorm = nullptr;
+        p.clamp = 0;
+        p.pad = l2 ? kHostInf : -kHostInf;
+        p.label_base = 0;
+        p.out_dist = out_dist;
+        p.out_labels = out_labels;
+        int64_t g = nq;
+        const int64_t cap = (int64_t)cached_sm_count() * 32;
+        if (g > cap) g = cap;
+        merge_small_kernel<int64_t><<<(int)g, MS_THREADS, 0, st>>>(p);
+        B200F_LAUNCH_CHECK();
+        return B200F_OK;
+    }
+    SortSelectParams p{};
+    p.keys = dist;
+    p.labels = labels;
+    p.P = P;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = l2 ? 1.f : -1.f;
+    p.has_prev = 0;
+    p.out_sign = l2 ? 1.f : -1.f;
+    p.qnorm = nullptr;
+    p.clamp = 0;
+    p.pad = l2 ? kHostInf : -kHostInf;
+    p.out_dist = out_dist;
+    p.out_labels = out_labels;
+    return launch_sort_select<SRC_LISTS>(p, st);
+}

@@ -1,0 +1,36 @@
+// Minimal stand-in for <faiss/Index.h> (see MetricType.h in this directory).
+// Only the members the flat GPU index and its tests touch are declared:
+// d, ntotal, metric_type, is_trained, verbose and the virtuals add / search /
+// reset / reconstruct (src/MetalIndexFlat.mm:167-171,185,313,492,508).
+#pragma once
+#include <cstddef>
+
+#include "MetricType.h"
+
+namespace faiss {
+
+struct SearchParameters {
+    virtual ~SearchParameters() {}
+};
+
+struct Index {
+    int d;
+    idx_t ntotal;
+    bool verbose;
+    bool is_trained;
+    MetricType metric_type;
+    float metric_arg;
+
+    explicit Index(idx_t d_ = 0, MetricType metric = METRIC_L2)
+            : d((int)d_), ntotal(0), verbose(false), is_trained(true), metric_type(metric), metric_arg(0) {}
+    virtual ~Index() {}
+
+    virtual void train(idx_t /*n*/, const float* /*x*/) {}
+    virtual void add(idx_t n, const float* x) = 0;
+    virtual void search(idx_t n, const float* x, idx_t k, float* distances, idx_t* labels,
+                        const SearchParameters* params = nullptr) const = 0;
+    virtual void reset() = 0;
+    virtual void reconstruct(idx_t key, float* recons) const;
+};
+
+}  // namespace faiss

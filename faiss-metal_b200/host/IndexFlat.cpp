@@ -1,0 +1,644 @@
+// B200IndexFlat: storage growth, conversion on add, search orchestration, async
+// tokens, reconstruct and the cpu<->gpu converters.
+// Counterpart of src/MetalIndexFlat.mm (add :185-311, search :313-401,
+// searchAsync :403-490, token :17-78, reset :492-506, reconstruct :508-527,
+// converters :552-587).  All device work goes through the C-ABI in
+// include/b200_flat.h; nothing here computes distances on the host.
+#include <cuda_runtime.h>
+#include <faiss/impl/FaissAssert.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/b200_flat.h"
+#include "../include/faiss-b200/B200IndexFlat.h"
+#include "../include/faiss-b200/B200Resources.h"
+
+namespace faiss_b200 {
+
+namespace {
+
+constexpr size_t kStageBytes = 64ull << 20;   // fp32 staging chunk for add / reconstruct_n
+constexpr int64_t kFusedBatch = 16384;        // queries per launch, k <= 32
+constexpr int64_t kSelectBatch = 8192;        // queries per launch, k  > 32
+
+void cudaCheck(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) {
+        std::string msg = std::string("faiss-b200: ") + what + ": " + cudaGetErrorString(e);
+        (void)cudaGetLastError();
+        throw std::runtime_error(msg);
+    }
+}
+
+void abiCheck(int rc, const char* what) {
+    if (rc == B200F_OK) return;
+    std::string msg = std::string("faiss-b200: ") + what + ": " + b200f_status_string(rc);
+    if (rc == B200F_ERR_BAD_ARG || rc == B200F_ERR_UNSUPPORTED) throw faiss::FaissException(msg);
+    throw std::runtime_error(msg);
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) cudaCheck(cudaSetDevice(dev), "cudaSetDevice");
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) (void)cudaSetDevice(prev);
+    }
+};
+
+bool isDevicePointer(const void* p) {
+    if (!p) return false;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+int64_t roundUp(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+size_t elemBytes(StorageType s) { return s == StorageType::Float32 ? 4 : 2; }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+struct B200IndexFlat::Impl {
+    std::shared_ptr<B200Resources> res;
+    StorageType storage = StorageType::Float32;
+    int d = 0;
+    bool l2 = true;
+    int64_t pitch = 0;       // elements per stored row
+    int64_t planePitch = 0;  // fp32 storage: elements per bf16 split-plane row
+    void* rows = nullptr;
+    uint16_t* planes = nullptr;
+    float* norms = nullptr;
+    int64_t capacity = 0;
+    int32_t* status = nullptr;    // device int32[4]
+    float* oneRow = nullptr;      // device fp32[d] for reconstruct
+    int32_t* hostStatus = nullptr;  // pinned int32[4]
+    int forcePath = B200F_PATH_AUTO;
+    int64_t labelBase = 0;
+    mutable std::vector<float> mirror;
+    mutable bool mirrorValid = false;
+    mutable int lastStatus = 0;
+
+    cudaStream_t stream() const { return reinterpret_cast<cudaStream_t>(res->getDefaultStream()); }
+    int storageCode() const { return (int)storage; }
+
+    void freeStorage() {
+        if (rows) res->deallocBuffer(rows);
+        if (planes) res->deallocBuffer(planes);
+        if (norms) res->deallocBuffer(norms);
+        rows = nullptr;
+        planes = nullptr;
+        norms = nullptr;
+        capacity = 0;
+    }
+
+    // Grow to hold at least `want` rows; keeps the first `keep` rows.
+    void grow(int64_t want, int64_t keep) {
+        if (want <= capacity) return;
+        const size_t es = elemBytes(storage);
+        void* newRows = res->allocBuffer((size_t)want * pitch * es);
+        uint16_t* newPlanes = nullptr;
+        float* newNorms = nullptr;
+        try {
+            if (storage == StorageType::Float32)
+                newPlanes = static_cast<uint16_t*>(res->allocBuffer((size_t)3 * want * planePitch * 2));
+            if (l2) newNorms = static_cast<float*>(res->allocBuffer((size_t)want * 4));
+        } catch (...) {
+            res->deallocBuffer(newRows);
+            if (newPlanes) res->deallocBuffer(newPlanes);
+            throw;
+        }
+        cudaStream_t st = stream();
+        if (keep > 0) {
+            cudaCheck(cudaMemcpyAsync(newRows, rows, (size_t)keep * pitch * es, cudaMemcpyDeviceToDevice, st),
+                      "copy rows");
+            if (newPlanes)
+                for (int p = 0; p < 3; p++)
+                    cudaCheck(cudaMemcpyAsync(newPlanes + (size_t)p * want * planePitch,
+                                              planes + (size_t)p * capacity * planePitch,
+                                              (size_t)keep * planePitch * 2, cudaMemcpyDeviceToDevice, st),
+                              "copy planes");
+            if (newNorms)
+                cudaCheck(cudaMemcpyAsync(newNorms, norms, (size_t)keep * 4, cudaMemcpyDeviceToDevice, st),
+                          "copy norms");
+            cudaCheck(cudaStreamSynchronize(st), "grow sync");
+        }
+        freeStorage();
+        rows = newRows;
+        planes = newPlanes;
+        norms = newNorms;
+        capacity = want;
+    }
+
+    void fillArgs(B200FSearchArgs& a, int64_t ntotal) const {
+        std::memset(&a, 0, sizeof(a));
+        a.d = d;
+        a.storage = storageCode();
+        a.rows = rows;
+        a.row_pitch = pitch;
+        a.planes = planes;
+        a.plane_pitch = planePitch;
+        a.plane_stride = capacity * planePitch;
+        a.norms = norms;
+        a.nb = ntotal;
+        a.metric = l2 ? B200F_METRIC_L2 : B200F_METRIC_INNER_PRODUCT;
+        a.label_base = labelBase;
+        a.status = status;
+        a.stream = stream();
+        a.path = forcePath;
+    }
+};
+
+// layout of one search call inside a device region
+namespace {
+struct CallLayout {
+    size_t offQueries, offDist, offLabels, offScratch, scratchBytes, total;
+};
+CallLayout makeLayout(int64_t nOut, int64_t nBatch, int d, int64_t k, bool stageQueries, int64_t nQueriesStaged,
+                      bool stageOutputs, size_t scratchBytes) {
+    CallLayout L{};
+    size_t off = 0;
+    L.offQueries = off;
+    if (stageQueries) off += align256((size_t)nQueriesStaged * d * 4);
+    L.offDist = off;
+    if (stageOutputs) off += align256((size_t)nOut * k * 4);
+    L.offLabels = off;
+    if (stageOutputs) off += align256((size_t)nOut * k * 8);
+    L.offScratch = off;
+    L.scratchBytes = scratchBytes;
+    off += align256(scratchBytes);
+    L.total = off;
+    (void)nBatch;
+    return L;
+}
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+B200IndexFlat::B200IndexFlat(std::shared_ptr<B200Resources> resources, int d_,
+                             faiss::MetricType metric, bool useFloat16Storage)
+        : B200IndexFlat(std::move(resources), d_, metric,
+                        useFloat16Storage ? StorageType::Float16 : StorageType::Float32) {}
+
+B200IndexFlat::B200IndexFlat(std::shared_ptr<B200Resources> resources, int d_,
+                             faiss::MetricType metric, StorageType storage)
+        : faiss::Index(d_, metric), impl_(new Impl) {
+    FAISS_THROW_IF_NOT_MSG(resources != nullptr, "resources must not be null");
+    FAISS_THROW_IF_NOT_MSG(d_ > 0, "d must be > 0");
+    FAISS_THROW_IF_NOT_MSG(metric == faiss::METRIC_L2 || metric == faiss::METRIC_INNER_PRODUCT,
+                           "only METRIC_L2 and METRIC_INNER_PRODUCT are supported");
+    FAISS_THROW_IF_NOT_MSG((int)storage >= 0 && (int)storage <= 2, "invalid storage type");
+    impl_->res = std::move(resources);
+    impl_->storage = storage;
+    impl_->d = d_;
+    impl_->l2 = metric == faiss::METRIC_L2;
+    impl_->pitch = storage == StorageType::Float32 ? roundUp(d_, 4) : roundUp(d_, 8);
+    impl_->planePitch = roundUp(d_, 8);
+    DeviceGuard g(impl_->res->getDevice());
+    impl_->status = static_cast<int32_t*>(impl_->res->allocBuffer(256));
+    impl_->oneRow = static_cast<float*>(impl_->res->allocBuffer((size_t)d_ * 4));
+    impl_->hostStatus = static_cast<int32_t*>(alloc_pinned(16));
+    if (!impl_->hostStatus) throw std::runtime_error("faiss-b200: pinned allocation failed");
+    cudaCheck(cudaMemsetAsync(impl_->status, 0, 256, impl_->stream()), "memset status");
+    is_trained = true;
+    ntotal = 0;
+}
+
+B200IndexFlat::~B200IndexFlat() {
+    if (!impl_) return;
+    try {
+        DeviceGuard g(impl_->res->getDevice());
+        (void)cudaStreamSynchronize(impl_->stream());
+        impl_->freeStorage();
+        impl_->res->deallocBuffer(impl_->status);
+        impl_->res->deallocBuffer(impl_->oneRow);
+        free_pinned(impl_->hostStatus);
+    } catch (...) {
+    }
+}
+
+void B200IndexFlat::reserve(faiss::idx_t n) {
+    DeviceGuard g(impl_->res->getDevice());
+    if (n > impl_->capacity) impl_->grow(n, ntotal);
+}
+
+void B200IndexFlat::add(faiss::idx_t n, const float* x) {
+    if (n == 0) return;  // src/MetalIndexFlat.mm:186
+    FAISS_THROW_IF_NOT_MSG(n > 0 && x != nullptr, "add: invalid arguments");
+    const int64_t newTotal = ntotal + n;
+    FAISS_THROW_IF_NOT_MSG(newTotal <= B200DeviceCapabilities::kMaxVectorsPerShard,
+                           "B200IndexFlat holds at most 2^31-1 vectors per shard (int32 row numbers)");
+    DeviceGuard g(impl_->res->getDevice());
+    if (newTotal > impl_->capacity) {
+        // growth rule of the reference: max(newTotal, 2 * capacity, 1024)
+        // (src/MetalIndexFlat.mm:196-197,272-273)
+        int64_t newCap = std::max<int64_t>(newTotal, impl_->capacity * 2);
+        newCap = std::max<int64_t>(newCap, 1024);
+        impl_->grow(newCap, ntotal);
+    }
+    cudaStream_t st = impl_->stream();
+    const size_t es = elemBytes(impl_->storage);
+    const bool onDevice = isDevicePointer(x);
+    const int64_t rowsPerChunk = std::max<int64_t>(1, (int64_t)(kStageBytes / ((size_t)d * 4)));
+    float* stage = nullptr;
+    if (!onDevice)
+        stage = static_cast<float*>(impl_->res->getScratch((size_t)std::min<int64_t>(rowsPerChunk, n) * d * 4));
+    for (int64_t r0 = 0; r0 < n; r0 += rowsPerChunk) {
+        const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
+        const float* src = x + (size_t)r0 * d;
+        if (!onDevice) {
+            cudaCheck(cudaMemcpyAsync(stage, src, (size_t)nr * d * 4, cudaMemcpyHostToDevice, st),
+                      "add: host to device copy");
+            src = stage;
+        }
+        const int64_t row = ntotal + r0;
+        abiCheck(b200f_store_rows(
+                         src, nr, d, impl_->storageCode(),
+                         static_cast<uint8_t*>(impl_->rows) + (size_t)row * impl_->pitch * es, impl_->pitch,
+                         impl_->planes ? impl_->planes + (size_t)row * impl_->planePitch : nullptr,
+                         impl_->planePitch, impl_->capacity * impl_->planePitch,
+                         impl_->norms ? impl_->norms + row : nullptr, st),
+                 "add: store rows");
+    }
+    // the caller may free x as soon as add returns
+    cudaCheck(cudaStreamSynchronize(st), "add: synchronize");
+    ntotal = newTotal;
+    impl_->mirrorValid = false;
+}
+
+void B200IndexFlat::reset() {
+    DeviceGuard g(impl_->res->getDevice());
+    cudaCheck(cudaStreamSynchronize(impl_->stream()), "reset: synchronize");
+    impl_->freeStorage();
+    impl_->mirror.clear();
+    impl_->mirror.shrink_to_fit();
+    impl_->mirrorValid = false;
+    ntotal = 0;
+}
+
+void B200IndexFlat::reconstruct_n(faiss::idx_t first, faiss::idx_t n, float* out) const {
+    FAISS_THROW_IF_NOT_FMT(first >= 0 && n >= 0 && first + n <= ntotal,
+                           "reconstruct_n: range [%lld, %lld) outside [0, %lld)", (long long)first,
+                           (long long)(first + n), (long long)ntotal);
+    if (n == 0) return;
+    FAISS_THROW_IF_NOT_MSG(out != nullptr, "reconstruct_n: null output");
+    DeviceGuard g(impl_->res->getDevice());
+    cudaStream_t st = impl_->stream();
+    const size_t es = elemBytes(impl_->storage);
+    const bool outOnDevice = isDevicePointer(out);
+    const int64_t rowsPerChunk = std::max<int64_t>(1, (int64_t)(kStageBytes / ((size_t)d * 4)));
+    float* stage = nullptr;
+    if (!outOnDevice)
+        stage = static_cast<float*>(impl_->res->getScratch((size_t)std::min<int64_t>(rowsPerChunk, n) * d * 4));
+    for (int64_t r0 = 0; r0 < n; r0 += rowsPerChunk) {
+        const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
+        float* dst = outOnDevice ? out + (size_t)r0 * d : stage;
+        abiCheck(b200f_load_rows(static_cast<const uint8_t*>(impl_->rows) + (size_t)(first + r0) * impl_->pitch * es,
+                                 impl_->storageCode(), nr, d, impl_->pitch, dst, st),
+                 "reconstruct_n: load rows");
+        if (!outOnDevice) {
+            cudaCheck(cudaMemcpyAsync(out + (size_t)r0 * d, stage, (size_t)nr * d * 4,
+                                      cudaMemcpyDeviceToHost, st),
+                      "reconstruct_n: device to host copy");
+            cudaCheck(cudaStreamSynchronize(st), "reconstruct_n: synchronize");
+        }
+    }
+    cudaCheck(cudaStreamSynchronize(st), "reconstruct_n: synchronize");
+}
+
+void B200IndexFlat::reconstruct(faiss::idx_t key, float* recons) const {
+    // range check of the reference: src/MetalIndexFlat.mm:509-511
+    FAISS_THROW_IF_NOT_FMT(key >= 0 && key < ntotal, "reconstruct: key %lld out of range [0, %lld)",
+                           (long long)key, (long long)ntotal);
+    FAISS_THROW_IF_NOT_MSG(recons != nullptr, "reconstruct: null output");
+    DeviceGuard g(impl_->res->getDevice());
+    cudaStream_t st = impl_->stream();
+    const size_t es = elemBytes(impl_->storage);
+    abiCheck(b200f_load_rows(static_cast<const uint8_t*>(impl_->rows) + (size_t)key * impl_->pitch * es,
+                             impl_->storageCode(), 1, d, impl_->pitch, impl_->oneRow, st),
+             "reconstruct: load row");
+    cudaCheck(cudaMemcpyAsync(recons, impl_->oneRow, (size_t)d * 4,
+                              isDevicePointer(recons) ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st),
+              "reconstruct: copy");
+    cudaCheck(cudaStreamSynchronize(st), "reconstruct: synchronize");
+}
+
+const float* B200IndexFlat::getVectorsData() const {
+    if (impl_->storage != StorageType::Float32) return nullptr;  // include/faiss-metal/MetalIndexFlat.h:92-94
+    if (ntotal == 0) return nullptr;
+    if (!impl_->mirrorValid) {
+        impl_->mirror.resize((size_t)ntotal * d);
+        reconstruct_n(0, ntotal, impl_->mirror.data());
+        impl_->mirrorValid = true;
+    }
+    return impl_->mirror.data();
+}
+
+bool B200IndexFlat::isFloat16Storage() const { return impl_->storage == StorageType::Float16; }
+bool B200IndexFlat::isBFloat16Storage() const { return impl_->storage == StorageType::BFloat16; }
+StorageType B200IndexFlat::getStorageType() const { return impl_->storage; }
+void B200IndexFlat::setForcePath(int path) {
+    FAISS_THROW_IF_NOT_MSG(path >= B200F_PATH_AUTO && path <= B200F_PATH_TENSOR, "invalid path");
+    impl_->forcePath = path;
+}
+void B200IndexFlat::setLabelBase(faiss::idx_t base) { impl_->labelBase = base; }
+const void* B200IndexFlat::getDeviceRows() const { return impl_->rows; }
+int B200IndexFlat::lastDeviceStatus() const { return impl_->lastStatus; }
+
+// ---------------------------------------------------------------------------------------
+// search
+// ---------------------------------------------------------------------------------------
+namespace {
+
+void checkSearchArgs(faiss::idx_t n, const float* x, faiss::idx_t k, const float* distances,
+                     const faiss::idx_t* labels, faiss::idx_t ntotal) {
+    FAISS_THROW_IF_NOT_MSG(k > 0, "k must be > 0");  // src/MetalIndexFlat.mm:321
+    FAISS_THROW_IF_NOT_FMT(k <= B200F_MAX_K, "k = %lld exceeds the maximum of %d", (long long)k,
+                           B200F_MAX_K);             // src/MetalSelect.mm:65-70
+    FAISS_THROW_IF_NOT_MSG(ntotal <= B200DeviceCapabilities::kMaxVectorsPerShard,
+                           "B200IndexFlat supports at most 2^31-1 vectors per shard (int32 row numbers)");
+    FAISS_THROW_IF_NOT_MSG(n >= 0, "n must be >= 0");
+    if (n > 0) FAISS_THROW_IF_NOT_MSG(x && distances && labels, "search: null pointer");
+}
+
+}  // namespace
+
+void B200IndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k, float* distances,
+                           faiss::idx_t* labels, const faiss::SearchParameters* /*params*/) const {
+    checkSearchArgs(n, x, k, distances, labels, ntotal);
+    if (n == 0) return;
+    DeviceGuard g(impl_->res->getDevice());
+    cudaStream_t st = impl_->stream();
+    const bool qOnDevice = isDevicePointer(x);
+    const bool dOnDevice = isDevicePointer(distances);
+    const bool lOnDevice = isDevicePointer(labels);
+    const int64_t batch = std::min<int64_t>(n, k <= B200F_FUSED_MAX_K ? kFusedBatch : kSelectBatch);
+    const size_t scratchBytes =
+            b200f_search_scratch_bytes(batch, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
+    FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "search: cannot plan this shape");
+    CallLayout L = makeLayout(batch, batch, d, k, !qOnDevice, batch, true, scratchBytes);
+    uint8_t* region = static_cast<uint8_t*>(impl_->res->getScratch(L.total));
+    impl_->lastStatus = 0;
+
+    for (int64_t q0 = 0; q0 < n; q0 += batch) {
+        const int64_t nq = std::min<int64_t>(batch, n - q0);
+        const float* dq = x + (size_t)q0 * d;
+        if (!qOnDevice) {
+            cudaCheck(cudaMemcpyAsync(region + L.offQueries, dq, (size_t)nq * d * 4,
+                                      cudaMemcpyHostToDevice, st),
+                      "search: host to device copy of queries");
+            dq = reinterpret_cast<const float*>(region + L.offQueries);
+        }
+        float* dDist = dOnDevice ? distances + (size_t)q0 * k : reinterpret_cast<float*>(region + L.offDist);
+        int64_t* dLab = lOnDevice ? reinterpret_cast<int64_t*>(labels) + (size_t)q0 * k
+                                  : reinterpret_cast<int64_t*>(region + L.offLabels);
+        B200FSearchArgs a;
+        impl_->fillArgs(a, ntotal);
+        a.queries = dq;
+        a.nq = nq;
+        a.k = (int)k;
+        a.out_dist = dDist;
+        a.out_labels = dLab;
+        a.scratch = region + L.offScratch;
+        a.scratch_bytes = L.scratchBytes;
+        abiCheck(b200f_search(&a), "search");
+        if (!dOnDevice)
+            cudaCheck(cudaMemcpyAsync(distances + (size_t)q0 * k, dDist, (size_t)nq * k * 4,
+                                      cudaMemcpyDeviceToHost, st),
+                      "search: device to host copy of distances");
+        if (!lOnDevice)
+            cudaCheck(cudaMemcpyAsync(labels + (size_t)q0 * k, dLab, (size_t)nq * k * 8,
+                                      cudaMemcpyDeviceToHost, st),
+                      "search: device to host copy of labels");
+        cudaCheck(cudaMemcpyAsync(impl_->hostStatus, impl_->status, 16, cudaMemcpyDeviceToHost, st),
+                  "search: status copy");
+        cudaCheck(cudaStreamSynchronize(st), "search: synchronize");
+        if (impl_->hostStatus[0] != 0) {
+            impl_->lastStatus = impl_->hostStatus[0];
+            throw std::runtime_error("faiss-b200: search kernel reported device status " +
+                                     std::to_string(impl_->hostStatus[0]) + " (" +
+                                     b200f_status_string(B200F_ERR_DEVICE_WAIT) + ")");
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// async search
+// ---------------------------------------------------------------------------------------
+struct B200SearchToken::Impl {
+    std::shared_ptr<B200Resources> res;
+    void* region = nullptr;       // device: queries, outputs, scratch
+    int32_t* status = nullptr;    // device int32[4 * nbatches]
+    uint8_t* host = nullptr;      // pinned: staged queries, result staging, status
+    size_t hostDistOff = 0, hostLabOff = 0, hostStatusOff = 0;
+    int64_t n = 0, k = 0;
+    int nbatches = 0;
+    float* userDist = nullptr;
+    faiss::idx_t* userLabels = nullptr;
+    bool distOnDevice = false, labelsOnDevice = false;
+    cudaEvent_t done = nullptr;
+    bool waited = false;
+
+    void release() {
+        if (res) {
+            int prev = -1;
+            (void)cudaGetDevice(&prev);
+            (void)cudaSetDevice(res->getDevice());
+            if (done) (void)cudaEventDestroy(done);
+            if (region) res->deallocBuffer(region);
+            if (status) res->deallocBuffer(status);
+            if (prev >= 0) (void)cudaSetDevice(prev);
+        }
+        free_pinned(host);
+        done = nullptr;
+        region = nullptr;
+        status = nullptr;
+        host = nullptr;
+    }
+    ~Impl() { release(); }
+};
+
+B200SearchToken::B200SearchToken(std::unique_ptr<Impl> impl) : impl_(std::move(impl)) {}
+B200SearchToken::B200SearchToken(B200SearchToken&&) noexcept = default;
+B200SearchToken& B200SearchToken::operator=(B200SearchToken&& o) noexcept {
+    if (this != &o) {
+        if (impl_ && !impl_->waited) {
+            try { wait(); } catch (...) {}
+        }
+        impl_ = std::move(o.impl_);
+    }
+    return *this;
+}
+
+B200SearchToken::~B200SearchToken() {
+    // wait if the caller never did (src/MetalIndexFlat.mm:41-47)
+    if (impl_ && !impl_->waited) {
+        try { wait(); } catch (...) {}
+    }
+}
+
+void B200SearchToken::wait() {
+    FAISS_THROW_IF_NOT_MSG(impl_ != nullptr, "wait() on a moved-from search token");  // :50
+    if (impl_->waited) return;
+    impl_->waited = true;
+    if (impl_->done) {
+        DeviceGuard g(impl_->res->getDevice());
+        cudaCheck(cudaEventSynchronize(impl_->done), "token wait");
+        if (!impl_->distOnDevice)
+            std::memcpy(impl_->userDist, impl_->host + impl_->hostDistOff, (size_t)impl_->n * impl_->k * 4);
+        if (!impl_->labelsOnDevice)
+            std::memcpy(impl_->userLabels, impl_->host + impl_->hostLabOff, (size_t)impl_->n * impl_->k * 8);
+        const int32_t* hs = reinterpret_cast<const int32_t*>(impl_->host + impl_->hostStatusOff);
+        int bad = 0;
+        for (int b = 0; b < impl_->nbatches; b++) bad |= hs[4 * b];
+        impl_->release();
+        if (bad)
+            throw std::runtime_error("faiss-b200: async search reported device status " + std::to_string(bad));
+    }
+}
+
+bool B200SearchToken::isReady() const {
+    FAISS_THROW_IF_NOT_MSG(impl_ != nullptr, "isReady() on a moved-from search token");  // :75
+    if (impl_->waited || !impl_->done) return true;
+    cudaError_t e = cudaEventQuery(impl_->done);
+    if (e == cudaSuccess) return true;
+    if (e == cudaErrorNotReady) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    cudaCheck(e, "token isReady");
+    return false;
+}
+
+B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss::idx_t k,
+                                           float* distances, faiss::idx_t* labels,
+                                           const faiss::SearchParameters* /*params*/) const {
+    checkSearchArgs(n, x, k, distances, labels, ntotal);
+    std::unique_ptr<B200SearchToken::Impl> t(new B200SearchToken::Impl);
+    if (n == 0) {  // ready token, nothing to write (src/MetalIndexFlat.mm:423-433)
+        t->waited = true;
+        return B200SearchToken(std::move(t));
+    }
+    DeviceGuard g(impl_->res->getDevice());
+    cudaStream_t st = impl_->stream();
+    t->res = impl_->res;
+    t->n = n;
+    t->k = k;
+    t->userDist = distances;
+    t->userLabels = labels;
+    t->distOnDevice = isDevicePointer(distances);
+    t->labelsOnDevice = isDevicePointer(labels);
+    const bool qOnDevice = isDevicePointer(x);
+    const int64_t batch = std::min<int64_t>(n, k <= B200F_FUSED_MAX_K ? kFusedBatch : kSelectBatch);
+    t->nbatches = (int)((n + batch - 1) / batch);
+    const size_t scratchBytes =
+            b200f_search_scratch_bytes(batch, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
+    FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "searchAsync: cannot plan this shape");
+    // per-call buffers: the token owns them (src/MetalIndexFlat.mm:441-476)
+    CallLayout L = makeLayout(n, batch, d, k, !qOnDevice, n, true, scratchBytes);
+    t->region = impl_->res->allocBuffer(L.total);
+    t->status = static_cast<int32_t*>(impl_->res->allocBuffer(align256((size_t)t->nbatches * 16)));
+    size_t hoff = 0;
+    const size_t hostQOff = hoff;
+    if (!qOnDevice) hoff += align256((size_t)n * d * 4);
+    t->hostDistOff = hoff;
+    hoff += align256((size_t)n * k * 4);
+    t->hostLabOff = hoff;
+    hoff += align256((size_t)n * k * 8);
+    t->hostStatusOff = hoff;
+    hoff += align256((size_t)t->nbatches * 16);
+    t->host = static_cast<uint8_t*>(alloc_pinned(hoff));
+    if (!t->host) throw std::runtime_error("faiss-b200: pinned allocation failed");
+    uint8_t* region = static_cast<uint8_t*>(t->region);
+
+    const float* dqAll = x;
+    if (!qOnDevice) {
+        // the caller's array is only read during this call
+        std::memcpy(t->host + hostQOff, x, (size_t)n * d * 4);
+        cudaCheck(cudaMemcpyAsync(region + L.offQueries, t->host + hostQOff, (size_t)n * d * 4,
+                                  cudaMemcpyHostToDevice, st),
+                  "searchAsync: host to device copy of queries");
+        dqAll = reinterpret_cast<const float*>(region + L.offQueries);
+    }
+    float* dDistAll = t->distOnDevice ? distances : reinterpret_cast<float*>(region + L.offDist);
+    int64_t* dLabAll = t->labelsOnDevice ? reinterpret_cast<int64_t*>(labels)
+                                         : reinterpret_cast<int64_t*>(region + L.offLabels);
+    for (int b = 0; b < t->nbatches; b++) {
+        const int64_t q0 = (int64_t)b * batch;
+        const int64_t nq = std::min<int64_t>(batch, n - q0);
+        B200FSearchArgs a;
+        impl_->fillArgs(a, ntotal);
+        a.queries = dqAll + (size_t)q0 * d;
+        a.nq = nq;
+        a.k = (int)k;
+        a.out_dist = dDistAll + (size_t)q0 * k;
+        a.out_labels = dLabAll + (size_t)q0 * k;
+        a.scratch = region + L.offScratch;
+        a.scratch_bytes = L.scratchBytes;
+        a.status = t->status + 4 * b;
+        abiCheck(b200f_search(&a), "searchAsync");
+    }
+    if (!t->distOnDevice)
+        cudaCheck(cudaMemcpyAsync(t->host + t->hostDistOff, dDistAll, (size_t)n * k * 4,
+                                  cudaMemcpyDeviceToHost, st),
+                  "searchAsync: distances copy");
+    if (!t->labelsOnDevice)
+        cudaCheck(cudaMemcpyAsync(t->host + t->hostLabOff, dLabAll, (size_t)n * k * 8,
+                                  cudaMemcpyDeviceToHost, st),
+                  "searchAsync: labels copy");
+    cudaCheck(cudaMemcpyAsync(t->host + t->hostStatusOff, t->status, (size_t)t->nbatches * 16,
+                              cudaMemcpyDeviceToHost, st),
+              "searchAsync: status copy");
+    cudaCheck(cudaEventCreateWithFlags(&t->done, cudaEventDisableTiming), "event create");
+    cudaCheck(cudaEventRecord(t->done, st), "event record");
+    return B200SearchToken(std::move(t));
+}
+
+// ---------------------------------------------------------------------------------------
+// converters (src/MetalIndexFlat.mm:552-587)
+// ---------------------------------------------------------------------------------------
+std::unique_ptr<B200IndexFlat> index_cpu_to_gpu(std::shared_ptr<B200Resources> resources,
+                                                const faiss::IndexFlat* cpu_index,
+                                                StorageType storage) {
+    FAISS_THROW_IF_NOT_MSG(cpu_index != nullptr, "index_cpu_to_gpu: null index");
+    std::unique_ptr<B200IndexFlat> out(
+            new B200IndexFlat(std::move(resources), cpu_index->d, cpu_index->metric_type, storage));
+    if (cpu_index->ntotal > 0) {
+        out->reserve(cpu_index->ntotal);
+        out->add(cpu_index->ntotal, cpu_index->get_xb());
+    }
+    return out;
+}
+
+std::unique_ptr<faiss::IndexFlat> index_gpu_to_cpu(const B200IndexFlat* gpu_index) {
+    FAISS_THROW_IF_NOT_MSG(gpu_index != nullptr, "index_gpu_to_cpu: null index");
+    std::unique_ptr<faiss::IndexFlat> out(new faiss::IndexFlat(gpu_index->d, gpu_index->metric_type));
+    const faiss::idx_t n = gpu_index->ntotal;
+    if (n > 0) {
+        // one bulk dequantising read for every storage type (the reference loops
+        // per vector for 16-bit storage, :574-580)
+        const faiss::idx_t chunk = std::max<faiss::idx_t>(1, (faiss::idx_t)((256ull << 20) / ((size_t)gpu_index->d * 4)));
+        std::vector<float> buf;
+        for (faiss::idx_t r0 = 0; r0 < n; r0 += chunk) {
+            const faiss::idx_t nr = std::min<faiss::idx_t>(chunk, n - r0);
+            buf.resize((size_t)nr * gpu_index->d);
+            gpu_index->reconstruct_n(r0, nr, buf.data());
+            out->add(nr, buf.data());
+        }
+    }
+    return out;
+}
+
+}  // namespace faiss_b200

@@ -1,0 +1,184 @@
+// StandardB200Resources: device, stream, buffers, grow-only scratch and pinned staging.
+// Counterpart of src/StandardMetalResources.mm:10-91 and
+// src/MetalDeviceCapabilities.mm:8-124.
+#include <cuda_runtime.h>
+
+#include <sstream>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/b200_flat.h"
+#include "../include/faiss-b200/StandardB200Resources.h"
+
+namespace faiss_b200 {
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) {
+        std::string msg = std::string("faiss-b200: ") + what + ": " + cudaGetErrorString(e);
+        (void)cudaGetLastError();
+        throw std::runtime_error(msg);
+    }
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) check(cudaSetDevice(dev), "cudaSetDevice");
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) (void)cudaSetDevice(prev);
+    }
+};
+
+}  // namespace
+
+void* alloc_pinned(size_t bytes) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+void free_pinned(void* ptr) {
+    if (ptr) (void)cudaFreeHost(ptr);
+}
+
+B200DeviceCapabilities queryDeviceCapabilities(int device) {
+    B200FCaps c;
+    int rc = b200f_device_caps(device, &c);
+    if (rc != B200F_OK)
+        throw std::runtime_error(std::string("faiss-b200: cannot query device: ") +
+                                 b200f_status_string(rc));
+    B200DeviceCapabilities caps;
+    caps.device = c.device;
+    caps.ccMajor = c.cc_major;
+    caps.ccMinor = c.cc_minor;
+    caps.smCount = c.sm_count;
+    caps.maxSharedMemPerBlock = c.max_smem_per_block;
+    caps.l2Bytes = c.l2_bytes;
+    caps.hbmBytes = c.hbm_bytes;
+    caps.smClockKHz = c.sm_clock_khz;
+    caps.memClockKHz = c.mem_clock_khz;
+    caps.supported = c.supported != 0;
+    caps.name = c.name;
+    return caps;
+}
+
+std::string describeCapabilities(const B200DeviceCapabilities& caps) {
+    std::ostringstream os;
+    os << "device " << caps.device << ": " << caps.name << " (sm_" << caps.ccMajor << caps.ccMinor
+       << "), " << caps.smCount << " SMs, " << (caps.hbmBytes >> 20) << " MiB HBM, "
+       << (caps.l2Bytes >> 20) << " MiB L2, " << caps.maxSharedMemPerBlock
+       << " B shared memory per block, SM clock " << caps.smClockKHz / 1000 << " MHz, "
+       << (caps.supported ? "supported" : "NOT supported (needs sm_100)");
+    return os.str();
+}
+
+struct StandardB200Resources::Impl {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    B200DeviceCapabilities caps;
+    void* scratch = nullptr;
+    size_t scratchBytes = 0;
+    void* pinned = nullptr;
+    size_t pinnedBytes = 0;
+};
+
+StandardB200Resources::StandardB200Resources(int device) : impl_(new Impl) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        (void)cudaGetLastError();
+        throw std::runtime_error(
+                "faiss-b200: no CUDA device available (this backend has no CPU fallback)");
+    }
+    if (device < 0) check(cudaGetDevice(&device), "cudaGetDevice");
+    if (device >= count) throw std::runtime_error("faiss-b200: device ordinal out of range");
+    impl_->device = device;
+    impl_->caps = queryDeviceCapabilities(device);
+    if (!impl_->caps.supported)
+        throw std::runtime_error("faiss-b200: device is not sm_100 (" + impl_->caps.name +
+                                 "); kernels are built for sm_100a only");
+    DeviceGuard g(device);
+    check(cudaStreamCreateWithFlags(&impl_->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+}
+
+StandardB200Resources::~StandardB200Resources() {
+    if (!impl_) return;
+    int prev = -1;
+    (void)cudaGetDevice(&prev);
+    (void)cudaSetDevice(impl_->device);
+    if (impl_->stream) {
+        (void)cudaStreamSynchronize(impl_->stream);
+        (void)cudaStreamDestroy(impl_->stream);
+    }
+    if (impl_->scratch) (void)cudaFree(impl_->scratch);
+    if (impl_->pinned) (void)cudaFreeHost(impl_->pinned);
+    if (prev >= 0) (void)cudaSetDevice(prev);
+    (void)cudaGetLastError();
+}
+
+const B200DeviceCapabilities& StandardB200Resources::getCapabilities() const { return impl_->caps; }
+int StandardB200Resources::getDevice() const { return impl_->device; }
+StreamHandle StandardB200Resources::getDefaultStream() const { return impl_->stream; }
+
+void* StandardB200Resources::allocBuffer(size_t size) {
+    DeviceGuard g(impl_->device);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, size ? size : 256);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        throw std::runtime_error("faiss-b200: failed to allocate device buffer of " +
+                                 std::to_string(size) + " bytes: " + cudaGetErrorString(e));
+    }
+    return p;
+}
+
+void StandardB200Resources::deallocBuffer(void* buf) {
+    if (!buf) return;
+    DeviceGuard g(impl_->device);
+    (void)cudaFree(buf);
+}
+
+void* StandardB200Resources::getScratch(size_t bytes) {
+    if (bytes > impl_->scratchBytes) {
+        DeviceGuard g(impl_->device);
+        // work already queued on the stream may still use the old region
+        check(cudaStreamSynchronize(impl_->stream), "cudaStreamSynchronize");
+        if (impl_->scratch) (void)cudaFree(impl_->scratch);
+        impl_->scratch = nullptr;
+        impl_->scratchBytes = 0;
+        size_t want = bytes + (bytes >> 3);  // a little headroom against regrowth
+        want = (want + 255) & ~(size_t)255;
+        cudaError_t e = cudaMalloc(&impl_->scratch, want);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            want = (bytes + 255) & ~(size_t)255;
+            check(cudaMalloc(&impl_->scratch, want), "cudaMalloc(scratch)");
+        }
+        impl_->scratchBytes = want;
+    }
+    return impl_->scratch;
+}
+
+size_t StandardB200Resources::getScratchSize() const { return impl_->scratchBytes; }
+
+void* StandardB200Resources::getPinnedStaging(size_t bytes) {
+    if (bytes > impl_->pinnedBytes) {
+        DeviceGuard g(impl_->device);
+        check(cudaStreamSynchronize(impl_->stream), "cudaStreamSynchronize");
+        if (impl_->pinned) (void)cudaFreeHost(impl_->pinned);
+        impl_->pinned = nullptr;
+        impl_->pinnedBytes = 0;
+        check(cudaHostAlloc(&impl_->pinned, bytes, cudaHostAllocDefault), "cudaHostAlloc(staging)");
+        impl_->pinnedBytes = bytes;
+    }
+    return impl_->pinned;
+}
+
+}  // namespace faiss_b200

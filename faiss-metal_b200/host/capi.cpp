@@ -1,0 +1,235 @@
+// Handle-based C mirror of the plugin class for bindings that cannot hold a C++
+// object (ctypes, cgo, JNI).  Every function catches C++ exceptions and returns a
+// status code; the message is kept per thread for b200f_last_error().
+#include <cuda_runtime.h>
+#include <faiss/impl/FaissAssert.h>
+
+#include <memory>
+#include <new>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/b200_flat.h"
+#include "../include/faiss-b200/faiss_b200.h"
+
+using namespace faiss_b200;
+
+struct B200FResources {
+    std::shared_ptr<StandardB200Resources> res;
+};
+struct B200FIndex {
+    std::unique_ptr<B200IndexFlat> index;
+};
+struct B200FToken {
+    std::unique_ptr<B200SearchToken> token;
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+int classify(const std::string& msg) {
+    if (msg.find("out of range") != std::string::npos || msg.find("outside [0") != std::string::npos)
+        return B200F_ERR_RANGE;
+    if (msg.find("exceeds the maximum") != std::string::npos || msg.find("2^31-1") != std::string::npos)
+        return B200F_ERR_UNSUPPORTED;
+    if (msg.find("moved-from") != std::string::npos) return B200F_ERR_STATE;
+    return B200F_ERR_BAD_ARG;
+}
+
+#define B200F_GUARD_BEGIN try {
+#define B200F_GUARD_END                                                        \
+    }                                                                          \
+    catch (const faiss::FaissException& e) {                                   \
+        return fail(classify(e.what()), e.what());                             \
+    }                                                                          \
+    catch (const std::bad_alloc& e) {                                          \
+        return fail(B200F_ERR_OOM, e.what());                                  \
+    }                                                                          \
+    catch (const std::runtime_error& e) {                                      \
+        std::string m = e.what();                                              \
+        int code = B200F_ERR_CUDA;                                             \
+        if (m.find("no CUDA device") != std::string::npos ||                   \
+            m.find("not sm_100") != std::string::npos)                         \
+            code = B200F_ERR_NO_DEVICE;                                        \
+        else if (m.find("allocat") != std::string::npos)                       \
+            code = B200F_ERR_OOM;                                              \
+        else if (m.find("device status") != std::string::npos)                 \
+            code = B200F_ERR_DEVICE_WAIT;                                      \
+        return fail(code, m);                                                  \
+    }                                                                          \
+    catch (const std::exception& e) {                                          \
+        return fail(B200F_ERR_CUDA, e.what());                                 \
+    }                                                                          \
+    catch (...) {                                                              \
+        return fail(B200F_ERR_CUDA, "unknown exception");                      \
+    }
+
+}  // namespace
+
+extern "C" {
+
+const char* b200f_last_error(void) { return g_last_error.c_str(); }
+
+int b200f_resources_create(int device, B200FResources** out) {
+    if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");
+    *out = nullptr;
+    B200F_GUARD_BEGIN
+    std::unique_ptr<B200FResources> h(new B200FResources);
+    h->res = std::make_shared<StandardB200Resources>(device);
+    *out = h.release();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+void b200f_resources_destroy(B200FResources* res) { delete res; }
+
+int b200f_resources_device(const B200FResources* res) { return res ? res->res->getDevice() : -1; }
+
+void* b200f_resources_stream(const B200FResources* res) {
+    return res ? static_cast<void*>(res->res->getDefaultStream()) : nullptr;
+}
+
+size_t b200f_resources_scratch_bytes(const B200FResources* res) {
+    return res ? res->res->getScratchSize() : 0;
+}
+
+int b200f_index_create(B200FResources* res, int d, int metric, int storage, B200FIndex** out) {
+    if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");
+    *out = nullptr;
+    if (!res) return fail(B200F_ERR_BAD_ARG, "null resources");
+    if (metric != B200F_METRIC_L2 && metric != B200F_METRIC_INNER_PRODUCT)
+        return fail(B200F_ERR_BAD_ARG, "metric must be L2 or inner product");
+    if (storage < 0 || storage > 2) return fail(B200F_ERR_BAD_ARG, "invalid storage type");
+    B200F_GUARD_BEGIN
+    std::unique_ptr<B200FIndex> h(new B200FIndex);
+    h->index.reset(new B200IndexFlat(res->res, d,
+                                     metric == B200F_METRIC_L2 ? faiss::METRIC_L2
+                                                               : faiss::METRIC_INNER_PRODUCT,
+                                     static_cast<StorageType>(storage)));
+    *out = h.release();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+void b200f_index_destroy(B200FIndex* index) { delete index; }
+
+int b200f_index_add(B200FIndex* index, int64_t n, const float* x) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->add(n, x);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_reserve(B200FIndex* index, int64_t n) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->reserve(n);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_search(const B200FIndex* index, int64_t n, const float* x, int64_t k,
+                       float* distances, int64_t* labels) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->search(n, x, k, distances, reinterpret_cast<faiss::idx_t*>(labels));
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_search_async(const B200FIndex* index, int64_t n, const float* x, int64_t k,
+                             float* distances, int64_t* labels, B200FToken** out) {
+    if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");
+    *out = nullptr;
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    std::unique_ptr<B200FToken> h(new B200FToken);
+    h->token.reset(new B200SearchToken(
+            index->index->searchAsync(n, x, k, distances, reinterpret_cast<faiss::idx_t*>(labels))));
+    *out = h.release();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_token_wait(B200FToken* token) {
+    if (!token || !token->token) return fail(B200F_ERR_STATE, "null or consumed token");
+    B200F_GUARD_BEGIN
+    token->token->wait();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_token_is_ready(const B200FToken* token, int* ready) {
+    if (!token || !token->token || !ready) return fail(B200F_ERR_STATE, "null or consumed token");
+    B200F_GUARD_BEGIN
+    *ready = token->token->isReady() ? 1 : 0;
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+void b200f_token_destroy(B200FToken* token) { delete token; }
+
+int b200f_index_reset(B200FIndex* index) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->reset();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_reconstruct(const B200FIndex* index, int64_t key, float* recons) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->reconstruct(key, recons);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_reconstruct_n(const B200FIndex* index, int64_t first, int64_t n, float* out) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->reconstruct_n(first, n, out);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int64_t b200f_index_ntotal(const B200FIndex* index) { return index ? index->index->ntotal : -1; }
+int b200f_index_d(const B200FIndex* index) { return index ? index->index->d : -1; }
+int b200f_index_metric(const B200FIndex* index) {
+    if (!index) return -1;
+    return index->index->metric_type == faiss::METRIC_L2 ? B200F_METRIC_L2 : B200F_METRIC_INNER_PRODUCT;
+}
+int b200f_index_storage(const B200FIndex* index) {
+    return index ? (int)index->index->getStorageType() : -1;
+}
+
+int b200f_index_set_path(B200FIndex* index, int path) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->setForcePath(path);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_set_label_base(B200FIndex* index, int64_t base) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    index->index->setLabelBase(base);
+    return B200F_OK;
+}
+
+const void* b200f_index_device_rows(const B200FIndex* index) {
+    return index ? index->index->getDeviceRows() : nullptr;
+}
+
+int b200f_index_last_device_status(const B200FIndex* index) {
+    return index ? index->index->lastDeviceStatus() : -1;
+}
+
+}  // extern "C"

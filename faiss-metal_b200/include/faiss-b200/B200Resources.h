@@ -1,0 +1,46 @@
+// Resource manager interface of the B200 backend.
+// Counterpart of include/faiss-metal/MetalResources.h:20-54: device handle,
+// default queue (a CUDA stream here), buffer allocation, and page-aligned host
+// allocation for staging (pinned memory here).
+#pragma once
+#include <cstddef>
+#include <memory>
+
+#include "B200DeviceCapabilities.h"
+
+struct CUstream_st;
+
+namespace faiss_b200 {
+
+typedef CUstream_st* StreamHandle;  // == cudaStream_t
+
+/// Pinned host memory suitable for asynchronous copies; the analogue of the
+/// reference's alloc_aligned / free_aligned (MetalResources.h:20-34).
+/// Returns nullptr on failure.
+void* alloc_pinned(size_t bytes);
+void free_pinned(void* ptr);
+
+class B200Resources {
+   public:
+    virtual ~B200Resources() = default;
+
+    virtual const B200DeviceCapabilities& getCapabilities() const = 0;
+    virtual int getDevice() const = 0;
+    virtual StreamHandle getDefaultStream() const = 0;
+
+    /// Device buffer (throws std::runtime_error on failure,
+    /// src/StandardMetalResources.mm:68-76).
+    virtual void* allocBuffer(size_t size) = 0;
+    virtual void deallocBuffer(void* buf) = 0;
+
+    /// Grow-only scratch region shared by the synchronous searches of every index
+    /// that uses these resources (src/MetalIndexFlat.mm:102-142 kept one per index).
+    /// The pointer stays valid until the next call with a larger size; work using it
+    /// must be ordered on the default stream.
+    virtual void* getScratch(size_t bytes) = 0;
+    virtual size_t getScratchSize() const = 0;
+    /// Grow-only pinned staging region (same lifetime rule as getScratch).
+    virtual void* getPinnedStaging(size_t bytes) = 0;
+};
+
+}  // namespace faiss_b200

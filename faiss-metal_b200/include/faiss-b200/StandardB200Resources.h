@@ -1,0 +1,30 @@
+// Default resource manager: one device, one stream, grow-only scratch arena.
+// Counterpart of include/faiss-metal/StandardMetalResources.h:9-32.
+#pragma once
+#include "B200Resources.h"
+
+namespace faiss_b200 {
+
+class StandardB200Resources : public B200Resources {
+   public:
+    /// device < 0 selects the calling thread's current CUDA device.
+    /// Throws std::runtime_error when there is no sm_100 device: there is no
+    /// CPU fallback (src/StandardMetalResources.mm:17-44 throws likewise).
+    explicit StandardB200Resources(int device = -1);
+    ~StandardB200Resources() override;
+
+    const B200DeviceCapabilities& getCapabilities() const override;
+    int getDevice() const override;
+    StreamHandle getDefaultStream() const override;
+    void* allocBuffer(size_t size) override;
+    void deallocBuffer(void* buf) override;
+    void* getScratch(size_t bytes) override;
+    size_t getScratchSize() const override;
+    void* getPinnedStaging(size_t bytes) override;
+
+   private:
+    struct Impl;
+    std::unique_ptr<Impl> impl_;
+};
+
+}  // namespace faiss_b200

@@ -1,0 +1,187 @@
+"""Python mirror of the plugin classes (faiss_metal::MetalIndexFlat and friends,
+include/faiss-metal/MetalIndexFlat.h:13-120) over the handle-based C-ABI.
+
+Arrays may be numpy arrays (host) or torch CUDA tensors (device); the C-ABI
+detects which from the pointer.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from . import abi
+
+
+def device_caps(device: int = -1) -> dict:
+    c = abi.Caps()
+    abi.check_op(abi.lib().b200f_device_caps(device, ctypes.byref(c)), "device_caps")
+    out = {name: getattr(c, name) for name, _ in abi.Caps._fields_}
+    out["name"] = c.name.decode()
+    return out
+
+
+def _ptr(a):
+    """Raw address of a numpy array or torch tensor (contiguous)."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        if not a.flags["C_CONTIGUOUS"]:
+            raise ValueError("array must be C-contiguous")
+        return ctypes.c_void_p(a.ctypes.data)
+    if hasattr(a, "data_ptr"):
+        if not a.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return ctypes.c_void_p(a.data_ptr())
+    raise TypeError("expected numpy array or torch tensor")
+
+
+class StandardB200Resources:
+    """StandardMetalResources (include/faiss-metal/StandardMetalResources.h:9-32)."""
+
+    def __init__(self, device: int = -1):
+        h = ctypes.c_void_p()
+        abi.check(abi.lib().b200f_resources_create(device, ctypes.byref(h)), "resources")
+        self._h = h
+
+    @property
+    def device(self) -> int:
+        return abi.lib().b200f_resources_device(self._h)
+
+    @property
+    def stream(self) -> int:
+        return abi.lib().b200f_resources_stream(self._h) or 0
+
+    @property
+    def scratch_bytes(self) -> int:
+        return abi.lib().b200f_resources_scratch_bytes(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            abi.lib().b200f_resources_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class SearchToken:
+    """MetalSearchToken (include/faiss-metal/MetalIndexFlat.h:15-36)."""
+
+    def __init__(self, handle, keepalive):
+        self._h = handle
+        self._keep = keepalive
+
+    def wait(self):
+        if self._h is None:
+            raise abi.B200Error(abi.lib().b200f_token_wait(None), "token already consumed")
+        abi.check(abi.lib().b200f_token_wait(self._h), "token wait")
+
+    def is_ready(self) -> bool:
+        r = ctypes.c_int(0)
+        abi.check(abi.lib().b200f_token_is_ready(self._h, ctypes.byref(r)), "token is_ready")
+        return bool(r.value)
+
+    def close(self):
+        if self._h is not None:
+            abi.lib().b200f_token_destroy(self._h)  # waits if never waited
+            self._h = None
+            self._keep = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class B200IndexFlat:
+    """MetalIndexFlat (include/faiss-metal/MetalIndexFlat.h:47-111)."""
+
+    def __init__(self, resources: StandardB200Resources, d: int, metric: int = abi.METRIC_L2,
+                 storage: int = abi.STORAGE_F32):
+        h = ctypes.c_void_p()
+        abi.check(abi.lib().b200f_index_create(resources._h, d, metric, storage, ctypes.byref(h)), "index")
+        self._h = h
+        self.resources = resources
+        self.d = d
+        self.metric_type = metric
+        self.storage = storage
+        self.is_trained = True
+
+    # -- faiss::Index surface ---------------------------------------------------------
+    @property
+    def ntotal(self) -> int:
+        return abi.lib().b200f_index_ntotal(self._h)
+
+    def add(self, x):
+        n = int(x.shape[0])
+        if n and int(x.shape[1]) != self.d:
+            raise ValueError("add: expected [n, %d]" % self.d)
+        abi.check(abi.lib().b200f_index_add(self._h, n, _ptr(x) if n else None), "add")
+
+    def reserve(self, n: int):
+        abi.check(abi.lib().b200f_index_reserve(self._h, int(n)), "reserve")
+
+    def search(self, x, k: int, distances=None, labels=None):
+        """Returns (distances float32 [n,k], labels int64 [n,k]) in the memory space of x
+        unless output arrays are given."""
+        n = int(x.shape[0])
+        if distances is None or labels is None:
+            if isinstance(x, np.ndarray):
+                distances = np.empty((n, k), dtype=np.float32)
+                labels = np.empty((n, k), dtype=np.int64)
+            else:
+                import torch
+                distances = torch.empty((n, k), dtype=torch.float32, device=x.device)
+                labels = torch.empty((n, k), dtype=torch.int64, device=x.device)
+        abi.check(abi.lib().b200f_index_search(self._h, n, _ptr(x) if n else None, int(k),
+                                                _ptr(distances), _ptr(labels)), "search")
+        return distances, labels
+
+    def search_async(self, x, k: int, distances, labels) -> SearchToken:
+        n = int(x.shape[0])
+        t = ctypes.c_void_p()
+        abi.check(abi.lib().b200f_index_search_async(self._h, n, _ptr(x) if n else None, int(k),
+                                                      _ptr(distances), _ptr(labels), ctypes.byref(t)),
+                  "search_async")
+        return SearchToken(t, (distances, labels))
+
+    def reset(self):
+        abi.check(abi.lib().b200f_index_reset(self._h), "reset")
+
+    def reconstruct(self, key: int) -> np.ndarray:
+        out = np.empty(self.d, dtype=np.float32)
+        abi.check(abi.lib().b200f_index_reconstruct(self._h, int(key), _ptr(out)), "reconstruct")
+        return out
+
+    def reconstruct_n(self, first: int, n: int, out=None):
+        if out is None:
+            out = np.empty((n, self.d), dtype=np.float32)
+        abi.check(abi.lib().b200f_index_reconstruct_n(self._h, int(first), int(n), _ptr(out)), "reconstruct_n")
+        return out
+
+    # -- extras ---------------------------------------------------------------------------
+    def set_path(self, path: int):
+        abi.check(abi.lib().b200f_index_set_path(self._h, int(path)), "set_path")
+
+    def set_label_base(self, base: int):
+        abi.check(abi.lib().b200f_index_set_label_base(self._h, int(base)), "set_label_base")
+
+    @property
+    def last_device_status(self) -> int:
+        return abi.lib().b200f_index_last_device_status(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            abi.lib().b200f_index_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

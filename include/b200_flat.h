@@ -1,0 +1,251 @@
+/*
+ * b200_flat.h -- C-ABI of the B200 (sm_100a) flat k-NN search backend.
+ *
+ * This is the whole drop-in boundary: plain C types, caller-owned pointers,
+ * status codes instead of exceptions.  Two groups of entry points:
+ *
+ *   1. "op" entry points: one launcher per device operation.  They are what the
+ *      reference's op wrappers (MetalL2Norm, MetalDistance, MetalSelect) were to
+ *      its index class.  Pointers are DEVICE pointers, work is enqueued on the
+ *      given CUDA stream and nothing is allocated inside.
+ *   2. "index" entry points: a handle-based mirror of the reference's plugin
+ *      class (faiss_metal::MetalIndexFlat) for bindings that cannot hold a C++
+ *      object (ctypes, cgo, JNI, N-API).  Pointers are HOST pointers unless the
+ *      comment says "host or device".
+ *
+ * Each declaration cites the reference interface it replaces
+ * (path inside the reference project : line).
+ */
+#ifndef B200_FLAT_H
+#define B200_FLAT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums ------------------------------------------------------------ */
+
+/* faiss::MetricType values used by the reference (src/MetalDistance.h:21-22). */
+#define B200F_METRIC_INNER_PRODUCT 0
+#define B200F_METRIC_L2 1
+
+/* faiss_metal::StorageType (include/faiss-metal/MetalIndexFlat.h:39-43). */
+#define B200F_STORAGE_F32 0
+#define B200F_STORAGE_F16 1
+#define B200F_STORAGE_BF16 2
+
+/* Status codes (the reference throws: src/MetalIndexFlat.mm:321-326,
+ * src/MetalSelect.mm:67-70, src/StandardMetalResources.mm:21-23,71-74). */
+#define B200F_OK 0
+#define B200F_ERR_BAD_ARG 1      /* null pointer, k <= 0, bad enum, misaligned pitch   */
+#define B200F_ERR_UNSUPPORTED 2  /* k above B200F_MAX_K, ntotal above 2^31-1            */
+#define B200F_ERR_SCRATCH 3      /* scratch buffer smaller than *_scratch_bytes()       */
+#define B200F_ERR_CUDA 4         /* CUDA runtime / driver call failed                   */
+#define B200F_ERR_DEVICE_WAIT 5  /* a bounded device-side wait ran out (status word)    */
+#define B200F_ERR_NO_DEVICE 6    /* no sm_100 device; there is no CPU fallback          */
+#define B200F_ERR_OOM 7          /* device or pinned-host allocation failed             */
+#define B200F_ERR_RANGE 8        /* reconstruct key out of range                        */
+#define B200F_ERR_STATE 9        /* token already consumed / moved-from                 */
+
+/* Largest k any path accepts (README.md:218-219 / src/MetalSelect.mm:65-70: 4096 on M3+). */
+#define B200F_MAX_K 4096
+/* Largest k served by the fused (no distance matrix) epilogue and scan kernels
+ * (src/MetalDistance.mm:346-354: k <= 32). */
+#define B200F_FUSED_MAX_K 32
+
+/* Path override for tests, the analogue of MetalIndexFlat::setForceMPS
+ * (include/faiss-metal/MetalIndexFlat.h:106): 0 = choose by (nq, k). */
+#define B200F_PATH_AUTO 0
+#define B200F_PATH_SCAN 1    /* streaming CUDA-core scan (small nq)          */
+#define B200F_PATH_TENSOR 2  /* tcgen05 GEMM with fused top-k / select      */
+
+const char* b200f_status_string(int status);
+
+/* ---- device capabilities ----------------------------------------------- */
+/* Replaces MetalDeviceCapabilities / queryDeviceCapabilities
+ * (include/faiss-metal/MetalDeviceCapabilities.h:23-61,
+ *  src/MetalDeviceCapabilities.mm:8-96). */
+typedef struct B200FCaps {
+    int32_t device;
+    int32_t cc_major, cc_minor;
+    int32_t sm_count;
+    int32_t max_smem_per_block;   /* opt-in bytes */
+    int32_t l2_bytes;
+    int64_t hbm_bytes;
+    int32_t sm_clock_khz;
+    int32_t mem_clock_khz;
+    int32_t supported;            /* 1 when the device is sm_100 */
+    char name[128];
+} B200FCaps;
+
+int b200f_device_count(int* count);
+int b200f_device_caps(int device, B200FCaps* caps);
+
+/* ---- op entry points (device pointers, async on `stream`) --------------- */
+
+/* out[r] = sum_j rows[r][j]^2 in fp32.
+ * Replaces MetalL2Norm::encode (src/MetalL2Norm.mm:42-74) and kernels
+ * l2_norm / l2_norm_large / l2_norm_f16 / l2_norm_f16_large
+ * (shaders/l2_norm.metal:7-66, shaders/l2_norm_f16.metal:10-67). */
+int b200f_row_norms(const void* rows, int storage, int64_t n, int d, int64_t pitch_elems,
+                    float* out, void* stream);
+
+/* Append-time conversion: src fp32 [n][d] (pitch d) -> dst rows in `storage`
+ * precision (pitch dst_pitch elements, pad columns zeroed), optional squared
+ * norms of the STORED values, and for FP32 storage the three bf16 split
+ * planes the tensor path multiplies (planes[p][r][plane_pitch], plane p at
+ * p*plane_stride elements).
+ * Replaces the conversion loops and the per-add norm pass of
+ * MetalIndexFlat::add (src/MetalIndexFlat.mm:224-255,259-268,296-307). */
+int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
+                     int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
+                     int64_t plane_stride, float* norms_or_null, void* stream);
+
+/* Stored rows -> fp32 [n][d] (pitch d).
+ * Replaces the per-element conversions of MetalIndexFlat::reconstruct
+ * (src/MetalIndexFlat.mm:508-527). */
+int b200f_load_rows(const void* rows, int storage, int64_t n, int d, int64_t pitch_elems,
+                    float* dst, void* stream);
+
+/* Arguments of one shard-local search. */
+typedef struct B200FSearchArgs {
+    const float* queries;    /* device fp32 [nq][d], pitch d                                */
+    int64_t nq;
+    int32_t d;
+    int32_t storage;         /* B200F_STORAGE_*                                             */
+    const void* rows;        /* device stored rows [nb][row_pitch]                          */
+    int64_t row_pitch;       /* elements; 16-bit: multiple of 8, fp32: multiple of 4        */
+    const uint16_t* planes;  /* FP32 storage: bf16 split planes, else NULL                  */
+    int64_t plane_pitch;     /* elements, multiple of 8                                     */
+    int64_t plane_stride;    /* elements between planes                                     */
+    const float* norms;      /* device [nb] squared norms (L2), NULL for inner product      */
+    int64_t nb;              /* rows in this shard, <= 2^31-1                               */
+    int32_t metric;          /* B200F_METRIC_*                                              */
+    int32_t k;
+    int64_t label_base;      /* added to local row numbers to form labels                   */
+    float* out_dist;         /* device [nq][k], best first; tail (+/-INF) when k > nb       */
+    int64_t* out_labels;     /* device [nq][k]; tail -1                                     */
+    void* scratch;           /* device, >= b200f_search_scratch_bytes(), 256-byte aligned   */
+    size_t scratch_bytes;
+    int32_t* status;         /* device int32[4], zeroed by the call; [0] != 0 after the
+                                stream drains means a bounded device wait ran out          */
+    void* stream;
+    int32_t path;            /* B200F_PATH_*                                                */
+    int32_t reserved;
+} B200FSearchArgs;
+
+/* Scratch bytes b200f_search needs for this shape (0 on bad arguments).
+ * Replaces the grow-only scratch getters of the reference's index
+ * (src/MetalIndexFlat.mm:102-142). */
+size_t b200f_search_scratch_bytes(int64_t nq, int64_t nb, int d, int k, int storage, int path);
+
+/* Shard-local k-NN: query norms, distance (tensor-core GEMM or streaming scan)
+ * fused with top-k, and the merge of per-range partial lists.
+ * Replaces MetalDistance::encodeFused / encode + MetalSelect::encode as driven
+ * by MetalIndexFlat::search (src/MetalIndexFlat.mm:358-378,
+ * src/MetalDistance.mm:107-128,225-408, src/MetalSelect.mm:34-89) and kernels
+ * simdgroup_gemm_* (shaders/simdgroup_gemm*.metal), fused_*_topk_*
+ * (shaders/fused_l2_topk.metal:19-444), warp_select_* / block_select_*
+ * (shaders/warp_select.metal:11-114, shaders/block_select.metal:111-274). */
+int b200f_search(const B200FSearchArgs* args);
+
+/* Full nq x nb score matrix (L2: ||q||^2 + ||x||^2 - 2 q.x, IP: q.x), fp32,
+ * leading dimension ld_out.  Same operands as b200f_search (k, out_*, label_base
+ * ignored).  Scratch: b200f_search_scratch_bytes(nq, nb, d, 1, storage, path).
+ * Replaces MetalDistance::encode / compute (src/MetalDistance.h:25-80,
+ * src/MetalDistance.mm:107-128); used by the unit tests the way
+ * tests/test_metal_distance.mm:98-230 uses it. */
+int b200f_pairwise(const B200FSearchArgs* args, float* out_matrix, int64_t ld_out);
+
+/* Top-k of every row of a device score matrix [nq][ncols] (leading dimension
+ * ld): smallest first for L2, largest first for inner product, ties to the
+ * lower column.  k <= B200F_MAX_K.  Scratch: b200f_select_scratch_bytes().
+ * Replaces MetalSelect::encode / select (src/MetalSelect.mm:34-108). */
+size_t b200f_select_scratch_bytes(int64_t nq, int k);
+int b200f_select_rows(const float* scores, int64_t nq, int64_t ncols, int64_t ld, int metric,
+                      int k, float* out_dist, int64_t* out_labels, void* scratch,
+                      size_t scratch_bytes, void* stream);
+
+/* k-way merge of P result lists per query.  dist / labels are device
+ * [P][nq][k] (each list best first, padded with -1 labels); output [nq][k]
+ * best first, ties to the lower label.  This is the step after the NCCL
+ * allgather of per-GPU candidates; the reference is single-device and has no
+ * counterpart (its closest relative is the final 4-list merge inside
+ * shaders/fused_l2_topk.metal:88-131). */
+int b200f_merge_lists(const float* dist, const int64_t* labels, int P, int64_t nq, int k,
+                      int metric, float* out_dist, int64_t* out_labels, void* stream);
+
+/* Deterministic synthetic rows on the device (benchmark inputs): element
+ * (row, col) depends only on (seed, row0 + row, col).
+ * dist: 0 = U[0,1), 1 = N(0,1) * scale, 2 = N(0,1) then row-normalised.
+ * No counterpart in the reference (its bench fills host arrays with
+ * std::mt19937, tests/bench_metal_flat.mm:27-33). */
+int b200f_fill_synthetic(float* dst, int64_t n, int d, int64_t row0, uint64_t seed, int dist,
+                         float scale, void* stream);
+
+/* ---- index entry points (mirror of faiss_metal::MetalIndexFlat) ---------- */
+
+typedef struct B200FResources B200FResources; /* StandardMetalResources (include/faiss-metal/StandardMetalResources.h:9-32) */
+typedef struct B200FIndex B200FIndex;         /* MetalIndexFlat (include/faiss-metal/MetalIndexFlat.h:47-111)               */
+typedef struct B200FToken B200FToken;         /* MetalSearchToken (include/faiss-metal/MetalIndexFlat.h:15-36)              */
+
+/* Message of the last failed index-level call on this thread. */
+const char* b200f_last_error(void);
+
+/* StandardMetalResources() (src/StandardMetalResources.mm:17-44): device < 0 = current device. */
+int b200f_resources_create(int device, B200FResources** out);
+void b200f_resources_destroy(B200FResources* res);
+int b200f_resources_device(const B200FResources* res);
+void* b200f_resources_stream(const B200FResources* res);
+/* bytes currently held by the grow-only scratch arena (src/MetalIndexFlat.mm:102-142) */
+size_t b200f_resources_scratch_bytes(const B200FResources* res);
+
+/* MetalIndexFlat(resources, d, metric, storage) (src/MetalIndexFlat.mm:162-183). */
+int b200f_index_create(B200FResources* res, int d, int metric, int storage, B200FIndex** out);
+void b200f_index_destroy(B200FIndex* index);
+/* add(n, x): x fp32 [n][d], host or device (src/MetalIndexFlat.mm:185-311). */
+int b200f_index_add(B200FIndex* index, int64_t n, const float* x);
+/* search(n, x, k, distances, labels): x host or device; outputs in the same
+ * memory space as x is NOT required: each output pointer may independently be
+ * host or device (src/MetalIndexFlat.mm:313-401). */
+int b200f_index_search(const B200FIndex* index, int64_t n, const float* x, int64_t k,
+                       float* distances, int64_t* labels);
+/* searchAsync -> token; token wait / isReady / destructor
+ * (src/MetalIndexFlat.mm:403-490, :41-78). */
+int b200f_index_search_async(const B200FIndex* index, int64_t n, const float* x, int64_t k,
+                             float* distances, int64_t* labels, B200FToken** out);
+int b200f_token_wait(B200FToken* token);
+int b200f_token_is_ready(const B200FToken* token, int* ready);
+void b200f_token_destroy(B200FToken* token);
+/* reset() (src/MetalIndexFlat.mm:492-506), reconstruct(key, out) (:508-527). */
+int b200f_index_reset(B200FIndex* index);
+int b200f_index_reconstruct(const B200FIndex* index, int64_t key, float* recons);
+/* Bulk form used by index_metal_to_cpu (src/MetalIndexFlat.mm:565-587):
+ * rows [first, first+n) as fp32 into out (host or device). */
+int b200f_index_reconstruct_n(const B200FIndex* index, int64_t first, int64_t n, float* out);
+/* getters (src/MetalIndexFlat.mm:529-548) */
+int64_t b200f_index_ntotal(const B200FIndex* index);
+int b200f_index_d(const B200FIndex* index);
+int b200f_index_metric(const B200FIndex* index);
+int b200f_index_storage(const B200FIndex* index);
+/* Path override for tests (setForceMPS analogue, include/faiss-metal/MetalIndexFlat.h:106). */
+int b200f_index_set_path(B200FIndex* index, int path);
+/* Pre-size the storage for n rows in total (avoids the x2 growth copies of
+ * src/MetalIndexFlat.mm:196-208 when the final size is known). */
+int b200f_index_reserve(B200FIndex* index, int64_t n);
+/* Row shards: labels returned by search = local row number + base. */
+int b200f_index_set_label_base(B200FIndex* index, int64_t base);
+/* Device pointers to the stored rows / norms of the shard (used by the
+ * multi-GPU layer and the benchmark; the reference's getVectorsData,
+ * include/faiss-metal/MetalIndexFlat.h:94, returned a unified-memory pointer). */
+const void* b200f_index_device_rows(const B200FIndex* index);
+/* Device-side status of the most recent search (0 = fine). */
+int b200f_index_last_device_status(const B200FIndex* index);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_FLAT_H */

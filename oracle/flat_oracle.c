@@ -1,0 +1,289 @@
+/*
+ * CPU oracle for flat (brute-force) k-NN search.  TEST INFRASTRUCTURE ONLY:
+ * nothing in the shipped library links, loads or calls this file; only the
+ * test-suite, the smoke check and the benchmark's CPU-baseline leg do.
+ *
+ * It restates the CPU semantics the reference is checked against
+ * (faiss::IndexFlatL2 / IndexFlatIP as exercised by
+ * tests/test_metal_flat.mm:73-78,108-113) using the reference's own plain
+ * CPU loops:
+ *   - squared row norm          tests/test_metal_distance.mm:46-51
+ *   - squared L2 distance       tests/test_metal_distance.mm:141-147  (sum (q-x)^2)
+ *   - inner product             tests/test_metal_distance.mm:193-198  (sum q*x)
+ *   - result order / padding    src/MetalIndexFlat.mm:328-334,384-400
+ *       best-first (ascending L2, descending IP), labels = insertion order,
+ *       tail j >= ntotal filled with (+INF,-1) for L2 and (-INF,-1) for IP
+ *   - bf16 rounding             src/MetalIndexFlat.mm:231-234 (round-to-nearest-even on bits)
+ *   - fp16 rounding             src/MetalIndexFlat.mm:245-255 ((__fp16)x, round-to-nearest-even)
+ *
+ * Accumulation is in double so that the order of summation does not matter
+ * at the tolerances the tests use.  Ties are broken towards the lower label.
+ *
+ * PARITY PINNING: the reference holds no golden vectors for this path (its
+ * tests compare against an external CPU FAISS build that is not available
+ * here).  The oracle is pinned on the reference's known-answer cases only
+ * (empty index, k > ntotal padding, fp32 reconstruct bit-exactness, fp16
+ * reconstruct tolerance, norm / distance loops); distances and ranks >= 2 are
+ * "parity unpinned" beyond those.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORACLE_METRIC_IP 0
+#define ORACLE_METRIC_L2 1
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* fp32 -> bf16 bits, round-to-nearest-even on the bit pattern
+ * (src/MetalIndexFlat.mm:231-234). NaN keeps a quiet-NaN pattern. */
+uint16_t oracle_f32_to_bf16(float f) {
+    uint32_t bits;
+    memcpy(&bits, &f, 4);
+    if ((bits & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((bits >> 16) | 0x0040u);
+    uint32_t lsb = (bits >> 16) & 1u;
+    return (uint16_t)((bits + 0x7fffu + lsb) >> 16);
+}
+
+float oracle_bf16_to_f32(uint16_t h) {
+    uint32_t bits = (uint32_t)h << 16; /* src/MetalIndexFlat.mm:508-527: bf16 << 16 */
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* fp32 -> IEEE binary16 bits, round-to-nearest-even, with subnormals and
+ * overflow to infinity: what the C cast (__fp16)x does. */
+uint16_t oracle_f32_to_fp16(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t absx = x & 0x7fffffffu;
+    if (absx > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);            /* NaN */
+    if (absx >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);           /* >= 65520 -> inf */
+    if (absx < 0x33000001u) return (uint16_t)sign;                        /* <= 2^-25 -> 0 */
+    int32_t exp = (int32_t)(absx >> 23) - 127;
+    uint32_t man = (absx & 0x7fffffu) | 0x800000u;
+    uint32_t shift, half_bits;
+    if (exp < -14) {                     /* subnormal half */
+        shift = (uint32_t)(13 + (-14 - exp));
+        half_bits = 0;
+    } else {
+        shift = 13;
+        half_bits = (uint32_t)(exp + 15) << 10;
+        man &= 0x7fffffu;
+    }
+    uint32_t q = man >> shift;
+    uint32_t rem = man & ((1u << shift) - 1u);
+    uint32_t halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (q & 1u))) q++;
+    return (uint16_t)(sign | (half_bits + q)); /* carry into exponent is correct */
+}
+
+float oracle_fp16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            int e = -1;
+            do { man <<= 1; e++; } while (!(man & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* storage: 0 = fp32 (copy), 1 = fp16, 2 = bf16.  out[i] = dequantised(in[i]). */
+void oracle_round_storage(const float* in, int64_t count, int storage, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < count; i++) {
+        if (storage == 1) out[i] = oracle_fp16_to_f32(oracle_f32_to_fp16(in[i]));
+        else if (storage == 2) out[i] = oracle_bf16_to_f32(oracle_f32_to_bf16(in[i]));
+        else out[i] = in[i];
+    }
+}
+
+void oracle_to_bits16(const float* in, int64_t count, int storage, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < count; i++)
+        out[i] = (storage == 1) ? oracle_f32_to_fp16(in[i]) : oracle_f32_to_bf16(in[i]);
+}
+
+/* out[r] = sum_j x[r][j]^2  (tests/test_metal_distance.mm:46-51), double accumulate */
+void oracle_row_norms(const float* x, int64_t n, int d, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; r++) {
+        const float* row = x + r * (int64_t)d;
+        double s = 0.0;
+        for (int j = 0; j < d; j++) s += (double)row[j] * (double)row[j];
+        out[r] = (float)s;
+    }
+}
+
+/* one (query,row) score in double.
+ * L2: sum (q-x)^2  (tests/test_metal_distance.mm:141-147)
+ * IP: sum q*x      (tests/test_metal_distance.mm:193-198) */
+static inline double score_l2(const float* q, const float* x, int d) {
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    int j = 0;
+    for (; j + 4 <= d; j += 4) {
+        double a = (double)q[j] - (double)x[j];
+        double b = (double)q[j + 1] - (double)x[j + 1];
+        double c = (double)q[j + 2] - (double)x[j + 2];
+        double e = (double)q[j + 3] - (double)x[j + 3];
+        s0 += a * a; s1 += b * b; s2 += c * c; s3 += e * e;
+    }
+    for (; j < d; j++) { double a = (double)q[j] - (double)x[j]; s0 += a * a; }
+    return (s0 + s1) + (s2 + s3);
+}
+
+static inline double score_ip(const float* q, const float* x, int d) {
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    int j = 0;
+    for (; j + 4 <= d; j += 4) {
+        s0 += (double)q[j] * (double)x[j];
+        s1 += (double)q[j + 1] * (double)x[j + 1];
+        s2 += (double)q[j + 2] * (double)x[j + 2];
+        s3 += (double)q[j + 3] * (double)x[j + 3];
+    }
+    for (; j < d; j++) s0 += (double)q[j] * (double)x[j];
+    return (s0 + s1) + (s2 + s3);
+}
+
+/* full nq x nb score matrix in double (small cases only) */
+void oracle_pairwise(int metric, const float* xb, int64_t nb, const float* xq,
+                     int64_t nq, int d, double* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < nq; i++)
+        for (int64_t j = 0; j < nb; j++)
+            out[i * nb + j] = (metric == ORACLE_METRIC_L2)
+                                      ? score_l2(xq + i * (int64_t)d, xb + j * (int64_t)d, d)
+                                      : score_ip(xq + i * (int64_t)d, xb + j * (int64_t)d, d);
+}
+
+/* scores of given (query, label) pairs: out[i*k+j] = score(q_i, x_{labels[i*k+j]});
+ * labels < 0 give +/-INF like the padding rule. */
+void oracle_rescore(int metric, const float* xb, int64_t nb, const float* xq,
+                    int64_t nq, int d, int64_t k, const int64_t* labels, double* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < nq; i++)
+        for (int64_t j = 0; j < k; j++) {
+            int64_t l = labels[i * k + j];
+            if (l < 0 || l >= nb) {
+                out[i * k + j] = (metric == ORACLE_METRIC_L2) ? INFINITY : -INFINITY;
+            } else {
+                out[i * k + j] = (metric == ORACLE_METRIC_L2)
+                                         ? score_l2(xq + i * (int64_t)d, xb + l * (int64_t)d, d)
+                                         : score_ip(xq + i * (int64_t)d, xb + l * (int64_t)d, d);
+            }
+        }
+}
+
+/* sorted bounded list: key ascending ("smaller is better"), ties -> lower id first */
+static inline void list_insert(double* keys, int64_t* ids, int64_t k, double key, int64_t id) {
+    /* caller guarantees key < keys[k-1] (strict: an equal later id never displaces) */
+    int64_t j = k - 1;
+    while (j > 0 && keys[j - 1] > key) {
+        keys[j] = keys[j - 1];
+        ids[j] = ids[j - 1];
+        j--;
+    }
+    keys[j] = key;
+    ids[j] = id;
+}
+
+/*
+ * Brute-force search.  out_d is float (what IndexFlat returns), out_d64 (may be
+ * NULL) keeps the double scores for tolerance checks.
+ * k > nb: tail padded with (+INF,-1) for L2, (-INF,-1) for IP
+ * (src/MetalIndexFlat.mm:387-399).  nb == 0 or nq == 0: everything padded
+ * (src/MetalIndexFlat.mm:328-334).
+ */
+int oracle_search(int metric, const float* xb, int64_t nb, const float* xq, int64_t nq,
+                  int d, int64_t k, float* out_d, int64_t* out_i, double* out_d64) {
+    if (k <= 0 || d <= 0 || nq < 0 || nb < 0) return 1;
+    const double pad = (metric == ORACLE_METRIC_L2) ? INFINITY : -INFINITY;
+#pragma omp parallel
+    {
+        double* keys = (double*)malloc(sizeof(double) * (size_t)k);
+        int64_t* ids = (int64_t*)malloc(sizeof(int64_t) * (size_t)k);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t i = 0; i < nq; i++) {
+            for (int64_t j = 0; j < k; j++) { keys[j] = INFINITY; ids[j] = -1; }
+            const float* q = xq + i * (int64_t)d;
+            for (int64_t r = 0; r < nb; r++) {
+                const float* x = xb + r * (int64_t)d;
+                double s = (metric == ORACLE_METRIC_L2) ? score_l2(q, x, d) : -score_ip(q, x, d);
+                if (s < keys[k - 1]) list_insert(keys, ids, k, s, r);
+            }
+            for (int64_t j = 0; j < k; j++) {
+                double v = (ids[j] < 0) ? pad : ((metric == ORACLE_METRIC_L2) ? keys[j] : -keys[j]);
+                out_d[i * k + j] = (float)v;
+                out_i[i * k + j] = ids[j];
+                if (out_d64) out_d64[i * k + j] = v;
+            }
+        }
+        free(keys);
+        free(ids);
+    }
+    return 0;
+}
+
+/* k-way merge of P per-shard sorted lists per query (host model of the
+ * multi-GPU exchange step): lists[p][q][k] hold (score, local id), base[p] is
+ * the shard's first global row.  Output is best-first with ties to lower
+ * global id; padded like oracle_search. */
+int oracle_merge(int metric, int P, int64_t nq, int64_t k, const float* dist,
+                 const int64_t* local_ids, const int64_t* base, float* out_d, int64_t* out_i) {
+    if (P <= 0 || k <= 0) return 1;
+    const float pad = (metric == ORACLE_METRIC_L2) ? INFINITY : -INFINITY;
+    for (int64_t q = 0; q < nq; q++) {
+        int64_t* pos = (int64_t*)calloc((size_t)P, sizeof(int64_t));
+        for (int64_t j = 0; j < k; j++) {
+            int best = -1;
+            double bkey = 0;
+            int64_t bid = 0;
+            for (int p = 0; p < P; p++) {
+                if (pos[p] >= k) continue;
+                int64_t off = ((int64_t)p * nq + q) * k + pos[p];
+                if (local_ids[off] < 0) continue;
+                double key = (metric == ORACLE_METRIC_L2) ? (double)dist[off] : -(double)dist[off];
+                int64_t gid = base[p] + local_ids[off];
+                if (best < 0 || key < bkey || (key == bkey && gid < bid)) {
+                    best = p; bkey = key; bid = gid;
+                }
+            }
+            if (best < 0) {
+                out_d[q * k + j] = pad;
+                out_i[q * k + j] = -1;
+            } else {
+                out_d[q * k + j] = (metric == ORACLE_METRIC_L2) ? (float)bkey : (float)-bkey;
+                out_i[q * k + j] = bid;
+                pos[best]++;
+            }
+        }
+        free(pos);
+    }
+    return 0;
+}
