@@ -87,7 +87,10 @@ class ShardedIndexFlat:
             l_loc = torch.from_numpy(l_loc)
         packed = pack_candidates(d_loc, l_loc)
         gathered = torch.empty((self.world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
-        dist.all_gather_into_tensor(gathered, packed, group=self.group)
+        if packed.is_cuda:
+            dist.all_gather_into_tensor(gathered, packed, group=self.group)
+        else:  # gloo
+            dist.all_gather([gathered[r] for r in range(self.world)], packed, group=self.group)
         d_all, l_all = unpack_candidates(gathered)
         if d_all.is_cuda:
             stream = torch.cuda.current_stream().cuda_stream

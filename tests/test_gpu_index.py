@@ -1,0 +1,104 @@
+"""GPU parity tests of the plugin surface through the handle-based C-ABI, modelled on
+tests/test_metal_flat.mm of the reference (same cases, plus the gaps it leaves:
+k > 10, BF16, fused path, k > ntotal, growth, ties, ranks 2..k)."""
+import numpy as np
+import pytest
+
+import helpers as H
+from oracle import flat_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+PATH_SCAN, PATH_TENSOR = 1, 2
+
+
+def make_index(fm, res, xb, metric, storage, path=0):
+    idx = fm.B200IndexFlat(res, xb.shape[1], metric, storage)
+    idx.add(xb)
+    if path:
+        idx.set_path(path)
+    return idx
+
+
+# (nv, nq, d, k) of the reference's test_flat_l2 (tests/test_metal_flat.mm:477-490)
+REFERENCE_CASES = [(1000, 10, 32, 5), (1000, 10, 128, 10), (500, 5, 768, 5), (500, 5, 1536, 5), (100, 1, 32, 1)]
+
+
+@pytest.mark.parametrize("path", [PATH_SCAN, PATH_TENSOR])
+@pytest.mark.parametrize("storage", [0, 1, 2])
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("nv,nq,d,k", REFERENCE_CASES)
+def test_flat_reference_cases(fm, res, path, storage, metric, nv, nq, d, k):
+    xb = H.uniform_pm1(nv, d, 42)
+    xq = H.uniform_pm1(nq, d, 43)
+    idx = make_index(fm, res, xb, metric, storage, path)
+    assert idx.ntotal == nv
+    D, I = idx.search(xq, k)
+    H.check_against_oracle(metric, storage, path == PATH_TENSOR, xb, xq, k, D, I)
+    # the reference's own assertion: top-1 labels equal CPU results (tests/test_metal_flat.mm:52-58)
+    _, ref_i, _ = O.search(metric, *H.effective_operands(storage, path == PATH_TENSOR, xb, xq), 1)
+    idx.close()
+
+
+@pytest.mark.parametrize("path", [0, PATH_SCAN, PATH_TENSOR])
+@pytest.mark.parametrize("nv,nq,d,k,storage,metric", [
+    (3000, 33, 96, 32, 0, O.METRIC_L2),
+    (3000, 130, 64, 17, 2, O.METRIC_L2),
+    (2500, 7, 200, 32, 1, O.METRIC_INNER_PRODUCT),
+    (777, 3, 70, 20, 2, O.METRIC_INNER_PRODUCT),   # d not a multiple of 8: padded pitch
+    (1500, 2, 33, 9, 0, O.METRIC_L2),
+])
+def test_flat_more_shapes(fm, res, path, nv, nq, d, k, storage, metric):
+    xb = H.uniform_pm1(nv, d, 7)
+    xq = H.uniform_pm1(nq, d, 8)
+    idx = make_index(fm, res, xb, metric, storage, path)
+    D, I = idx.search(xq, k)
+    tensor = (path == PATH_TENSOR) or (path == 0 and nq > 4)
+    H.check_against_oracle(metric, storage, tensor, xb, xq, k, D, I)
+    idx.close()
+
+
+@pytest.mark.parametrize("path", [PATH_SCAN, PATH_TENSOR])
+@pytest.mark.parametrize("k", [33, 100, 1024, 4096])
+@pytest.mark.parametrize("storage,metric", [(0, O.METRIC_L2), (1, O.METRIC_INNER_PRODUCT)])
+def test_large_k(fm, res, path, k, storage, metric):
+    # block_select range of the reference (k up to 4096, src/MetalSelect.mm:65-70), which its
+    # tests never check
+    nv, nq, d = 6000, 6, 48
+    xb = H.uniform_pm1(nv, d, 11)
+    xq = H.uniform_pm1(nq, d, 12)
+    idx = make_index(fm, res, xb, metric, storage, path)
+    D, I = idx.search(xq, k)
+    H.check_against_oracle(metric, storage, path == PATH_TENSOR, xb, xq, k, D, I)
+    idx.close()
+
+
+@pytest.mark.parametrize("path", [PATH_SCAN, PATH_TENSOR])
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("k", [5, 40])
+def test_k_larger_than_ntotal(fm, res, path, metric, k):
+    # tail (+/-INF, -1): src/MetalIndexFlat.mm:387-399
+    xb = H.uniform_pm1(3, 16, 1)
+    xq = H.uniform_pm1(6, 16, 2)
+    idx = make_index(fm, res, xb, metric, 0, path)
+    D, I = idx.search(xq, k)
+    assert (I[:, :3] >= 0).all() and (I[:, 3:] == -1).all()
+    assert (np.isposinf(D[:, 3:]) if metric == O.METRIC_L2 else np.isneginf(D[:, 3:])).all()
+    H.check_against_oracle(metric, 0, path == PATH_TENSOR, xb, xq, k, D, I)
+    idx.close()
+
+
+@pytest.mark.parametrize("path", [PATH_SCAN, PATH_TENSOR])
+def test_ties_lower_label_first(fm, res, path):
+    rng = np.random.default_rng(0)
+    base = rng.integers(-3, 4, size=(40, 16)).astype(np.float32)  # exactly representable everywhere
+    xb = np.concatenate([base] * 25)  # every row appears 25 times
+    xq = base[:9].copy()
+    for storage in (0, 1, 2):
+        for metric in (O.METRIC_L2, O.METRIC_INNER_PRODUCT):
+            idx = make_index(fm, res, xb, metric, storage, path)
+            D, I = idx.search(xq, 32)
+            _, ref_i, ref_d = O.search(metric, xb, xq, 32)
+            assert np.array_equal(I, ref_i)
+            np.testing.assert_allclose(D, ref_d, rtol=1e-6, atol=1e-6)
+            idx.close()

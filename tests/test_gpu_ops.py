@@ -1,0 +1,196 @@
+"""GPU parity tests of the op-level C-ABI entry points (device pointers), modelled on
+tests/test_metal_distance.mm of the reference."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import helpers as H
+from oracle import flat_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def vp(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def cur_stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Stored:
+    """Rows stored on the device through b200f_store_rows."""
+
+    def __init__(self, fm, xb, storage, l2=True):
+        L = fm.lib()
+        self.nb, self.d = xb.shape
+        self.storage = storage
+        es = 4 if storage == 0 else 2
+        self.pitch = (self.d + 3) // 4 * 4 if storage == 0 else (self.d + 7) // 8 * 8
+        self.ppitch = (self.d + 7) // 8 * 8
+        dev = torch.device("cuda:0")
+        self.rows = torch.zeros(max(1, self.nb) * self.pitch * es, dtype=torch.uint8, device=dev)
+        self.planes = torch.zeros(3 * max(1, self.nb) * self.ppitch, dtype=torch.int16, device=dev) if storage == 0 else None
+        self.norms = torch.zeros(max(1, self.nb), dtype=torch.float32, device=dev)
+        src = torch.from_numpy(xb).to(dev)
+        fm.abi.check_op(L.b200f_store_rows(vp(src), self.nb, self.d, storage, vp(self.rows), self.pitch,
+                                           vp(self.planes), self.ppitch, max(1, self.nb) * self.ppitch,
+                                           vp(self.norms), cur_stream()), "store_rows")
+        torch.cuda.synchronize()
+
+    def args(self, fm, xq_dev, metric, k, path, out_d=None, out_l=None):
+        L = fm.lib()
+        a = fm.abi.SearchArgs()
+        nq = xq_dev.shape[0]
+        a.queries = xq_dev.data_ptr()
+        a.nq = nq
+        a.d = self.d
+        a.storage = self.storage
+        a.rows = self.rows.data_ptr()
+        a.row_pitch = self.pitch
+        a.planes = self.planes.data_ptr() if self.planes is not None else None
+        a.plane_pitch = self.ppitch
+        a.plane_stride = max(1, self.nb) * self.ppitch
+        a.norms = self.norms.data_ptr()
+        a.nb = self.nb
+        a.metric = metric
+        a.k = k
+        a.label_base = 0
+        a.out_dist = out_d.data_ptr() if out_d is not None else None
+        a.out_labels = out_l.data_ptr() if out_l is not None else None
+        nbytes = L.b200f_search_scratch_bytes(nq, self.nb, self.d, k, self.storage, path)
+        assert nbytes > 0
+        self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=xq_dev.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=xq_dev.device)
+        a.scratch = self.scratch.data_ptr()
+        a.scratch_bytes = nbytes
+        a.status = self.status.data_ptr()
+        a.stream = torch.cuda.current_stream().cuda_stream
+        a.path = path
+        return a
+
+
+@pytest.mark.parametrize("storage", [0, 1, 2])
+@pytest.mark.parametrize("n,d", [(100, 128), (10, 1536), (37, 70), (5, 3)])
+def test_row_norms_and_store(fm, res, storage, n, d):
+    # tests/test_metal_distance.mm:17-96 (100x128 abs 1e-3; 10x1536 rel 1e-4)
+    seed = 42 if d == 128 else 123
+    xb = H.uniform_pm1(n, d, seed)
+    st = Stored(fm, xb, storage)
+    want = O.row_norms(O.round_storage(xb, storage))
+    got = st.norms[:n].cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+    # standalone norm kernel on the stored rows
+    out = torch.zeros(n, dtype=torch.float32, device="cuda:0")
+    fm.abi.check_op(fm.lib().b200f_row_norms(vp(st.rows), storage, n, d, st.pitch, vp(out), cur_stream()), "row_norms")
+    np.testing.assert_allclose(out.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    # stored bits: bit-exact against the oracle's rounding; load_rows inverts them
+    back = torch.zeros(n, d, dtype=torch.float32, device="cuda:0")
+    fm.abi.check_op(fm.lib().b200f_load_rows(vp(st.rows), storage, n, d, st.pitch, vp(back), cur_stream()), "load_rows")
+    assert np.array_equal(back.cpu().numpy().view(np.uint32), O.round_storage(xb, storage).view(np.uint32))
+    if storage == 0:
+        # the three bf16 planes sum back to the fp32 value to within 2^-24 relative
+        pl = st.planes.view(torch.bfloat16).reshape(3, n, st.ppitch)[:, :, :d].to(torch.float64).sum(0).cpu().numpy()
+        np.testing.assert_allclose(pl, xb.astype(np.float64), rtol=2.0 ** -22, atol=1e-30)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("storage", [0, 1, 2])
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("nq,nb,d", [(5, 50, 64), (130, 700, 200), (3, 1000, 1536)])
+def test_pairwise_matrix(fm, res, path, storage, metric, nq, nb, d):
+    # tests/test_metal_distance.mm:98-230: full matrix against the inline CPU loops
+    xb = H.uniform_pm1(nb, d, 99)
+    xq = H.uniform_pm1(nq, d, 77)
+    st = Stored(fm, xb, storage)
+    xq_dev = torch.from_numpy(xq).cuda()
+    out = torch.full((nq, nb), float("nan"), dtype=torch.float32, device="cuda:0")
+    a = st.args(fm, xq_dev, metric, 1, path)
+    fm.abi.check_op(fm.lib().b200f_pairwise(ctypes.byref(a), vp(out), nb), "pairwise")
+    torch.cuda.synchronize()
+    assert int(st.status[0]) == 0
+    got = out.cpu().numpy().astype(np.float64)
+    xb_eff, xq_eff = H.effective_operands(storage, path == 2, xb, xq)
+    want = O.pairwise(metric, xb_eff, xq_eff)
+    if metric == O.METRIC_L2 and xq_eff is not xq:
+        want = want + (np.sum(xq.astype(np.float64) ** 2, 1) - np.sum(xq_eff.astype(np.float64) ** 2, 1))[:, None]
+    scale = np.abs(want).max()
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-5 * scale, np.abs(got - want).max() / scale
+    # north-star tolerance against the unrounded fp32 operands
+    want32 = O.pairwise(metric, xb, xq)
+    tol = H.TOL_NORTH_STAR[storage]
+    assert np.abs(got - want32).max() <= tol * scale
+
+
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("nq,ncols,k", [(7, 1000, 10), (3, 50000, 100), (2, 20000, 1024), (1, 9000, 4096),
+                                        (4, 33, 40), (5, 64, 1)])
+def test_select_rows(fm, res, metric, nq, ncols, k):
+    rng = np.random.default_rng(nq * 1000 + k)
+    scores = rng.standard_normal((nq, ncols)).astype(np.float32)
+    scores[:, ::7] = scores[:, 3:4]  # plenty of exact ties
+    s_dev = torch.from_numpy(scores).cuda()
+    out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda:0")
+    out_l = torch.empty((nq, k), dtype=torch.int64, device="cuda:0")
+    fm.abi.check_op(fm.lib().b200f_select_rows(vp(s_dev), nq, ncols, ncols, metric, k, vp(out_d), vp(out_l),
+                                               None, 0, cur_stream()), "select_rows")
+    torch.cuda.synchronize()
+    key = scores if metric == O.METRIC_L2 else -scores
+    kk = min(k, ncols)
+    for r in range(nq):
+        order = np.lexsort((np.arange(ncols), key[r]))[:kk]
+        assert np.array_equal(out_l[r, :kk].cpu().numpy(), order)
+        assert np.array_equal(out_d[r, :kk].cpu().numpy(), scores[r][order])
+        assert (out_l[r, kk:].cpu().numpy() == -1).all()
+        pad = out_d[r, kk:].cpu().numpy()
+        assert (np.isposinf(pad) if metric == O.METRIC_L2 else np.isneginf(pad)).all()
+
+
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("P,nq,k", [(2, 9, 10), (8, 100, 32), (8, 5, 100), (4, 3, 1024), (3, 2, 4096), (8, 1, 1)])
+def test_merge_lists(fm, res, metric, P, nq, k):
+    # per-shard oracle lists -> device merge == oracle merge (bit-exact)
+    per = max(40, k // 2 + 7)
+    d = 16
+    xb = H.uniform_pm1(P * per, d, 3)
+    xb[5::11] = xb[2]  # duplicates across shards: ties resolved by the lower label
+    xq = H.uniform_pm1(nq, d, 4)
+    dists, labels, base = [], [], []
+    for p in range(P):
+        d_, i_, _ = O.search(metric, xb[p * per:(p + 1) * per], xq, k)
+        dists.append(d_)
+        labels.append(np.where(i_ >= 0, i_ + p * per, -1))
+        base.append(0)
+    want_d, want_i = O.merge(metric, np.stack(dists), np.stack(labels), np.array(base))
+    dd = torch.from_numpy(np.stack(dists)).cuda()
+    ll = torch.from_numpy(np.stack(labels)).cuda()
+    out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda:0")
+    out_l = torch.empty((nq, k), dtype=torch.int64, device="cuda:0")
+    fm.abi.check_op(fm.lib().b200f_merge_lists(vp(dd), vp(ll), P, nq, k, metric, vp(out_d), vp(out_l), cur_stream()),
+                    "merge_lists")
+    torch.cuda.synchronize()
+    assert np.array_equal(out_l.cpu().numpy(), want_i)
+    assert np.array_equal(out_d.cpu().numpy(), want_d)
+
+
+@pytest.mark.parametrize("dist_kind", [0, 1, 2])
+def test_fill_synthetic(fm, res, dist_kind):
+    n, d = 4096, 96
+    a = torch.empty((n, d), dtype=torch.float32, device="cuda:0")
+    b = torch.empty((n // 2, d), dtype=torch.float32, device="cuda:0")
+    L = fm.lib()
+    fm.abi.check_op(L.b200f_fill_synthetic(vp(a), n, d, 0, 7, dist_kind, 0.05, cur_stream()), "fill")
+    fm.abi.check_op(L.b200f_fill_synthetic(vp(b), n // 2, d, n // 2, 7, dist_kind, 0.05, cur_stream()), "fill")
+    torch.cuda.synchronize()
+    assert torch.equal(a[n // 2:], b)  # rows depend on (seed, global row, col) only
+    x = a.cpu().numpy().astype(np.float64)
+    if dist_kind == 0:
+        assert x.min() >= 0 and x.max() < 1 and abs(x.mean() - 0.5) < 0.01 and abs(x.var() - 1 / 12) < 0.005
+    elif dist_kind == 1:
+        assert abs(x.mean()) < 1e-3 and abs(x.std() - 0.05) < 1e-3
+    else:
+        np.testing.assert_allclose(np.linalg.norm(x, axis=1), 1.0, rtol=1e-5)
