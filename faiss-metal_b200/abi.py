@@ -64,6 +64,8 @@ SIGNATURES = {
     "b200f_select_rows": (c_int, [c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "b200f_merge_lists": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "b200f_fill_synthetic": (c_int, [c_vp, c_i64, c_int, c_i64, ctypes.c_uint64, c_int, ctypes.c_float, c_vp]),
+    "b200f_profile_enable": (c_int, [c_int]),
+    "b200f_profile_read": (c_int, [ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(ctypes.c_double), c_int]),
     "b200f_last_error": (ctypes.c_char_p, []),
     "b200f_resources_create": (c_int, [c_int, ctypes.POINTER(c_vp)]),
     "b200f_resources_destroy": (None, [c_vp]),

@@ -117,4 +117,11 @@ int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t 
 
 int cached_sm_count();
 
+// Profiling (off by default): counts kernel launches of this library and, when enabled,
+// brackets every launch of the dominant distance kernel (tensor GEMM or scan) with CUDA
+// events on the launching stream.
+void count_launch(int n = 1);
+void main_kernel_begin(cudaStream_t stream);
+void main_kernel_end(cudaStream_t stream);
+
 }  // namespace b200f

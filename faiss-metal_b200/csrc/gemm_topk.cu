@@ -564,7 +564,10 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set = true;
     }
+    main_kernel_begin(stream);
     gemm_topk_kernel<<<plan.grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+    main_kernel_end(stream);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }

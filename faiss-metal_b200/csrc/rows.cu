@@ -281,6 +281,7 @@ int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint1
     if (nq <= 0) return B200F_OK;
     prepare_queries_kernel<<<grid_for_rows(nq), ROW_THREADS, 0, stream>>>(
             q, nq, d, storage, a_planes, a_pitch, a_plane_stride, qnorm);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -308,6 +309,7 @@ extern "C" int b200f_row_norms(const void* rows, int storage, int64_t n, int d, 
         default:
             return B200F_ERR_BAD_ARG;
     }
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -336,6 +338,7 @@ extern "C" int b200f_store_rows(const float* src, int64_t n, int d, int storage,
         default:
             return B200F_ERR_BAD_ARG;
     }
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -362,6 +365,7 @@ extern "C" int b200f_load_rows(const void* rows, int storage, int64_t n, int d, 
         default:
             return B200F_ERR_BAD_ARG;
     }
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -372,6 +376,7 @@ extern "C" int b200f_fill_synthetic(float* dst, int64_t n, int d, int64_t row0, 
     if (n == 0) return B200F_OK;
     fill_synthetic_kernel<<<grid_for_rows(n), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
             dst, n, d, row0, seed, dist, scale);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }

@@ -290,7 +290,10 @@ int launch_nq(const ScanParams& p, int grid, size_t smem, cudaStream_t stream) {
             B200F_CUDA_TRY(cudaFuncSetAttribute(scan_kernel<STORAGE, NQ, STORE>,                 \
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                                 (int)smem));                                     \
+        main_kernel_begin(stream);                                                               \
         scan_kernel<STORAGE, NQ, STORE><<<grid, SCAN_THREADS, smem, stream>>>(p);                \
+        main_kernel_end(stream);                                                                 \
+        count_launch();                                                                          \
     }
     if (p.nq == 1) B200F_SCAN_CASE(1)
     else if (p.nq == 2) B200F_SCAN_CASE(2)

@@ -9,6 +9,9 @@
 //   k   > 32           distance keys written per column chunk, running sort-select
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 
@@ -20,6 +23,17 @@ constexpr int64_t MATRIX_BUDGET_BYTES = 512ll << 20;
 constexpr int SCAN_GROUP = 4;
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct ProfileState {
+    bool enabled = false;
+    long long launches = 0;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;  // recorded, not yet read
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pool;
+    long long main_launches = 0;
+    double main_ms = 0.0;
+};
+ProfileState g_prof;
+std::mutex g_prof_mu;
 
 struct SearchPlan {
     int path;         // B200F_PATH_SCAN or B200F_PATH_TENSOR
@@ -164,9 +178,69 @@ int fill_operands(const B200FSearchArgs& a, const SearchPlan& pl, uint8_t* scrat
 
 }  // namespace
 
+void count_launch(int n) {
+    std::lock_guard<std::mutex> g(g_prof_mu);
+    g_prof.launches += n;
+}
+
+void main_kernel_begin(cudaStream_t stream) {
+    std::lock_guard<std::mutex> g(g_prof_mu);
+    if (!g_prof.enabled) return;
+    std::pair<cudaEvent_t, cudaEvent_t> ev;
+    if (!g_prof.pool.empty()) {
+        ev = g_prof.pool.back();
+        g_prof.pool.pop_back();
+    } else {
+        if (cudaEventCreate(&ev.first) != cudaSuccess || cudaEventCreate(&ev.second) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return;
+        }
+    }
+    cudaEventRecord(ev.first, stream);
+    g_prof.pending.push_back(ev);
+}
+
+void main_kernel_end(cudaStream_t stream) {
+    std::lock_guard<std::mutex> g(g_prof_mu);
+    if (!g_prof.enabled || g_prof.pending.empty()) return;
+    cudaEventRecord(g_prof.pending.back().second, stream);
+}
+
 }  // namespace b200f
 
 using namespace b200f;
+
+extern "C" int b200f_profile_enable(int on) {
+    std::lock_guard<std::mutex> g(g_prof_mu);
+    g_prof.enabled = on != 0;
+    return B200F_OK;
+}
+
+extern "C" int b200f_profile_read(int64_t* launches, int64_t* main_launches, double* main_ms,
+                                  int reset) {
+    std::lock_guard<std::mutex> g(g_prof_mu);
+    for (auto& ev : g_prof.pending) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(ev.second) == cudaSuccess &&
+            cudaEventElapsedTime(&ms, ev.first, ev.second) == cudaSuccess) {
+            g_prof.main_ms += ms;
+            g_prof.main_launches++;
+        } else {
+            (void)cudaGetLastError();
+        }
+        g_prof.pool.push_back(ev);
+    }
+    g_prof.pending.clear();
+    if (launches) *launches = g_prof.launches;
+    if (main_launches) *main_launches = g_prof.main_launches;
+    if (main_ms) *main_ms = g_prof.main_ms;
+    if (reset) {
+        g_prof.launches = 0;
+        g_prof.main_launches = 0;
+        g_prof.main_ms = 0.0;
+    }
+    return B200F_OK;
+}
 
 extern "C" const char* b200f_status_string(int status) {
     switch (status) {
@@ -244,6 +318,7 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         const int64_t n = a->nq * a->k;
         fill_pad_kernel<<<(int)(ceil_div64(n, 256) < 1024 ? ceil_div64(n, 256) : 1024), 256, 0, st>>>(
                 a->out_dist, a->out_labels, n, l2 ? kHostInf : -kHostInf);
+        count_launch();
         B200F_LAUNCH_CHECK();
         return B200F_OK;
     }
@@ -364,6 +439,7 @@ extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64
     if (g > (int64_t)sm * 16) g = (int64_t)sm * 16;
     finish_matrix_kernel<<<(int)g, 256, 0, st>>>(out_matrix, a->nq, a->nb, ld_out, l2 ? 1.f : -1.f,
                                                  l2 ? qnorm : nullptr);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }

@@ -343,6 +343,7 @@ int launch_sort_select(const SortSelectParams& p, cudaStream_t stream) {
     const int64_t cap = (int64_t)cached_sm_count() * 2 * 8;
     if (g > cap) g = cap;
     sort_select_kernel<SRC><<<(int)g, SS_THREADS, smem, stream>>>(p);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -397,6 +398,7 @@ int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P,
     const int64_t cap = (int64_t)cached_sm_count() * 32;
     if (g > cap) g = cap;
     merge_small_kernel<int32_t><<<(int)g, MS_THREADS, 0, stream>>>(p);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -432,6 +434,7 @@ int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t 
                                                       l2 ? qnorm : nullptr, l2 ? 1 : 0,
                                                       l2 ? kHostInf : -kHostInf, label_base,
                                                       out_dist, out_labels);
+    count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
@@ -508,6 +511,7 @@ extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P
         const int64_t cap = (int64_t)cached_sm_count() * 32;
         if (g > cap) g = cap;
         merge_small_kernel<int64_t><<<(int)g, MS_THREADS, 0, st>>>(p);
+        count_launch();
         B200F_LAUNCH_CHECK();
         return B200F_OK;
     }

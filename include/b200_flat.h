@@ -186,6 +186,15 @@ int b200f_merge_lists(const float* dist, const int64_t* labels, int P, int64_t n
 int b200f_fill_synthetic(float* dst, int64_t n, int d, int64_t row0, uint64_t seed, int dist,
                          float scale, void* stream);
 
+/* Profiling, off by default.  While enabled every launch of the dominant distance
+ * kernel (tensor GEMM or streaming scan) is bracketed by CUDA events on its stream.
+ * b200f_profile_read waits for the recorded events and returns the totals since the
+ * last reset: kernels launched by this library, launches of the dominant kernel and
+ * their summed duration in milliseconds.  The reference measures with wall clocks
+ * around search() only (tests/bench_metal_flat.mm:43-54); it has no counterpart. */
+int b200f_profile_enable(int on);
+int b200f_profile_read(int64_t* launches, int64_t* main_launches, double* main_ms, int reset);
+
 /* ---- index entry points (mirror of faiss_metal::MetalIndexFlat) ---------- */
 
 typedef struct B200FResources B200FResources; /* StandardMetalResources (include/faiss-metal/StandardMetalResources.h:9-32) */

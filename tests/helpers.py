@@ -64,7 +64,9 @@ def check_against_oracle(metric, storage, tensor_path, xb, xq, k, got_d, got_i, 
     if loose:
         _, ref_i, ref_d = O.search(metric, xb, xq, k)
         true_d = O.rescore(metric, xb, xq, got_i)
-        eps = 1e-2 * float(np.nanmax(np.abs(ref_d[np.isfinite(ref_d)]))) if np.isfinite(ref_d).any() else 1e-6
+        # relative error is meaningless for scores that cross zero (inner product, large k):
+        # the denominator is floored at 10 % of the largest score of the result
+        eps = 1e-1 * float(np.nanmax(np.abs(ref_d[np.isfinite(ref_d)]))) if np.isfinite(ref_d).any() else 1e-6
         r = O.compare_results(metric, got_d, got_i, ref_d, ref_i, true_d, TOL_NORTH_STAR[storage], eps=max(eps, 1e-6))
         out["loose"] = r
         assert O.passed(r), ("loose", r)
