@@ -206,3 +206,233 @@ def run_reference(args, w, rank, world):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+# B200 arm
+# ---------------------------------------------------------------------------------------
+def build_shard(fm, torch, res, w, lo, hi, seed):
+    """Generates rows [lo, hi) of the synthetic database on the device and adds them."""
+    import ctypes
+    idx = fm.B200IndexFlat(res, w["d"], w["metric"], w["storage"])
+    n = hi - lo
+    idx.reserve(max(n, 1))
+    chunk = max(1, min(n, (256 << 20) // (w["d"] * 4)))
+    buf = torch.empty((chunk, w["d"]), dtype=torch.float32, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for r0 in range(0, n, chunk):
+        nr = min(chunk, n - r0)
+        fm.abi.check_op(fm.lib().b200f_fill_synthetic(ctypes.c_void_p(buf.data_ptr()), nr, w["d"], lo + r0, seed,
+                                                      w["dist"], w["scale"], stream), "fill_synthetic")
+        torch.cuda.current_stream().synchronize()
+        idx.add(buf[:nr])
+    idx.set_label_base(lo)
+    del buf
+    return idx
+
+
+def spot_check(fm, torch, w, index_local, lo, hi, xq_host, D, I, nsample=8):
+    """Outside the timed region: exact re-score (float64, from the stored rows) of the labels
+    returned for a few queries that fall in this rank's shard, order and tolerance check."""
+    import numpy as np
+    worst = 0.0
+    checked = 0
+    for qi in range(min(nsample, xq_host.shape[0])):
+        prev = None
+        for j in range(I.shape[1]):
+            lab = int(I[qi, j])
+            if lab < 0:
+                continue
+            dist = float(D[qi, j])
+            if prev is not None:
+                assert (dist >= prev - 1e-5 * abs(prev)) if w["metric"] == 1 else (dist <= prev + 1e-5 * abs(prev)), \
+                    "results are not best-first"
+            prev = dist
+            if not (lo <= lab < hi):
+                continue
+            row = index_local.reconstruct(lab - lo).astype(np.float64)
+            q = xq_host[qi].astype(np.float64)
+            exact = float(((q - row) ** 2).sum()) if w["metric"] == 1 else float((q * row).sum())
+            err = abs(exact - dist) / max(abs(exact), 1e-6)
+            worst = max(worst, err)
+            checked += 1
+    tol = 1e-4 if w["storage"] == 0 else 2e-2
+    assert worst <= tol, "distance error %g above tolerance %g" % (worst, tol)
+    return {"pairs_rescored": checked, "max_rel_dist_err": worst, "tolerance": tol}
+
+
+def run_b200(args, w, rank, world, local_rank):
+    import ctypes
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import faiss_metal_b200 as fm
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = load_peaks()
+    res = fm.StandardB200Resources(local_rank)
+    ext = torch.cuda.ExternalStream(res.stream, device=torch.device("cuda", local_rank))
+    lo, hi = fm.shard_range(w["nb"], rank, world)
+    L = fm.lib()
+
+    with torch.cuda.stream(ext):
+        index = build_shard(fm, torch, res, w, lo, hi, seed=1)
+        sharded = fm.ShardedIndexFlat(index, rank, world)
+        nq, d, k = w["nq"], w["d"], w["k"]
+        xq_dev = torch.empty((nq, d), dtype=torch.float32, device="cuda")
+        fm.abi.check_op(L.b200f_fill_synthetic(ctypes.c_void_p(xq_dev.data_ptr()), nq, d, 0, 2, w["dist"], w["scale"],
+                                               ctypes.c_void_p(ext.cuda_stream)), "fill queries")
+        ext.synchronize()
+        xq_pin = torch.empty((nq, d), dtype=torch.float32, pin_memory=True)
+        xq_pin.copy_(xq_dev)
+        d_pin = torch.empty((nq, k), dtype=torch.float32, pin_memory=True)
+        l_pin = torch.empty((nq, k), dtype=torch.int64, pin_memory=True)
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def step_device():
+            return sharded.search(xq_dev, k)
+
+        def step_e2e():
+            # public API with HOST buffers: H2D of the queries and D2H of the results inside
+            if world == 1:
+                index.search(xq_pin.numpy(), k, d_pin.numpy(), l_pin.numpy())
+            else:
+                dd, ll = sharded.search(xq_dev.copy_(xq_pin, non_blocking=True), k)
+                d_pin.copy_(dd, non_blocking=True)
+                l_pin.copy_(ll, non_blocking=True)
+                ext.synchronize()
+
+        # ---- device-resident timing ------------------------------------------------------
+        for _ in range(max(args.warmup, 3)):
+            step_device()
+        barrier()
+        L.b200f_profile_enable(1)
+        L.b200f_profile_read(None, None, None, 1)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev1 = torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record(ext)
+        for _ in range(args.steps):
+            D_dev, I_dev = step_device()
+        ev1.record(ext)
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        ms_total = ev0.elapsed_time(ev1)
+        launches = ctypes.c_int64(0)
+        main_launches = ctypes.c_int64(0)
+        main_ms = ctypes.c_double(0.0)
+        L.b200f_profile_read(ctypes.byref(launches), ctypes.byref(main_launches), ctypes.byref(main_ms), 1)
+        L.b200f_profile_enable(0)
+        t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item()) / args.steps
+
+        # ---- end-to-end timing -------------------------------------------------------------
+        e2e = None
+        if not args.no_e2e:
+            for _ in range(2):
+                step_e2e()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                step_e2e()
+            barrier()
+            dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            e2e_s = float(dt.item()) / args.steps
+            e2e = {"value": nq / e2e_s, "unit": "queries/s", "ms_per_step": e2e_s * 1e3,
+                   "h2d_bytes_per_step": world * nq * d * 4, "d2h_bytes_per_step": world * nq * k * 12}
+
+        # ---- checks outside the timed region ---------------------------------------------
+        D_host = D_dev.cpu().numpy()
+        I_host = I_dev.cpu().numpy()
+        check = spot_check(fm, torch, w, index, lo, hi, xq_pin.numpy(), D_host, I_host)
+        if not args.no_e2e:
+            assert np.array_equal(l_pin.numpy(), I_host), "end-to-end labels differ from device-resident labels"
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    nb_local = hi - lo
+    flops_per_launch = 2.0 * nq * nb_local * d
+    bytes_per_launch = nb_local * d * ELEM_BYTES[w["storage"]] + nq * d * 4 + nq * k * 12
+    n_main = max(1, main_launches.value)
+    main_avg_ms = main_ms.value / n_main
+    tensor_bound = nq > 64
+    if tensor_bound:
+        achieved = flops_per_launch / (main_avg_ms * 1e-3) / 1e12 if main_avg_ms > 0 else 0.0
+        peak = peaks["bf16_tflops_sustained"] if ms_step * args.steps > 1000 else peaks["bf16_tflops"]
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak, "traffic": None, "kernel": "gemm_topk_kernel",
+                    "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
+                    "peak_source": peaks["source"] + (" sustained" if peak == peaks["bf16_tflops_sustained"] else " burst"),
+                    "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
+                    "frac_of_nominal_2250": achieved / 2250.0}
+    else:
+        achieved = bytes_per_launch / (main_avg_ms * 1e-3) / 1e9 if main_avg_ms > 0 else 0.0
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "scan_kernel",
+                    "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
+                    "peak_source": peaks["source"], "frac_of_nominal_8000": achieved / 8000.0}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        qps_c, ms_c, cores, sample = cpu_time_steps(w, 3, 1)
+        cpu = {"value": qps_c, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample}
+
+    line = {
+        "metric": "QPS (flat kNN %s)" % w["desc"],
+        "value": nq / (ms_step * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": DTYPE_NAME[w["storage"]].split(" ")[0], "data": "synthetic",
+        "config": {"workload": args.workload, "desc": w["desc"], "nb": w["nb"], "nq": nq, "d": d, "k": k,
+                   "rows_per_gpu": nb_local, "parallelism": "row-sharded x%d, NCCL all-gather + k-way merge" % world,
+                   "l2_policy": "inputs larger than L2 (database shard %.1f GB streams every step)"
+                                % (nb_local * d * ELEM_BYTES[w["storage"]] / 1e9),
+                   "seeds": {"database": 1, "queries": 2},
+                   "headline": not (args.nb or args.nq)},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches.value),
+        "clocks": clocks, "check": check,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.nb:
+        w["nb"] = args.nb
+    if args.nq:
+        w["nq"] = args.nq
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("--gpus %d needs one process per GPU: launch with "
+                             "python -m torch.distributed.run --nproc-per-node %d bench.py ..." % (args.gpus, args.gpus))
+    run_b200(args, w, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -93,5 +93,22 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_contract_test() -> str:
+    """C++ test binary of the plugin classes (tests/cpp/contract_test.cpp), linked against
+    the in-tree library with a relative rpath so it runs wherever the tree is copied."""
+    src = os.path.join(REPO, "tests", "cpp", "contract_test.cpp")
+    out_dir = os.path.join(REPO, "tests", "_build")
+    out = os.path.join(out_dir, "contract_test")
+    os.makedirs(out_dir, exist_ok=True)
+    if _newer(out, [src, LIB_PATH]):
+        incs = []
+        for d in include_dirs():
+            incs += ["-I", d]
+        _run([HOST_CXX, "-O1", "-std=c++17", "-Wall", *incs, src, "-o", out, "-L", LIB_DIR, "-lb200flat",
+              "-Wl,-rpath,$ORIGIN/../../faiss-metal_b200/lib"])
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_contract_test())
