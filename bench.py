@@ -311,24 +311,25 @@ def run_b200(args, w, rank, world, local_rank):
                 ext.synchronize()
 
         # ---- device-resident timing ------------------------------------------------------
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()  # started before the warm-up so that its own start-up is not timed
         for _ in range(max(args.warmup, 3)):
             step_device()
         barrier()
         L.b200f_profile_enable(1)
         L.b200f_profile_read(None, None, None, 1)
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
-        ev0 = torch.cuda.Event(enable_timing=True)
-        ev1 = torch.cuda.Event(enable_timing=True)
+        sampler.lines.clear()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         barrier()
-        ev0.record(ext)
-        for _ in range(args.steps):
+        evs[0].record(ext)
+        for i in range(args.steps):
             D_dev, I_dev = step_device()
-        ev1.record(ext)
+            evs[i + 1].record(ext)
         barrier()
         clocks = sampler.stop() if rank == 0 else None
-        ms_total = ev0.elapsed_time(ev1)
+        ms_total = evs[0].elapsed_time(evs[-1])
+        step_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
         launches = ctypes.c_int64(0)
         main_launches = ctypes.c_int64(0)
         main_ms = ctypes.c_double(0.0)
@@ -407,7 +408,7 @@ def run_b200(args, w, rank, world, local_rank):
                    "seeds": {"database": 1, "queries": 2},
                    "headline": not (args.nb or args.nq)},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches.value),
-        "clocks": clocks, "check": check,
+        "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
     }
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -94,7 +94,7 @@ struct GemmOperands {
 // Fused top-k (k <= 32): partial lists part_key/part_idx [nq][P][k].
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
                      float alpha, const float* bias, int k, float* part_key, int32_t* part_idx,
-                     int32_t* status, cudaStream_t stream);
+                     uint32_t* gthr, int32_t* status, cudaStream_t stream);
 // Store mode: out[row*ld + (col-col0)] = sign*(alpha*dot + bias[col]) + rowadd[row].
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
                       float alpha, const float* bias, float sign, const float* rowadd, float* out,

@@ -82,6 +82,7 @@ struct GemmParams {
     const float* rowadd; // per query row, may be null (0)
     float* part_key;
     int32_t* part_idx;
+    uint32_t* gthr;      // per query row: ordered-float upper bound of the k-th best key so far
     float* out;
     int64_t ld;
     int32_t* status;
@@ -203,21 +204,68 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     return desc;
 }
 
-// Sorted insertion into the thread's own row list (column `row` of lkey/lidx).
-// Precondition: s < current k-th key.  Equal keys keep arrival order (ids ascend).
-__device__ __noinline__ float list_insert(float* lkey, int32_t* lidx, int row, int k, float s,
-                                          int32_t id) {
-    int j = k - 1;
-    while (j > 0) {
-        float prev = lkey[(j - 1) * BM + row];
-        if (!(prev > s)) break;
-        lkey[j * BM + row] = prev;
-        lidx[j * BM + row] = lidx[(j - 1) * BM + row];
-        j--;
+// Per-row candidate list in shared memory (column `row` of lkey/lidx), UNSORTED: the
+// thread keeps the position of its worst entry and overwrites it, then rescans the k
+// entries for the new worst (independent loads, no dependent chain).  "Worst" is the
+// lexicographic maximum of (key, id).  Returns the new worst key; `worst` is updated.
+// Precondition: s < key at `worst` (ids arrive ascending, so an equal key never enters).
+__device__ __noinline__ float list_replace_worst(float* lkey, int32_t* lidx, int row, int k,
+                                                 float s, int32_t id, int& worst) {
+    lkey[worst * BM + row] = s;
+    lidx[worst * BM + row] = id;
+    float mk = lkey[row];
+    int mp = 0;
+    int32_t mi = 0;
+    bool mi_valid = false;
+#pragma unroll 8
+    for (int j = 1; j < k; j++) {
+        const float key = lkey[j * BM + row];
+        if (key > mk) {
+            mk = key;
+            mp = j;
+            mi_valid = false;
+        } else if (key == mk) {
+            if (!mi_valid) {
+                mi = lidx[mp * BM + row];
+                mi_valid = true;
+            }
+            const int32_t ci = lidx[j * BM + row];
+            if ((uint32_t)ci > (uint32_t)mi) {  // empty slots (-1) count as the worst
+                mi = ci;
+                mp = j;
+            }
+        }
     }
-    lkey[j * BM + row] = s;
-    lidx[j * BM + row] = id;
-    return lkey[(k - 1) * BM + row];
+    worst = mp;
+    return mk;
+}
+
+// Writes the row list best-first: k rounds of "extract the lexicographic minimum".
+__device__ __noinline__ void list_write_sorted(float* lkey, int32_t* lidx, int row, int k,
+                                               float* out_key, int32_t* out_idx) {
+    for (int r = 0; r < k; r++) {
+        float bk = lkey[row];
+        int32_t bi = lidx[row];
+        int bp = 0;
+        for (int j = 1; j < k; j++) {
+            const float key = lkey[j * BM + row];
+            if (key < bk) {
+                bk = key;
+                bi = lidx[j * BM + row];
+                bp = j;
+            } else if (key == bk) {
+                const int32_t ci = lidx[j * BM + row];
+                if ((uint32_t)ci < (uint32_t)bi) {
+                    bi = ci;
+                    bp = j;
+                }
+            }
+        }
+        out_key[r] = bk;
+        out_idx[r] = bi;
+        lkey[bp * BM + row] = CUDART_INF_F;  // consumed
+        lidx[bp * BM + row] = -1;
+    }
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -378,7 +426,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
             const int64_t grow = (int64_t)qb * BM + row;
             const bool row_live = grow < p.nq;
-            float thr = CUDART_INF_F;
+            float thr = CUDART_INF_F;      // worst key of this thread's list (k-th best of the range)
+            float thr_eff = CUDART_INF_F;  // filter: min(thr, bound shared by all ranges of the row)
+            float thr_pub = CUDART_INF_F;  // last value published to gthr
+            int worst = 0;
             float radd = 0.f;
             if (p.mode == MODE_TOPK) {
                 for (int j = 0; j < k; j++) {
@@ -414,6 +465,18 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
                 tc_fence_after();
+                if (p.mode == MODE_TOPK && row_live) {
+                    // Any range's k-th best key bounds the row's global k-th best from above:
+                    // publish ours, adopt the smallest seen.  A key equal to the bound may
+                    // still win a tie on the id, so the filter admits s <= bound.
+                    if (thr < thr_pub) {
+                        atomicMin(p.gthr + grow, float_to_ordered(thr));
+                        thr_pub = thr;
+                    }
+                    const uint32_t g = *reinterpret_cast<volatile uint32_t*>(p.gthr + grow);
+                    const float gnext = (g >= 0xff800000u) ? CUDART_INF_F : ordered_to_float(g + 1u);
+                    thr_eff = fminf(thr, gnext);
+                }
                 const float* bs = sbias + acc * BN;
                 const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN;
 #pragma unroll 1
@@ -427,15 +490,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         for (int c = 0; c < 32; c++) {
                             const float s = fmaf(p.alpha, __uint_as_float(r[c]), bs[ch * 32 + c]);
                             r[c] = __float_as_uint(s);
-                            hits |= (s < thr ? 1u : 0u) << c;
+                            hits |= (s < thr_eff ? 1u : 0u) << c;
                         }
                         if (hits != 0 && row_live) {
                             const int32_t id0 = (int32_t)(c_tile + ch * 32);
 #pragma unroll
                             for (int c = 0; c < 32; c++) {
                                 const float s = __uint_as_float(r[c]);
-                                if (((hits >> c) & 1u) && s < thr)
-                                    thr = list_insert(lkey, lidx, row, k, s, id0 + c);
+                                if (((hits >> c) & 1u) && s < thr_eff) {
+                                    thr = list_replace_worst(lkey, lidx, row, k, s, id0 + c, worst);
+                                    thr_eff = fminf(thr_eff, thr);
+                                }
                             }
                         }
                     } else {
@@ -460,12 +525,9 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (acc == 0) acc_phase ^= 1;
             }
             if (p.mode == MODE_TOPK && row_live && ok) {
-                float* ok_ = p.part_key + (grow * p.P + xr) * k;
-                int32_t* oi_ = p.part_idx + (grow * p.P + xr) * k;
-                for (int j = 0; j < k; j++) {
-                    ok_[j] = lkey[j * BM + row];
-                    oi_[j] = lidx[j * BM + row];
-                }
+                if (thr < thr_pub) atomicMin(p.gthr + grow, float_to_ordered(thr));
+                list_write_sorted(lkey, lidx, row, k, p.part_key + (grow * p.P + xr) * k,
+                                  p.part_idx + (grow * p.P + xr) * k);
             }
         }
     }
@@ -608,8 +670,11 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
 
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
                      float alpha, const float* bias, int k, float* part_key, int32_t* part_idx,
-                     int32_t* status, cudaStream_t stream) {
+                     uint32_t* gthr, int32_t* status, cudaStream_t stream) {
     if (k <= 0 || k > KMAX) return B200F_ERR_UNSUPPORTED;
+    if (!gthr) return B200F_ERR_BAD_ARG;
+    // all-ones is above every ordered float: no bound yet
+    B200F_CUDA_TRY(cudaMemsetAsync(gthr, 0xff, (size_t)op.nq * sizeof(uint32_t), stream));
     GemmParams p{};
     p.mode = MODE_TOPK;
     p.k = k;
@@ -619,6 +684,7 @@ int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0,
     p.rowadd = nullptr;
     p.part_key = part_key;
     p.part_idx = part_idx;
+    p.gthr = gthr;
     p.out = nullptr;
     p.ld = 0;
     p.status = status;

@@ -44,7 +44,7 @@ struct SearchPlan {
     ScanPlan scan;
     int64_t chunk_cols;
     int64_t ngroups;  // scan path: query groups of SCAN_GROUP
-    size_t off_qnorm, off_a, off_part_key, off_part_idx, off_matrix, off_run_key, off_run_idx;
+    size_t off_qnorm, off_gthr, off_a, off_part_key, off_part_idx, off_matrix, off_run_key, off_run_idx;
     size_t total;
 };
 
@@ -62,6 +62,8 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     pl.ngroups = ceil_div64(nq, SCAN_GROUP);
     size_t off = 0;
     pl.off_qnorm = off;
+    off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+    pl.off_gthr = off;
     off += align256((size_t)(nq > 0 ? nq : 1) * 4);
     if (pl.path == B200F_PATH_TENSOR) {
         pl.off_a = off;
@@ -350,7 +352,7 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         if (pl.path == B200F_PATH_TENSOR) {
             P = pl.gemm.P;
             rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, alpha, bias, a->k, part_key, part_idx,
-                                  a->status, st);
+                                  reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
             P = pl.scan.grid;
