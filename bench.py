@@ -387,7 +387,7 @@ def run_b200(args, w, rank, world, local_rank):
     else:
         achieved = bytes_per_launch / (main_avg_ms * 1e-3) / 1e9 if main_avg_ms > 0 else 0.0
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "scan_kernel",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "scan_mma_kernel",
                     "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
                     "peak_source": peaks["source"], "frac_of_nominal_8000": achieved / 8000.0}
 

@@ -45,7 +45,7 @@ class SearchArgs(ctypes.Structure):
         ("norms", c_vp), ("nb", c_i64), ("metric", c_i32), ("k", c_i32),
         ("label_base", c_i64), ("out_dist", c_vp), ("out_labels", c_vp),
         ("scratch", c_vp), ("scratch_bytes", c_sz), ("status", c_vp), ("stream", c_vp),
-        ("path", c_i32), ("reserved", c_i32),
+        ("path", c_i32), ("norm_cols", c_i32),
     ]
 
 
@@ -55,7 +55,7 @@ SIGNATURES = {
     "b200f_device_count": (c_int, [ctypes.POINTER(c_int)]),
     "b200f_device_caps": (c_int, [c_int, ctypes.POINTER(Caps)]),
     "b200f_row_norms": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_vp]),
-    "b200f_store_rows": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_i64, c_vp, c_i64, c_i64, c_vp, c_vp]),
+    "b200f_store_rows": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_i64, c_vp, c_i64, c_i64, c_vp, c_int, c_vp]),
     "b200f_load_rows": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_vp]),
     "b200f_search_scratch_bytes": (c_sz, [c_i64, c_i64, c_int, c_int, c_int, c_int]),
     "b200f_search": (c_int, [ctypes.POINTER(SearchArgs)]),

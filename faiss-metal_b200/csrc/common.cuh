@@ -57,7 +57,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // rows.cu: queries fp32 [nq][d] -> A planes (16-bit, [npl][nq][d_pad]) + squared norms.
 int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,
-                           int64_t a_pitch, int64_t a_plane_stride, float* qnorm,
+                           int64_t a_pitch, int64_t a_plane_stride, float* qnorm, int norm_cols,
                            cudaStream_t stream);
 
 // scan.cu: streaming search for small nq, k <= 32.  Writes P = *out_P partial lists.
@@ -66,8 +66,9 @@ struct ScanPlan {
     int threads;
 };
 ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count);
+// *out_P receives the number of partial lists per query actually written (<= plan.grid).
 int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part_key,
-                     int32_t* part_idx, cudaStream_t stream);
+                     int32_t* part_idx, int* out_P, cudaStream_t stream);
 // Scan that stores keys (smaller = better) to a matrix [nq][ld] for columns [col0, col0+ncols).
 int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, float* out,
                       int64_t ld, int sm_count, cudaStream_t stream);
@@ -89,15 +90,15 @@ struct GemmOperands {
     int npl;                   // 1 (fp16 / bf16 storage) or 3 (fp32 storage split)
     int is_bf16;               // element format of both operands
     int64_t nq, nb;
-    int d_pad;                 // K extent (multiple of 8)
+    int d_pad;                 // K extent (multiple of 8), norm columns included
 };
 // Fused top-k (k <= 32): partial lists part_key/part_idx [nq][P][k].
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                     float alpha, const float* bias, int k, float* part_key, int32_t* part_idx,
+                     float kscale, int k, float* part_key, int32_t* part_idx,
                      uint32_t* gthr, int32_t* status, cudaStream_t stream);
-// Store mode: out[row*ld + (col-col0)] = sign*(alpha*dot + bias[col]) + rowadd[row].
+// Store mode: out[row*ld + (col-col0)] = sign*(-kscale*t) + rowadd[row], t = q.x (- ||x||^2/2).
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                      float alpha, const float* bias, float sign, const float* rowadd, float* out,
+                      float kscale, float sign, const float* rowadd, float* out,
                       int64_t ld, int32_t* status, cudaStream_t stream);
 
 // select.cu

@@ -13,8 +13,9 @@
 //   warp 1     MMA issuer: tcgen05.mma kind::f16, M=128 N=256 K=16, fp32 accumulators
 //              in TMEM, two accumulator buffers (2 x 256 columns)
 //   warps 2-5  epilogue: tcgen05.ld (thread t owns query row t of the tile),
-//              key = bias[col] + alpha * dot, threshold filter against the row's
-//              current k-th best, sorted insertion into a per-row list in shared memory
+//              one max per column (the L2 bias -||x||^2/2 is part of the dot product:
+//              8 extra K columns, see rows.cu), threshold filter against the row's current
+//              k-th best, replace-worst insertion into a per-row list in shared memory
 // A work item is (query block, column range); every item yields one sorted
 // partial list per query row, merged afterwards by merge_partials.
 //
@@ -52,10 +53,9 @@ constexpr int SM_A = 0;
 constexpr int SM_B = SM_A + STAGES * A_STAGE_BYTES;
 constexpr int SM_LKEY = SM_B + STAGES * B_STAGE_BYTES;
 constexpr int SM_LIDX = SM_LKEY + KMAX * BM * 4;
-constexpr int SM_BIAS = SM_LIDX + KMAX * BM * 4;
-constexpr int SM_BAR = SM_BIAS + 2 * BN * 4;
-// barriers: full[4] empty[4] tfull[2] tempty[2] bias[2]  = 14 x 8 bytes
-constexpr int SM_TMEMPTR = SM_BAR + 14 * 8;
+constexpr int SM_BAR = SM_LIDX + KMAX * BM * 4;
+// barriers: full[4] empty[4] tfull[2] tempty[2]  = 12 x 8 bytes
+constexpr int SM_TMEMPTR = SM_BAR + 12 * 8;
 constexpr int SM_ABORT = SM_TMEMPTR + 4;
 constexpr int SMEM_BYTES = SM_ABORT + 4 + 8;
 
@@ -70,14 +70,14 @@ struct GemmParams {
     int nqb;
     int P;
     int kb_per_pass;     // k-blocks of 64 per plane product
+    int k_extent;        // valid K elements per plane product (multiple of 8)
     int npass;
     uint32_t pass_a;     // 4 bits per pass: plane index of A
     uint32_t pass_b;
     uint32_t idesc;
     int mode;
     int k;
-    float alpha;
-    const float* bias;   // per global column, may be null (0)
+    float kscale;        // key = -kscale * t  (2 for L2, 1 for inner product)
     float sign;
     const float* rowadd; // per query row, may be null (0)
     float* part_key;
@@ -242,7 +242,7 @@ __device__ __noinline__ float list_replace_worst(float* lkey, int32_t* lidx, int
 
 // Writes the row list best-first: k rounds of "extract the lexicographic minimum".
 __device__ __noinline__ void list_write_sorted(float* lkey, int32_t* lidx, int row, int k,
-                                               float* out_key, int32_t* out_idx) {
+                                               float kscale, float* out_key, int32_t* out_idx) {
     for (int r = 0; r < k; r++) {
         float bk = lkey[row];
         int32_t bi = lidx[row];
@@ -261,7 +261,7 @@ __device__ __noinline__ void list_write_sorted(float* lkey, int32_t* lidx, int r
                 }
             }
         }
-        out_key[r] = bk;
+        out_key[r] = kscale * bk;  // INF stays INF for empty slots
         out_idx[r] = bi;
         lkey[bp * BM + row] = CUDART_INF_F;  // consumed
         lidx[bp * BM + row] = -1;
@@ -278,7 +278,6 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     float* lkey = reinterpret_cast<float*>(smem + SM_LKEY);
     int32_t* lidx = reinterpret_cast<int32_t*>(smem + SM_LIDX);
-    float* sbias = reinterpret_cast<float*>(smem + SM_BIAS);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + SM_TMEMPTR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_ABORT);
 
@@ -286,7 +285,6 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t bar_empty = bar_full + STAGES * 8;
     const uint32_t bar_tfull = bar_empty + STAGES * 8;
     const uint32_t bar_tempty = bar_tfull + 2 * 8;
-    const uint32_t bar_bias = bar_tempty + 2 * 8;
 
     if ((sbase & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
         if (threadIdx.x == 0 && p.status) atomicOr(p.status, kDevErrSmemAlign);
@@ -302,7 +300,6 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int s = 0; s < 2; s++) {
             mbar_init(bar_tfull + s * 8, 1);
             mbar_init(bar_tempty + s * 8, 4);
-            mbar_init(bar_bias + s * 8, NUM_EPI_THREADS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -391,11 +388,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         tc_fence_after();
                         const uint64_t da = make_smem_desc(sbase + SM_A + stage * A_STAGE_BYTES);
                         const uint64_t db = make_smem_desc(sbase + SM_B + stage * B_STAGE_BYTES);
+                        // the last k-block of a plane product may hold fewer than 64 valid
+                        // K elements (TMA zero-fills the rest): skip the all-zero sub-steps
+                        const int kin = kb % p.kb_per_pass;
+                        const int kvalid = p.k_extent - kin * BK;
+                        const int nk4 = kvalid >= BK ? BK / UMMA_K : (kvalid + UMMA_K - 1) / UMMA_K;
 #pragma unroll
                         for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
                             // advance 32 bytes (16 elements) along K inside the swizzle row
-                            tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
-                                       p.idesc, (kb | k4) != 0 ? 1u : 0u);
+                            if (k4 < nk4)
+                                tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
+                                           p.idesc, (kb | k4) != 0 ? 1u : 0u);
                         }
                         tc_commit(bar_empty + stage * 8);  // frees the stage when the MMAs retire
                         if (++stage == STAGES) {
@@ -414,7 +417,6 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ------------------------------ epilogue -----------------------------------
         const int ew = warp & 3;              // TMEM lane quarter this warp may read
         const int row = ew * 32 + lane;       // row of the tile owned by this thread
-        const int et = threadIdx.x - 64;      // 0..127
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -441,25 +443,9 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             for (int64_t t = t0; t < t1 && ok; t++) {
                 const int64_t c_tile = p.col0 + t * BN;
-                // stage the per-column bias of this tile (+INF beyond the last valid column)
-                {
-                    float* bs = sbias + acc * BN;
-                    for (int c = et; c < BN; c += NUM_EPI_THREADS) {
-                        const int64_t gc = c_tile + c;
-                        float b = CUDART_INF_F;
-                        if (gc < p.ncols_end) b = p.bias ? __ldg(p.bias + gc) : 0.f;
-                        bs[c] = b;
-                    }
-                    mbar_arrive(bar_bias + acc * 8);
-                    const bool w = mbar_wait(bar_bias + acc * 8, acc_phase, abort_flag, p.status);
-                    if (!__all_sync(0xffffffffu, w)) {  // keep the warp converged for tcgen05.ld
-                        ok = false;
-                        break;
-                    }
-                }
                 {
                     const bool w = mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag, p.status);
-                    if (!__all_sync(0xffffffffu, w)) {
+                    if (!__all_sync(0xffffffffu, w)) {  // keep the warp converged for tcgen05.ld
                         ok = false;
                         break;
                     }
@@ -477,42 +463,51 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const float gnext = (g >= 0xff800000u) ? CUDART_INF_F : ordered_to_float(g + 1u);
                     thr_eff = fminf(thr, gnext);
                 }
-                const float* bs = sbias + acc * BN;
+                // The accumulator holds t = q.x (- ||x||^2/2 for L2): larger is better; the
+                // lists keep s = -t (smaller is better).  Rows of X beyond the last valid
+                // column are zero-filled by TMA (t = 0) and must be masked out.
+                const bool partial = c_tile + BN > p.ncols_end;
                 const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN;
 #pragma unroll 1
                 for (int ch = 0; ch < BN / 32; ch++) {
                     uint32_t r[32];
                     tc_ld32(taddr + ch * 32, r);
                     tc_wait_ld();
+                    const int64_t cbase = c_tile + ch * 32;
                     if (p.mode == MODE_TOPK) {
-                        uint32_t hits = 0;
+                        if (partial) {
 #pragma unroll
-                        for (int c = 0; c < 32; c++) {
-                            const float s = fmaf(p.alpha, __uint_as_float(r[c]), bs[ch * 32 + c]);
-                            r[c] = __float_as_uint(s);
-                            hits |= (s < thr_eff ? 1u : 0u) << c;
+                            for (int c = 0; c < 32; c++)
+                                if (cbase + c >= p.ncols_end) r[c] = 0xff800000u;  // -INF
                         }
-                        if (hits != 0 && row_live) {
-                            const int32_t id0 = (int32_t)(c_tile + ch * 32);
+                        // one max per column (tree), one compare per 32 columns
+                        float m[16];
+#pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            m[c] = fmaxf(__uint_as_float(r[c]), __uint_as_float(r[c + 16]));
+#pragma unroll
+                        for (int w2 = 8; w2 > 0; w2 >>= 1)
+#pragma unroll
+                            for (int c = 0; c < w2; c++) m[c] = fmaxf(m[c], m[c + w2]);
+                        if (-m[0] < thr_eff && row_live) {
+                            const int32_t id0 = (int32_t)cbase;
 #pragma unroll
                             for (int c = 0; c < 32; c++) {
-                                const float s = __uint_as_float(r[c]);
-                                if (((hits >> c) & 1u) && s < thr_eff) {
-                                    thr = list_replace_worst(lkey, lidx, row, k, s, id0 + c, worst);
+                                const float sc = -__uint_as_float(r[c]);
+                                if (sc < thr_eff) {
+                                    thr = list_replace_worst(lkey, lidx, row, k, sc, id0 + c, worst);
                                     thr_eff = fminf(thr_eff, thr);
                                 }
                             }
                         }
                     } else {
                         if (row_live) {
-                            const int64_t cbase = c_tile + ch * 32;
                             float* orow = p.out + grow * p.ld + (cbase - p.col0);
 #pragma unroll
                             for (int c = 0; c < 32; c++) {
                                 if (cbase + c < p.ncols_end) {
-                                    const float s =
-                                            fmaf(p.alpha, __uint_as_float(r[c]), bs[ch * 32 + c]);
-                                    orow[c] = fmaf(p.sign, s, radd);
+                                    const float key = -p.kscale * __uint_as_float(r[c]);
+                                    orow[c] = fmaf(p.sign, key, radd);
                                 }
                             }
                         }
@@ -526,7 +521,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             if (p.mode == MODE_TOPK && row_live && ok) {
                 if (thr < thr_pub) atomicMin(p.gthr + grow, float_to_ordered(thr));
-                list_write_sorted(lkey, lidx, row, k, p.part_key + (grow * p.P + xr) * k,
+                list_write_sorted(lkey, lidx, row, k, p.kscale, p.part_key + (grow * p.P + xr) * k,
                                   p.part_idx + (grow * p.P + xr) * k);
             }
         }
@@ -606,6 +601,7 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
     p.nqb = plan.nqb;
     p.P = plan.P;
     p.kb_per_pass = (int)ceil_div64(op.d_pad, BK);
+    p.k_extent = op.d_pad;
     if (op.npl == 1) {
         p.npass = 1;
         p.pass_a = 0;
@@ -669,7 +665,7 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
 }
 
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                     float alpha, const float* bias, int k, float* part_key, int32_t* part_idx,
+                     float kscale, int k, float* part_key, int32_t* part_idx,
                      uint32_t* gthr, int32_t* status, cudaStream_t stream) {
     if (k <= 0 || k > KMAX) return B200F_ERR_UNSUPPORTED;
     if (!gthr) return B200F_ERR_BAD_ARG;
@@ -678,8 +674,7 @@ int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0,
     GemmParams p{};
     p.mode = MODE_TOPK;
     p.k = k;
-    p.alpha = alpha;
-    p.bias = bias;
+    p.kscale = kscale;
     p.sign = 1.f;
     p.rowadd = nullptr;
     p.part_key = part_key;
@@ -692,13 +687,12 @@ int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0,
 }
 
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                      float alpha, const float* bias, float sign, const float* rowadd, float* out,
+                      float kscale, float sign, const float* rowadd, float* out,
                       int64_t ld, int32_t* status, cudaStream_t stream) {
     GemmParams p{};
     p.mode = MODE_STORE;
     p.k = 0;
-    p.alpha = alpha;
-    p.bias = bias;
+    p.kscale = kscale;
     p.sign = sign;
     p.rowadd = rowadd;
     p.part_key = nullptr;

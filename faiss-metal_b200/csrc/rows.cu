@@ -99,15 +99,55 @@ __global__ void row_norms_kernel(const void* __restrict__ rows, int64_t n, int d
     }
 }
 
+// ---- norm columns ------------------------------------------------------------------------
+// The tensor path and the 16-bit scan get "||x||^2" out of the same dot product as q.x: a
+// stored row carries 8 extra columns [d8, d8+8) holding -||x||^2/2 split into 16-bit pieces
+// c_i, the query row carries the matching scales S_i there, so that
+//     q_ext . x_ext = q.x - ||x||^2/2      (L2 key = -2 * that, + ||q||^2 at the end).
+// bf16 has the exponent range of fp32: three pieces at scale 1.  fp16 does not: four
+// pieces at scales 2^12, 2^1, 2^-10, 2^-21 (each an exact fp16 value) cover
+// ||x||^2/2 up to 2.7e8 with at least 22 significant bits.
+__device__ __forceinline__ float norm_scale(int storage, int slot) {
+    if (storage == B200F_STORAGE_F16) {
+        return slot == 0 ? 4096.f : slot == 1 ? 2.f : slot == 2 ? 9.765625e-4f : slot == 3 ? 4.76837158203125e-7f : 0.f;
+    }
+    return slot < 3 ? 1.f : 0.f;
+}
+
+// pieces of v for the 8 norm columns (16-bit patterns), format = fp16 or bf16
+__device__ __forceinline__ void norm_pieces(float v, int storage, uint16_t (&out)[8]) {
+    float r = v;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float S = norm_scale(storage, i);
+        uint16_t bits = 0;
+        if (S != 0.f) {
+            const float c = r / S;
+            float back;
+            if (storage == B200F_STORAGE_F16) {
+                bits = float_to_fp16_bits(c);
+                back = fp16_bits_to_float(bits);
+            } else {
+                bits = float_to_bf16_bits(c);
+                back = bf16_bits_to_float(bits);
+            }
+            r = fmaf(-S, back, r);
+        }
+        out[i] = bits;
+    }
+}
+
 // ---- append-time conversion -----------------------------------------------------------
 // One warp per row.  Writes the stored row (pad columns zeroed), the squared norm of
-// the stored values and, for fp32 storage, the three bf16 split planes.
+// the stored values, for fp32 storage the three bf16 split planes, and (norm_cols) the
+// 8 norm columns after the d8 = round_up(d, 8) data columns of the 16-bit row / plane 0.
 template <int STORAGE>
 __global__ void store_rows_kernel(const float* __restrict__ src, int64_t n, int d,
                                   void* __restrict__ dst, int64_t dst_pitch,
                                   uint16_t* __restrict__ planes, int64_t plane_pitch,
-                                  int64_t plane_stride, float* __restrict__ norms) {
+                                  int64_t plane_stride, float* __restrict__ norms, int norm_cols) {
     const int lane = threadIdx.x & 31;
+    const int d8 = (d + 7) & ~7;
     const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
          r += warps_total) {
@@ -153,9 +193,21 @@ __global__ void store_rows_kernel(const float* __restrict__ src, int64_t n, int 
                 s = fmaf(back, back, s);
             }
         }
-        if (norms) {
-            s = warp_sum(s);
-            if (lane == 0) norms[r] = s;
+        s = warp_sum(s);
+        if (norms && lane == 0) norms[r] = s;
+        if (norm_cols) {
+            __syncwarp();
+            if (lane == 0) {
+                uint16_t pc[8];
+                norm_pieces(-0.5f * s, STORAGE == B200F_STORAGE_F32 ? B200F_STORAGE_BF16 : STORAGE, pc);
+                uint16_t* o = (STORAGE == B200F_STORAGE_F32)
+                                      ? (planes ? planes + r * plane_pitch + d8 : nullptr)
+                                      : reinterpret_cast<uint16_t*>(dst) + r * dst_pitch + d8;
+                if (o) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) o[i] = pc[i];
+                }
+            }
         }
     }
 }
@@ -174,11 +226,15 @@ __global__ void load_rows_kernel(const void* __restrict__ rows, int64_t n, int d
 
 // ---- query preparation -------------------------------------------------------------------
 // fp32 queries -> operand planes of the tensor path (+ exact fp32 squared norms).
-// npl == 1: one plane in the storage format (fp16 or bf16); npl == 3: bf16 split planes.
+// One plane in the storage format (fp16 / bf16) or three bf16 split planes (fp32 storage).
+// With norm_cols the 8 columns after d8 of plane 0 receive the norm scales (see above).
 __global__ void prepare_queries_kernel(const float* __restrict__ q, int64_t nq, int d, int storage,
                                        uint16_t* __restrict__ a, int64_t a_pitch,
-                                       int64_t a_plane_stride, float* __restrict__ qnorm) {
+                                       int64_t a_plane_stride, float* __restrict__ qnorm,
+                                       int norm_cols) {
     const int lane = threadIdx.x & 31;
+    const int d8 = (d + 7) & ~7;
+    const int fmt = storage == B200F_STORAGE_F16 ? B200F_STORAGE_F16 : B200F_STORAGE_BF16;
     const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nq;
          r += warps_total) {
@@ -189,6 +245,8 @@ __global__ void prepare_queries_kernel(const float* __restrict__ q, int64_t nq, 
             s = fmaf(v, v, s);
             if (a && j < a_pitch) {
                 uint16_t* p0 = a + r * a_pitch + j;
+                const bool ncol = norm_cols && j >= d8 && j < d8 + 8;
+                if (ncol) v = norm_scale(fmt, j - d8);
                 if (storage == B200F_STORAGE_F16) {
                     *p0 = float_to_fp16_bits(v);
                 } else if (storage == B200F_STORAGE_BF16) {
@@ -276,11 +334,11 @@ int cached_sm_count() {
 }
 
 int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,
-                           int64_t a_pitch, int64_t a_plane_stride, float* qnorm,
+                           int64_t a_pitch, int64_t a_plane_stride, float* qnorm, int norm_cols,
                            cudaStream_t stream) {
     if (nq <= 0) return B200F_OK;
     prepare_queries_kernel<<<grid_for_rows(nq), ROW_THREADS, 0, stream>>>(
-            q, nq, d, storage, a_planes, a_pitch, a_plane_stride, qnorm);
+            q, nq, d, storage, a_planes, a_pitch, a_plane_stride, qnorm, norm_cols);
     count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
@@ -316,24 +374,30 @@ extern "C" int b200f_row_norms(const void* rows, int storage, int64_t n, int d, 
 
 extern "C" int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
                                 int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
-                                int64_t plane_stride, float* norms_or_null, void* stream) {
+                                int64_t plane_stride, float* norms_or_null, int norm_cols,
+                                void* stream) {
     if (n < 0 || d <= 0 || dst_pitch < d || (n > 0 && (!src || !dst_rows))) return B200F_ERR_BAD_ARG;
     if (planes && (plane_pitch < d || plane_stride < plane_pitch)) return B200F_ERR_BAD_ARG;
+    if (norm_cols) {
+        const int64_t need = ((d + 7) & ~7) + 8;
+        if (storage == B200F_STORAGE_F32 ? (planes && plane_pitch < need) : dst_pitch < need)
+            return B200F_ERR_BAD_ARG;
+    }
     if (n == 0) return B200F_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int g = grid_for_rows(n);
     switch (storage) {
         case B200F_STORAGE_F32:
             store_rows_kernel<B200F_STORAGE_F32><<<g, ROW_THREADS, 0, st>>>(
-                    src, n, d, dst_rows, dst_pitch, planes, plane_pitch, plane_stride, norms_or_null);
+                    src, n, d, dst_rows, dst_pitch, planes, plane_pitch, plane_stride, norms_or_null, norm_cols);
             break;
         case B200F_STORAGE_F16:
             store_rows_kernel<B200F_STORAGE_F16><<<g, ROW_THREADS, 0, st>>>(
-                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null);
+                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null, norm_cols);
             break;
         case B200F_STORAGE_BF16:
             store_rows_kernel<B200F_STORAGE_BF16><<<g, ROW_THREADS, 0, st>>>(
-                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null);
+                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null, norm_cols);
             break;
         default:
             return B200F_ERR_BAD_ARG;

@@ -13,6 +13,7 @@
 // (ITERS = ceil(C / LPR) pieces per lane); a warp therefore covers 32 / LPR rows per
 // step and U steps per block, keeping U independent 16-byte loads in flight per lane.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200f {
 
@@ -38,10 +39,18 @@ struct ScanParams {
     int lpr;                // lanes per row (power of two)
     int iters;              // pieces per lane
     int qstride;            // floats per query in shared memory (C * E)
+    int norm_cols;          // 16-bit rows carry -||x||^2/2 in 8 columns after d8 (see rows.cu)
+    float nscale[4];        // scales the query side puts into those columns
     float* part_key;        // top-k mode: [nq][P][k]
     int32_t* part_idx;
     float* out;             // store mode: [nq][ld]
     int64_t ld;
+    // bulk-copy pipeline (scan_bulk_kernel)
+    int rb;                 // rows per consumer warp per stage
+    int stage_rows;         // rows per stage = SB_NW * rb
+    int stage_stride;       // bytes between stages in shared memory
+    int nstage;
+    int32_t* status;
 };
 
 template <int STORAGE>
@@ -114,7 +123,13 @@ scan_kernel(const ScanParams p) {
     for (int i = threadIdx.x; i < NQ * p.qstride; i += SCAN_THREADS) {
         const int qi = i / p.qstride;
         const int j = i - qi * p.qstride;
-        sq[i] = (qi < p.nq && j < p.d) ? p.queries[(int64_t)qi * p.d + j] : 0.f;
+        float v = 0.f;
+        if (qi < p.nq) {
+            const int d8 = (p.d + 7) & ~7;
+            if (j < p.d) v = p.queries[(int64_t)qi * p.d + j];
+            else if (p.norm_cols && j >= d8 && j < d8 + 4) v = p.nscale[j - d8];
+        }
+        sq[i] = v;
     }
     __syncthreads();
 
@@ -264,17 +279,248 @@ scan_kernel(const ScanParams p) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Streaming pipeline for 16-bit storage (top-k mode, up to 8 queries per pass): one CTA per
+// SM.  Warp 0 streams whole blocks of rows (contiguous in memory) into a shared-memory ring
+// with cp.async.bulk + mbarriers, so the bytes in flight are set by the ring depth.  The
+// SM_NW consumer warps take 16-row tiles and evaluate them with mma.sync m16n8k16
+// (A = 16 stored rows, B = the queries as 8 columns, fp32 accumulate): about two
+// instructions per row instead of a convert + FMA per element, and no shuffle reduction --
+// the accumulator fragment leaves the score of (row g / g+8, query 2t / 2t+1) in lane 4g+t.
+// The dot product is invariant under a permutation of K applied to both operands, so each
+// lane simply takes 16 contiguous bytes per 32-column chunk (row g and row g+8 at column
+// 32c + 8t) and the query matrix in shared memory is read with the same pattern.  With
+// norm columns in the rows the L2 term -||x||^2/2 is part of the same dot product.
+// ---------------------------------------------------------------------------------------
+constexpr int SM_NW = 8;
+constexpr int SM_THREADS = 32 * (1 + SM_NW);
+constexpr int SM_MAX_STAGES = 8;
+constexpr int SM_NQ = 8;
+
+template <bool BF16>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    if (BF16) {
+        asm volatile(
+                "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                "{%8,%9}, {%0,%1,%2,%3};"
+                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile(
+                "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                "{%8,%9}, {%0,%1,%2,%3};"
+                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParams p) {
+    extern __shared__ __align__(128) uint8_t sm[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t sbase = smem_u32(sm);
+    const int ring_bytes = p.nstage * p.stage_stride;
+    // query matrix [8][kq] in the storage format, kq = 32 * nchunk (zero padded)
+    const int nchunk = p.iters;          // 32-column chunks per row, norm columns included
+    const int kq = nchunk * 32;
+    uint16_t* sqh = reinterpret_cast<uint16_t*>(sm + ring_bytes);
+    const int qbytes = SM_NQ * kq * 2;
+    const uint32_t bar_full = sbase + ring_bytes + qbytes;
+    const uint32_t bar_empty = bar_full + SM_MAX_STAGES * 8;
+    volatile int* abort_flag =
+            reinterpret_cast<volatile int*>(sm + ring_bytes + qbytes + 2 * SM_MAX_STAGES * 8);
+    const int d8 = (p.d + 7) & ~7;
+    const int kext = d8 + (p.norm_cols ? 8 : 0);  // valid columns of a stored row
+
+    for (int i = threadIdx.x; i < SM_NQ * kq; i += SM_THREADS) {
+        const int qi = i / kq;
+        const int j = i - qi * kq;
+        float v = 0.f;
+        if (qi < p.nq) {
+            if (j < p.d) v = p.queries[(int64_t)qi * p.d + j];
+            else if (p.norm_cols && j >= d8 && j < d8 + 4) v = p.nscale[j - d8];
+        }
+        sqh[i] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+    }
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < p.nstage; s++) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, SM_NW);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int64_t nrows_total = p.col1 - p.col0;
+    const int64_t nchunks = ceil_div64(nrows_total, p.stage_rows);
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(p.rows);
+    const float kmul = p.metric == B200F_METRIC_L2 ? -2.f : -1.f;
+
+    float lk[SM_NQ];
+    int li[SM_NQ];
+    float thr[SM_NQ];
+    int thr_id[SM_NQ];
+#pragma unroll
+    for (int qi = 0; qi < SM_NQ; qi++) {
+        lk[qi] = CUDART_INF_F;
+        li[qi] = -1;
+        thr[qi] = CUDART_INF_F;
+        thr_id[qi] = -1;
+    }
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+                if (!mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status,
+                                       kDevErrBarrierWait)) {
+                    ok = false;
+                    break;
+                }
+                const int64_t row0 = p.col0 + c * p.stage_rows;
+                const int64_t nr = min((int64_t)p.stage_rows, p.col1 - row0);
+                const uint32_t bytes = (uint32_t)(nr * p.pitch_bytes);
+                mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
+                bulk_load(sbase + stage * p.stage_stride, base + row0 * p.pitch_bytes, bytes,
+                          bar_full + stage * 8);
+                if (++stage == p.nstage) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) {  // let copies already issued land before shared memory goes away
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000LL) {
+                }
+            }
+        }
+    } else {
+        const int wc = warp - 1;
+        const int g = lane >> 2;
+        const int t = lane & 3;
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+            const bool w = mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status,
+                                             kDevErrBarrierWait);
+            if (!__all_sync(FULL, w)) break;
+            const int64_t row0 = p.col0 + c * p.stage_rows;
+            const int nr = (int)min((int64_t)p.stage_rows, p.col1 - row0);
+            const uint32_t sstage = sbase + stage * p.stage_stride;
+            const int ntiles = (nr + 15) >> 4;
+            for (int tile = wc; tile < ntiles; tile += SM_NW) {
+                const int r0 = tile * 16 + g;      // local rows of this lane
+                const int r1 = r0 + 8;
+                const bool v0 = r0 < nr, v1 = r1 < nr;
+                const uint32_t a_row0 = sstage + (uint32_t)r0 * (uint32_t)p.pitch_bytes + t * 16;
+                const uint32_t a_row1 = sstage + (uint32_t)r1 * (uint32_t)p.pitch_bytes + t * 16;
+                const uint32_t b_row = sbase + ring_bytes + (uint32_t)(g * kq * 2) + t * 16;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+                for (int ch = 0; ch < nchunk; ch++) {
+                    const bool kv = ch * 32 + t * 8 < kext;  // beyond the row: the next row's bytes
+                    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+                    if (kv && v0) x0 = lds128(a_row0 + ch * 64);
+                    if (kv && v1) x1 = lds128(a_row1 + ch * 64);
+                    const uint4 q = lds128(b_row + ch * 64);
+                    // A fragment: a0 = row g cols k, a1 = row g+8 cols k, a2 = row g cols k+8, a3 = row g+8 cols k+8
+                    mma16816<BF16>(acc, x0.x, x1.x, x0.y, x1.y, q.x, q.y);
+                    mma16816<BF16>(acc, x0.z, x1.z, x0.w, x1.w, q.z, q.w);
+                }
+                // acc[0]: (row r0, query 2t)  acc[1]: (r0, 2t+1)  acc[2]: (r1, 2t)  acc[3]: (r1, 2t+1)
+#pragma unroll
+                for (int qi = 0; qi < SM_NQ; qi++) {
+                    if (qi >= p.nq) break;
+                    const bool mine = (qi >> 1) == t;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const float key = kmul * ((qi & 1) ? acc[2 * h + 1] : acc[2 * h]);
+                        const int row = (int)(row0 + (h ? r1 : r0));
+                        const bool hit = mine && (h ? v1 : v0) && before(key, row, thr[qi], thr_id[qi]);
+                        unsigned m = __ballot_sync(FULL, hit);
+                        while (m) {
+                            const int src = __ffs(m) - 1;
+                            m &= m - 1;
+                            const float s = __shfl_sync(FULL, key, src);
+                            const int id = __shfl_sync(FULL, row, src);
+                            if (before(s, id, thr[qi], thr_id[qi])) {
+                                warp_insert(lk[qi], li[qi], s, id, lane);
+                                thr[qi] = __shfl_sync(FULL, lk[qi], p.k - 1);
+                                thr_id[qi] = __shfl_sync(FULL, li[qi], p.k - 1);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+            if (++stage == p.nstage) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+    }
+
+    // CTA merge in the (now idle) ring memory: consumer warp wc publishes its lists,
+    // warp 1 + qi folds them for query qi.
+    __syncthreads();
+    float* mk = reinterpret_cast<float*>(sm);                        // [SM_NW][SM_NQ][32]
+    int* mi = reinterpret_cast<int*>(sm) + SM_NW * SM_NQ * 32;
+    if (warp > 0) {
+#pragma unroll
+        for (int qi = 0; qi < SM_NQ; qi++) {
+            mk[((warp - 1) * SM_NQ + qi) * 32 + lane] = lk[qi];
+            mi[((warp - 1) * SM_NQ + qi) * 32 + lane] = li[qi];
+        }
+    }
+    __syncthreads();
+    if (warp >= 1 && warp - 1 < p.nq) {
+        const int qi = warp - 1;
+        float k0 = mk[qi * 32 + lane];
+        int i0 = mi[qi * 32 + lane];
+        float tk = __shfl_sync(FULL, k0, p.k - 1);
+        int tid = __shfl_sync(FULL, i0, p.k - 1);
+        for (int w2 = 1; w2 < SM_NW; w2++) {
+            for (int j = 0; j < p.k; j++) {
+                const float s = mk[(w2 * SM_NQ + qi) * 32 + j];
+                const int id = mi[(w2 * SM_NQ + qi) * 32 + j];
+                if (id < 0 || !before(s, id, tk, tid)) break;
+                warp_insert(k0, i0, s, id, lane);
+                tk = __shfl_sync(FULL, k0, p.k - 1);
+                tid = __shfl_sync(FULL, i0, p.k - 1);
+            }
+        }
+        if (lane < p.k) {
+            const int64_t o = ((int64_t)qi * gridDim.x + blockIdx.x) * p.k + lane;
+            p.part_key[o] = k0;
+            p.part_idx[o] = i0;
+        }
+    }
+}
+
 size_t scan_smem_bytes(int nq_t, int qstride) {
     size_t a = (size_t)nq_t * qstride * 4;
     size_t b = (size_t)SCAN_WARPS * nq_t * 32 * 8;
     return a > b ? a : b;
 }
 
-void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch) {
+void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch, int norm_cols) {
     const int E = storage == B200F_STORAGE_F32 ? 4 : 8;
     const int es = storage == B200F_STORAGE_F32 ? 4 : 2;
     p.pitch_bytes = row_pitch * es;
-    p.C = (d + E - 1) / E;
+    p.norm_cols = (norm_cols && storage != B200F_STORAGE_F32) ? 1 : 0;
+    p.C = (d + E - 1) / E;  // data pieces; the norm piece (if any) follows them in the row
+    if (storage == B200F_STORAGE_F16) {
+        p.nscale[0] = 4096.f; p.nscale[1] = 2.f; p.nscale[2] = 9.765625e-4f; p.nscale[3] = 4.76837158203125e-7f;
+    } else {
+        p.nscale[0] = 1.f; p.nscale[1] = 1.f; p.nscale[2] = 1.f; p.nscale[3] = 0.f;
+    }
     int lpr = 1;
     while (lpr < p.C && lpr < 32) lpr <<= 1;
     p.lpr = lpr;
@@ -316,9 +562,31 @@ int launch_storage(const ScanParams& p, int storage, int grid, cudaStream_t stre
     return B200F_ERR_BAD_ARG;
 }
 
+
+// Stage geometry of the streaming pipeline; returns false when it does not apply.
+bool plan_stream(ScanParams& p, int storage, int d, int norm_cols) {
+    if (storage == B200F_STORAGE_F32 || (p.pitch_bytes % 16) != 0) return false;
+    const int d8 = (d + 7) & ~7;
+    const int kext = d8 + (norm_cols ? 8 : 0);
+    p.norm_cols = norm_cols ? 1 : 0;
+    p.iters = (kext + 31) / 32;                 // 32-column chunks
+    int64_t rows = (36 * 1024) / p.pitch_bytes; // ~36 KiB per stage
+    rows = rows / 16 * 16;
+    if (rows < 16) rows = 16;
+    if (rows > 16 * SM_NW * 2) rows = 16 * SM_NW * 2;
+    p.stage_rows = (int)rows;
+    p.rb = 16;
+    p.stage_stride = (int)round_up64((int64_t)p.stage_rows * p.pitch_bytes + 64, 128);
+    const int64_t fixed = (int64_t)SM_NQ * p.iters * 32 * 2 + 2 * SM_MAX_STAGES * 8 + 16;
+    int64_t ns = (220 * 1024 - fixed) / p.stage_stride;
+    if (ns > SM_MAX_STAGES) ns = SM_MAX_STAGES;
+    p.nstage = (int)ns;
+    return ns >= 3;
+}
+
 int scan_grid(int64_t nrows, int d, int storage, int sm_count) {
     ScanParams t{};
-    fill_geometry(t, storage, d, d);
+    fill_geometry(t, storage, d, d, 0);
     const int rows_per_block = (32 / t.lpr) * SCAN_U;
     const int64_t nblocks = ceil_div64(nrows, rows_per_block);
     int64_t g = ceil_div64(nblocks, SCAN_WARPS);
@@ -339,10 +607,10 @@ ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count) {
 }
 
 int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part_key,
-                     int32_t* part_idx, cudaStream_t stream) {
-    if (a.nq < 1 || a.nq > 4 || a.k < 1 || a.k > 32) return B200F_ERR_UNSUPPORTED;
+                     int32_t* part_idx, int* out_P, cudaStream_t stream) {
+    if (a.nq < 1 || a.nq > 8 || a.k < 1 || a.k > 32) return B200F_ERR_UNSUPPORTED;
     ScanParams p{};
-    fill_geometry(p, a.storage, a.d, a.row_pitch);
+    fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0);
     p.queries = a.queries;
     p.rows = a.rows;
     p.norms = a.norms;
@@ -355,6 +623,38 @@ int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part
     p.metric = a.metric;
     p.part_key = part_key;
     p.part_idx = part_idx;
+    p.status = a.status;
+    const int sm = cached_sm_count();
+    {
+        ScanParams ps = p;
+        const int nc = (a.metric == B200F_METRIC_L2 && a.norm_cols) ? 1 : 0;
+        if ((a.metric != B200F_METRIC_L2 || nc) && plan_stream(ps, a.storage, a.d, nc) &&
+            a.nb >= (int64_t)ps.stage_rows * sm) {
+            // streaming pipeline: one CTA per SM, one partial list per CTA
+            const int64_t nchunks = ceil_div64(a.nb, ps.stage_rows);
+            const int grid = (int)(nchunks < sm ? nchunks : sm);
+            const size_t smem = (size_t)ps.nstage * ps.stage_stride + (size_t)SM_NQ * ps.iters * 32 * 2 +
+                                2 * SM_MAX_STAGES * 8 + 16;
+            *out_P = grid;
+            if (a.storage == B200F_STORAGE_BF16) {
+                B200F_CUDA_TRY(cudaFuncSetAttribute(scan_mma_kernel<true>,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                main_kernel_begin(stream);
+                scan_mma_kernel<true><<<grid, SM_THREADS, smem, stream>>>(ps);
+            } else {
+                B200F_CUDA_TRY(cudaFuncSetAttribute(scan_mma_kernel<false>,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                main_kernel_begin(stream);
+                scan_mma_kernel<false><<<grid, SM_THREADS, smem, stream>>>(ps);
+            }
+            main_kernel_end(stream);
+            count_launch();
+            B200F_LAUNCH_CHECK();
+            return B200F_OK;
+        }
+    }
+    if (a.nq > 4) return B200F_ERR_UNSUPPORTED;
+    *out_P = plan.grid;
     return launch_storage<false>(p, a.storage, plan.grid, stream);
 }
 
@@ -363,7 +663,7 @@ int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, flo
     if (a.nq < 1 || a.nq > 4) return B200F_ERR_UNSUPPORTED;
     if (ncols <= 0) return B200F_OK;
     ScanParams p{};
-    fill_geometry(p, a.storage, a.d, a.row_pitch);
+    fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0);
     p.queries = a.queries;
     p.rows = a.rows;
     p.norms = a.norms;

@@ -50,6 +50,7 @@ struct SearchPlan {
 
 bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool pairwise,
                SearchPlan& pl) {
+    // the query operand always reserves the 8 norm columns (used for L2 only)
     if (nq < 0 || nb < 0 || d <= 0 || k <= 0 || storage < 0 || storage > 2) return false;
     const int sm = cached_sm_count();
     pl = SearchPlan{};
@@ -57,7 +58,7 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     if (path == B200F_PATH_AUTO) pl.path = (nq <= SCAN_GROUP) ? B200F_PATH_SCAN : B200F_PATH_TENSOR;
     pl.fused = (k <= B200F_FUSED_MAX_K) && !pairwise;
     pl.npl = (storage == B200F_STORAGE_F32) ? 3 : 1;
-    pl.a_pitch = round_up64(d, 8);
+    pl.a_pitch = round_up64(d, 8) + 8;
     pl.a_plane_stride = round_up64((nq > 0 ? nq : 1) * pl.a_pitch, 128);
     pl.ngroups = ceil_div64(nq, SCAN_GROUP);
     size_t off = 0;
@@ -81,7 +82,8 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
             P = pl.gemm.P;
         } else {
             pl.scan = plan_scan(nq, nb, d, storage, sm);
-            P = pl.scan.grid;
+            // room for either scan kernel: the streaming one writes one list per SM
+            P = pl.scan.grid > sm ? pl.scan.grid : sm;
         }
         if (P < 1) P = 1;
         pl.off_part_key = off;
@@ -159,7 +161,9 @@ int fill_operands(const B200FSearchArgs& a, const SearchPlan& pl, uint8_t* scrat
     op.npl = pl.npl;
     op.nq = a.nq;
     op.nb = a.nb;
-    op.d_pad = (int)round_up64(a.d, 8);
+    const bool l2 = a.metric == B200F_METRIC_L2;
+    if (l2 && !a.norm_cols) return B200F_ERR_BAD_ARG;  // the tensor path takes ||x||^2 from the rows
+    op.d_pad = (int)round_up64(a.d, 8) + (l2 ? 8 : 0);
     if (a.storage == B200F_STORAGE_F32) {
         if (!a.planes || a.plane_pitch < op.d_pad || (a.plane_pitch % 8) != 0 ||
             (a.plane_stride % 8) != 0)
@@ -330,8 +334,8 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
     uint8_t* scratch = static_cast<uint8_t*>(a->scratch);
     float* qnorm = reinterpret_cast<float*>(scratch + pl.off_qnorm);
     const int sm = cached_sm_count();
-    const float alpha = l2 ? -2.f : -1.f;
-    const float* bias = l2 ? a->norms : nullptr;
+    const float kscale = l2 ? 2.f : 1.f;
+    const int qnc = l2 ? 1 : 0;
 
     GemmOperands op{};
     if (pl.path == B200F_PATH_TENSOR) {
@@ -339,9 +343,9 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         if (rc != B200F_OK) return rc;
         rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage,
                                     reinterpret_cast<uint16_t*>(scratch + pl.off_a), pl.a_pitch,
-                                    pl.a_plane_stride, qnorm, st);
+                                    pl.a_plane_stride, qnorm, qnc, st);
     } else {
-        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, st);
+        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, st);
     }
     if (rc != B200F_OK) return rc;
 
@@ -351,18 +355,22 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         int P;
         if (pl.path == B200F_PATH_TENSOR) {
             P = pl.gemm.P;
-            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, alpha, bias, a->k, part_key, part_idx,
+            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, a->k, part_key, part_idx,
                                   reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
+            // every group of <= 4 queries writes the same number of lists (same shard, same
+            // geometry); the first launch reports it
             P = pl.scan.grid;
             for (int64_t g = 0; g < pl.ngroups; g++) {
                 B200FSearchArgs sub = *a;
                 sub.queries = a->queries + g * SCAN_GROUP * (int64_t)a->d;
                 sub.nq = (a->nq - g * SCAN_GROUP) < SCAN_GROUP ? (a->nq - g * SCAN_GROUP) : SCAN_GROUP;
+                int Pg = P;
                 rc = launch_scan_topk(sub, pl.scan, part_key + g * SCAN_GROUP * (int64_t)P * a->k,
-                                      part_idx + g * SCAN_GROUP * (int64_t)P * a->k, st);
+                                      part_idx + g * SCAN_GROUP * (int64_t)P * a->k, &Pg, st);
                 if (rc != B200F_OK) return rc;
+                if (g == 0) P = Pg;
             }
         }
         return launch_merge_partials(part_key, part_idx, P, a->nq, a->k, a->metric, qnorm,
@@ -378,7 +386,7 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         const int64_t nc = (a->nb - c0) < pl.chunk_cols ? (a->nb - c0) : pl.chunk_cols;
         if (pl.path == B200F_PATH_TENSOR) {
             GemmPlan g = plan_gemm(a->nq, nc, sm);
-            rc = launch_gemm_store(op, g, c0, nc, alpha, bias, 1.f, nullptr, matrix, pl.chunk_cols,
+            rc = launch_gemm_store(op, g, c0, nc, kscale, 1.f, nullptr, matrix, pl.chunk_cols,
                                    a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
@@ -413,8 +421,7 @@ extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64
     uint8_t* scratch = static_cast<uint8_t*>(a->scratch);
     float* qnorm = reinterpret_cast<float*>(scratch + pl.off_qnorm);
     const bool l2 = a->metric == B200F_METRIC_L2;
-    const float alpha = l2 ? -2.f : -1.f;
-    const float* bias = l2 ? a->norms : nullptr;
+    const float kscale = l2 ? 2.f : 1.f;
     const int sm = cached_sm_count();
     if (pl.path == B200F_PATH_TENSOR) {
         GemmOperands op{};
@@ -422,12 +429,12 @@ extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64
         if (rc != B200F_OK) return rc;
         rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage,
                                     reinterpret_cast<uint16_t*>(scratch + pl.off_a), pl.a_pitch,
-                                    pl.a_plane_stride, qnorm, st);
+                                    pl.a_plane_stride, qnorm, l2 ? 1 : 0, st);
         if (rc != B200F_OK) return rc;
-        return launch_gemm_store(op, pl.gemm, 0, a->nb, alpha, bias, l2 ? 1.f : -1.f,
+        return launch_gemm_store(op, pl.gemm, 0, a->nb, kscale, l2 ? 1.f : -1.f,
                                  l2 ? qnorm : nullptr, out_matrix, ld_out, a->status, st);
     }
-    rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, st);
+    rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, st);
     if (rc != B200F_OK) return rc;
     for (int64_t g = 0; g < pl.ngroups; g++) {
         B200FSearchArgs sub = *a;

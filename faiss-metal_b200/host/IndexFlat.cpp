@@ -159,6 +159,7 @@ struct B200IndexFlat::Impl {
         a.status = status;
         a.stream = stream();
         a.path = forcePath;
+        a.norm_cols = l2 ? 1 : 0;
     }
 };
 
@@ -204,8 +205,10 @@ B200IndexFlat::B200IndexFlat(std::shared_ptr<B200Resources> resources, int d_,
     impl_->storage = storage;
     impl_->d = d_;
     impl_->l2 = metric == faiss::METRIC_L2;
-    impl_->pitch = storage == StorageType::Float32 ? roundUp(d_, 4) : roundUp(d_, 8);
-    impl_->planePitch = roundUp(d_, 8);
+    // L2: the 16-bit row (or split plane 0) carries 8 norm columns after round_up(d, 8)
+    const int64_t normCols = impl_->l2 ? 8 : 0;
+    impl_->pitch = storage == StorageType::Float32 ? roundUp(d_, 4) : roundUp(d_, 8) + normCols;
+    impl_->planePitch = roundUp(d_, 8) + normCols;
     DeviceGuard g(impl_->res->getDevice());
     impl_->status = static_cast<int32_t*>(impl_->res->allocBuffer(256));
     impl_->oneRow = static_cast<float*>(impl_->res->allocBuffer((size_t)d_ * 4));
@@ -269,7 +272,7 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
                          static_cast<uint8_t*>(impl_->rows) + (size_t)row * impl_->pitch * es, impl_->pitch,
                          impl_->planes ? impl_->planes + (size_t)row * impl_->planePitch : nullptr,
                          impl_->planePitch, impl_->capacity * impl_->planePitch,
-                         impl_->norms ? impl_->norms + row : nullptr, st),
+                         impl_->norms ? impl_->norms + row : nullptr, impl_->l2 ? 1 : 0, st),
                  "add: store rows");
     }
     // the caller may free x as soon as add returns

@@ -97,12 +97,15 @@ int b200f_row_norms(const void* rows, int storage, int64_t n, int d, int64_t pit
  * precision (pitch dst_pitch elements, pad columns zeroed), optional squared
  * norms of the STORED values, and for FP32 storage the three bf16 split
  * planes the tensor path multiplies (planes[p][r][plane_pitch], plane p at
- * p*plane_stride elements).
+ * p*plane_stride elements).  With norm_cols = 1 the 16-bit row (or split plane 0)
+ * also receives, in the 8 columns after round_up(d, 8), the value -||x||^2/2 split
+ * into 16-bit pieces, so that the distance GEMM / scan obtains q.x - ||x||^2/2 from
+ * one dot product (the pitch must then be >= round_up(d, 8) + 8).
  * Replaces the conversion loops and the per-add norm pass of
  * MetalIndexFlat::add (src/MetalIndexFlat.mm:224-255,259-268,296-307). */
 int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
                      int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
-                     int64_t plane_stride, float* norms_or_null, void* stream);
+                     int64_t plane_stride, float* norms_or_null, int norm_cols, void* stream);
 
 /* Stored rows -> fp32 [n][d] (pitch d).
  * Replaces the per-element conversions of MetalIndexFlat::reconstruct
@@ -134,7 +137,9 @@ typedef struct B200FSearchArgs {
                                 stream drains means a bounded device wait ran out          */
     void* stream;
     int32_t path;            /* B200F_PATH_*                                                */
-    int32_t reserved;
+    int32_t norm_cols;       /* 1: 16-bit rows / split plane 0 carry the 8 norm columns
+                                written by b200f_store_rows(norm_cols = 1); required for
+                                L2 on 16-bit storage and on the tensor path                */
 } B200FSearchArgs;
 
 /* Scratch bytes b200f_search needs for this shape (0 on bad arguments).

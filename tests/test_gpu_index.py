@@ -102,3 +102,19 @@ def test_ties_lower_label_first(fm, res, path):
             assert np.array_equal(I, ref_i)
             np.testing.assert_allclose(D, ref_d, rtol=1e-6, atol=1e-6)
             idx.close()
+
+
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("storage", [0, 1, 2])
+@pytest.mark.parametrize("nv,nq,d,k", [(40_000, 1, 64, 10), (40_000, 4, 128, 32), (40_001, 3, 200, 7),
+                                       (5_000, 2, 1536, 32), (150_000, 1, 128, 10), (40_000, 1, 100, 1)])
+def test_scan_streaming_pipeline(fm, res, metric, storage, nv, nq, d, k):
+    # shards large enough for the streaming ring of the scan path (small ones use the plain
+    # kernel); with 16-bit storage that kernel multiplies queries rounded to the storage format
+    xb = H.uniform_pm1(nv, d, 17)
+    xb[nv // 2::997] = xb[5]  # a few exact duplicates: ties by label
+    xq = H.uniform_pm1(nq, d, 18)
+    idx = make_index(fm, res, xb, metric, storage, PATH_SCAN)
+    D, I = idx.search(xq, k)
+    H.check_against_oracle(metric, storage, storage != 0, xb, xq, k, D, I)
+    idx.close()

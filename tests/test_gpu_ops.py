@@ -29,8 +29,9 @@ class Stored:
         self.nb, self.d = xb.shape
         self.storage = storage
         es = 4 if storage == 0 else 2
-        self.pitch = (self.d + 3) // 4 * 4 if storage == 0 else (self.d + 7) // 8 * 8
-        self.ppitch = (self.d + 7) // 8 * 8
+        # 8 norm columns after round_up(d, 8) in the 16-bit row / split plane 0
+        self.pitch = (self.d + 3) // 4 * 4 if storage == 0 else (self.d + 7) // 8 * 8 + 8
+        self.ppitch = (self.d + 7) // 8 * 8 + 8
         dev = torch.device("cuda:0")
         self.rows = torch.zeros(max(1, self.nb) * self.pitch * es, dtype=torch.uint8, device=dev)
         self.planes = torch.zeros(3 * max(1, self.nb) * self.ppitch, dtype=torch.int16, device=dev) if storage == 0 else None
@@ -38,7 +39,7 @@ class Stored:
         src = torch.from_numpy(xb).to(dev)
         fm.abi.check_op(L.b200f_store_rows(vp(src), self.nb, self.d, storage, vp(self.rows), self.pitch,
                                            vp(self.planes), self.ppitch, max(1, self.nb) * self.ppitch,
-                                           vp(self.norms), cur_stream()), "store_rows")
+                                           vp(self.norms), 1, cur_stream()), "store_rows")
         torch.cuda.synchronize()
 
     def args(self, fm, xq_dev, metric, k, path, out_d=None, out_l=None):
@@ -70,6 +71,7 @@ class Stored:
         a.status = self.status.data_ptr()
         a.stream = torch.cuda.current_stream().cuda_stream
         a.path = path
+        a.norm_cols = 1
         return a
 
 
@@ -93,8 +95,19 @@ def test_row_norms_and_store(fm, res, storage, n, d):
     assert np.array_equal(back.cpu().numpy().view(np.uint32), O.round_storage(xb, storage).view(np.uint32))
     if storage == 0:
         # the three bf16 planes sum back to the fp32 value to within 2^-24 relative
-        pl = st.planes.view(torch.bfloat16).reshape(3, n, st.ppitch)[:, :, :d].to(torch.float64).sum(0).cpu().numpy()
+        planes = st.planes.view(torch.bfloat16).reshape(3, n, st.ppitch).to(torch.float64)
+        pl = planes[:, :, :d].sum(0).cpu().numpy()
         np.testing.assert_allclose(pl, xb.astype(np.float64), rtol=2.0 ** -22, atol=1e-30)
+        ncols = planes[0, :, st.ppitch - 8:].sum(1).cpu().numpy()     # scales are 1 for bf16
+        np.testing.assert_allclose(ncols, -0.5 * want.astype(np.float64), rtol=2.0 ** -21)
+    else:
+        # norm columns: sum_i S_i * c_i == -||x||^2 / 2 to >= 21 bits
+        d8 = (d + 7) // 8 * 8
+        view = st.rows.view(torch.float16 if storage == 1 else torch.bfloat16).reshape(n, st.pitch)
+        pieces = view[:, d8:d8 + 8].to(torch.float64).cpu().numpy()
+        scales = np.array([4096.0, 2.0, 2.0 ** -10, 2.0 ** -21, 0, 0, 0, 0]) if storage == 1 else \
+            np.array([1.0, 1.0, 1.0, 0, 0, 0, 0, 0])
+        np.testing.assert_allclose(pieces @ scales, -0.5 * want.astype(np.float64), rtol=2.0 ** -21)
 
 
 @pytest.mark.parametrize("path", [1, 2])
