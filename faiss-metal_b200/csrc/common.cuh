@@ -75,7 +75,8 @@ int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, flo
 
 // gemm_topk.cu
 struct GemmPlan {
-    int nqb;             // query blocks of 128 rows
+    int pair;            // 1: CTA pairs (cta_group::2), query blocks of 256 rows
+    int nqb;             // query blocks of 128 (256) rows
     int64_t ntiles;      // column tiles of 256 rows in the launch
     int P;               // column ranges == partial lists per query
     int64_t tiles_per_range;

@@ -29,6 +29,8 @@
 // all roles drain out, TMEM is released and the kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200f {
@@ -38,26 +40,36 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;  // 16-bit elements: 128 bytes = one swizzle row
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int KMAX = B200F_FUSED_MAX_K;
 constexpr int NUM_THREADS = 192;
 constexpr int NUM_EPI_THREADS = 128;
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
-// shared memory map (bytes from the 1024-aligned dynamic base)
-constexpr int SM_A = 0;
-constexpr int SM_B = SM_A + STAGES * A_STAGE_BYTES;
-constexpr int SM_LKEY = SM_B + STAGES * B_STAGE_BYTES;
-constexpr int SM_LIDX = SM_LKEY + KMAX * BM * 4;
-constexpr int SM_BAR = SM_LIDX + KMAX * BM * 4;
-// barriers: full[4] empty[4] tfull[2] tempty[2]  = 12 x 8 bytes
-constexpr int SM_TMEMPTR = SM_BAR + 12 * 8;
-constexpr int SM_ABORT = SM_TMEMPTR + 4;
-constexpr int SMEM_BYTES = SM_ABORT + 4 + 8;
+// Two shapes of the same kernel:
+//  PAIR = false  one CTA per tile: M = 128 queries, N = 256 rows of X, cta_group::1
+//  PAIR = true   two CTAs of a cluster share a 256 x 256 tile (cta_group::2): each CTA stages
+//                its own 128 query rows and HALF of the X rows of every k-block, so the
+//                shared-memory fill per FLOP is halved; the MMA is issued by the even CTA.
+template <bool PAIR>
+struct Cfg {
+    static constexpr int STAGES = PAIR ? 6 : 4;
+    static constexpr int B_ROWS = PAIR ? 128 : 256;        // rows of X staged by this CTA
+    static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;  // 16 / 32 KiB
+    static constexpr int QB = PAIR ? 256 : 128;            // query rows per work item
+    // shared memory map (bytes from the 1024-aligned dynamic base)
+    static constexpr int SM_A = 0;
+    static constexpr int SM_B = SM_A + STAGES * A_STAGE_BYTES;
+    static constexpr int SM_LKEY = SM_B + STAGES * B_STAGE_BYTES;
+    static constexpr int SM_LIDX = SM_LKEY + KMAX * BM * 4;
+    static constexpr int SM_BAR = SM_LIDX + KMAX * BM * 4;
+    // barriers: full[STAGES] empty[STAGES] tfull[2] tempty[2]
+    static constexpr int SM_TMEMPTR = SM_BAR + (2 * STAGES + 4) * 8;
+    static constexpr int SM_ABORT = SM_TMEMPTR + 4;
+    static constexpr int SMEM_BYTES = SM_ABORT + 4 + 8;
+};
 
 enum { MODE_TOPK = 0, MODE_STORE = 1 };
 
@@ -155,6 +167,56 @@ __device__ __forceinline__ void tc_fence_before() {
 }
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// arrive on an mbarrier given by a shared::cluster address (own or peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA load issued inside a CTA pair: the mbarrier may live in the peer CTA
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 int c0, int c1, int c2) {
+    asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+            : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}\n" ::"r"(d_tmem),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -268,13 +330,22 @@ __device__ __noinline__ void list_write_sorted(float* lkey, int32_t* lidx, int r
     }
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    using C = Cfg<PAIR>;
+    constexpr int STAGES = C::STAGES;
+    constexpr int B_STAGE_BYTES = C::B_STAGE_BYTES;
+    constexpr int SM_A = C::SM_A, SM_B = C::SM_B, SM_LKEY = C::SM_LKEY, SM_LIDX = C::SM_LIDX;
+    constexpr int SM_BAR = C::SM_BAR, SM_TMEMPTR = C::SM_TMEMPTR, SM_ABORT = C::SM_ABORT;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;   // 0 = MMA issuer of the pair
+    const int64_t unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;  // work is dealt to CTAs / CTA pairs
+    const int64_t nunits = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
     float* lkey = reinterpret_cast<float*>(smem + SM_LKEY);
     int32_t* lidx = reinterpret_cast<int32_t*>(smem + SM_LIDX);
@@ -286,7 +357,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t bar_tfull = bar_empty + STAGES * 8;
     const uint32_t bar_tempty = bar_tfull + 2 * 8;
 
-    if ((sbase & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
+    if ((sbase & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base (same in both CTAs)
         if (threadIdx.x == 0 && p.status) atomicOr(p.status, kDevErrSmemAlign);
         return;
     }
@@ -299,19 +370,28 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(bar_tfull + s * 8, 1);
-            mbar_init(bar_tempty + s * 8, 4);
+            mbar_init(bar_tempty + s * 8, PAIR ? 8 : 4);  // epilogue warps of one / both CTAs
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                             sbase + SM_TMEMPTR),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                                 sbase + SM_TMEMPTR),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                                 sbase + SM_TMEMPTR),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
 
@@ -324,7 +404,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+            for (int64_t item = unit; item < nitems && ok; item += nunits) {
                 const int qb = (int)(item % p.nqb);
                 const int64_t xr = item / p.nqb;
                 const int64_t t0 = xr * p.tiles_per_range;
@@ -340,11 +420,23 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const int kk = (kb - pass * p.kb_per_pass) * BK;
                         const int pa = (p.pass_a >> (4 * pass)) & 15;
                         const int pb = (p.pass_b >> (4 * pass)) & 15;
-                        mbar_arrive_expect_tx(bar_full + stage * 8, A_STAGE_BYTES + B_STAGE_BYTES);
-                        tma_load_3d(sbase + SM_A + stage * A_STAGE_BYTES, &tmap_a,
-                                    bar_full + stage * 8, kk, qb * BM, pa);
-                        tma_load_3d(sbase + SM_B + stage * B_STAGE_BYTES, &tmap_b,
-                                    bar_full + stage * 8, kk, xrow, pb);
+                        if (PAIR) {
+                            // both CTAs' copies complete on the issuer's barrier
+                            const uint32_t fb = map_to_cta(bar_full + stage * 8, 0);
+                            if (cta_rank == 0)
+                                mbar_arrive_expect_tx(bar_full + stage * 8,
+                                                      2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+                            tma_load_3d_pair(sbase + SM_A + stage * A_STAGE_BYTES, &tmap_a, fb, kk,
+                                             qb * C::QB + (int)cta_rank * BM, pa);
+                            tma_load_3d_pair(sbase + SM_B + stage * B_STAGE_BYTES, &tmap_b, fb, kk,
+                                             xrow + (int)cta_rank * C::B_ROWS, pb);
+                        } else {
+                            mbar_arrive_expect_tx(bar_full + stage * 8, A_STAGE_BYTES + B_STAGE_BYTES);
+                            tma_load_3d(sbase + SM_A + stage * A_STAGE_BYTES, &tmap_a,
+                                        bar_full + stage * 8, kk, qb * BM, pa);
+                            tma_load_3d(sbase + SM_B + stage * B_STAGE_BYTES, &tmap_b,
+                                        bar_full + stage * 8, kk, xrow, pb);
+                        }
                         if (++stage == STAGES) {
                             stage = 0;
                             phase ^= 1;
@@ -363,13 +455,13 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        if (lane == 0 && cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int64_t item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+            for (int64_t item = unit; item < nitems && ok; item += nunits) {
                 const int64_t xr = item / p.nqb;
                 const int64_t t0 = xr * p.tiles_per_range;
                 const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
@@ -396,18 +488,35 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                         for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
                             // advance 32 bytes (16 elements) along K inside the swizzle row
-                            if (k4 < nk4)
-                                tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
-                                           p.idesc, (kb | k4) != 0 ? 1u : 0u);
+                            if (k4 < nk4) {
+                                if (PAIR)
+                                    tc_mma_f16_pair(d_tmem, da + (uint64_t)(k4 * 2),
+                                                    db + (uint64_t)(k4 * 2), p.idesc,
+                                                    (kb | k4) != 0 ? 1u : 0u);
+                                else
+                                    tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
+                                               p.idesc, (kb | k4) != 0 ? 1u : 0u);
+                            }
                         }
-                        tc_commit(bar_empty + stage * 8);  // frees the stage when the MMAs retire
+                        // frees the stage (in both CTAs of a pair) when the MMAs retire
+                        if (PAIR) {
+                            tc_commit_pair(map_to_cta(bar_empty + stage * 8, 0));
+                            tc_commit_pair(map_to_cta(bar_empty + stage * 8, 1));
+                        } else {
+                            tc_commit(bar_empty + stage * 8);
+                        }
                         if (++stage == STAGES) {
                             stage = 0;
                             phase ^= 1;
                         }
                     }
                     if (!ok) break;
-                    tc_commit(bar_tfull + acc * 8);  // accumulator complete
+                    if (PAIR) {  // accumulator complete, in both CTAs
+                        tc_commit_pair(map_to_cta(bar_tfull + acc * 8, 0));
+                        tc_commit_pair(map_to_cta(bar_tfull + acc * 8, 1));
+                    } else {
+                        tc_commit(bar_tfull + acc * 8);
+                    }
                     acc ^= 1;
                     if (acc == 0) acc_phase ^= 1;
                 }
@@ -421,12 +530,12 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t acc_phase = 0;
         bool ok = true;
         const int k = p.k;
-        for (int64_t item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+        for (int64_t item = unit; item < nitems && ok; item += nunits) {
             const int qb = (int)(item % p.nqb);
             const int64_t xr = item / p.nqb;
             const int64_t t0 = xr * p.tiles_per_range;
             const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
-            const int64_t grow = (int64_t)qb * BM + row;
+            const int64_t grow = (int64_t)qb * C::QB + (int64_t)cta_rank * BM + row;
             const bool row_live = grow < p.nq;
             float thr = CUDART_INF_F;      // worst key of this thread's list (k-th best of the range)
             float thr_eff = CUDART_INF_F;  // filter: min(thr, bound shared by all ranges of the row)
@@ -489,14 +598,32 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         for (int w2 = 8; w2 > 0; w2 >>= 1)
 #pragma unroll
                             for (int c = 0; c < w2; c++) m[c] = fmaxf(m[c], m[c + w2]);
-                        if (-m[0] < thr_eff && row_live) {
-                            const int32_t id0 = (int32_t)cbase;
+                        // Slow path, entered by the whole warp when any row has a candidate in
+                        // this chunk.  Every lane first marks its own hit columns; the lanes then
+                        // insert in lock-step (round j = each lane's j-th hit, ascending column),
+                        // so the number of rounds is the largest hit count of a lane, not the
+                        // number of distinct hit columns of the warp.
+                        const bool any_hit = (-m[0] < thr_eff) && row_live;
+                        if (__any_sync(0xffffffffu, any_hit)) {
+                            uint32_t mask = 0;
+                            if (any_hit) {
 #pragma unroll
-                            for (int c = 0; c < 32; c++) {
-                                const float sc = -__uint_as_float(r[c]);
-                                if (sc < thr_eff) {
-                                    thr = list_replace_worst(lkey, lidx, row, k, sc, id0 + c, worst);
-                                    thr_eff = fminf(thr_eff, thr);
+                                for (int c = 0; c < 32; c++)
+                                    mask |= (-__uint_as_float(r[c]) < thr_eff ? 1u : 0u) << c;
+                            }
+                            const int32_t id0 = (int32_t)cbase;
+                            while (__any_sync(0xffffffffu, mask != 0)) {
+                                if (mask != 0) {
+                                    const int cc = __ffs(mask) - 1;
+                                    mask &= mask - 1;
+                                    uint32_t bits = 0;
+#pragma unroll
+                                    for (int c = 0; c < 32; c++) bits = (c == cc) ? r[c] : bits;
+                                    const float sc = -__uint_as_float(bits);
+                                    if (sc < thr_eff) {
+                                        thr = list_replace_worst(lkey, lidx, row, k, sc, id0 + cc, worst);
+                                        thr_eff = fminf(thr_eff, thr);
+                                    }
                                 }
                             }
                         }
@@ -515,7 +642,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + acc * 8);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + acc * 8, 0));
+                    else mbar_arrive(bar_tempty + acc * 8);
+                }
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1;
             }
@@ -529,11 +659,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the peer may still read this CTA's tiles / signal its barriers
     if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"(TMEM_COLS)
-                     : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"(TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"(TMEM_COLS)
+                         : "memory");
     }
 }
 
@@ -590,7 +726,7 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
                               op.a_plane_stride, BM);
     if (rc != B200F_OK) return rc;
     rc = make_operand_map(&mb, op.b_planes, op.is_bf16, op.d_pad, op.nb, op.b_pitch, op.npl,
-                          op.b_plane_stride, BN);
+                          op.b_plane_stride, plan.pair ? Cfg<true>::B_ROWS : Cfg<false>::B_ROWS);
     if (rc != B200F_OK) return rc;
 
     p.nq = op.nq;
@@ -613,17 +749,43 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
         p.pass_b = 0x001021u;
     }
     const uint32_t fmt = op.is_bf16 ? 1u : 0u;
+    // fp32 accumulate, K-major operands, N = 256, M = 128 (one CTA) or 256 (CTA pair)
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
-              ((uint32_t)(BM >> 4) << 24);
+              ((uint32_t)((plan.pair ? 2 * BM : BM) >> 4) << 24);
 
     static bool attr_set = false;
     if (!attr_set) {
-        B200F_CUDA_TRY(cudaFuncSetAttribute(gemm_topk_kernel,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200F_CUDA_TRY(cudaFuncSetAttribute(gemm_topk_kernel<false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            Cfg<false>::SMEM_BYTES));
+        B200F_CUDA_TRY(cudaFuncSetAttribute(gemm_topk_kernel<true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            Cfg<true>::SMEM_BYTES));
         attr_set = true;
     }
     main_kernel_begin(stream);
-    gemm_topk_kernel<<<plan.grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+    if (plan.pair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)plan.grid, 1, 1);
+        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_topk_kernel<true>, ma, mb, p);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            main_kernel_end(stream);
+            return B200F_ERR_CUDA;
+        }
+    } else {
+        gemm_topk_kernel<false><<<plan.grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, stream>>>(ma, mb, p);
+    }
     main_kernel_end(stream);
     count_launch();
     B200F_LAUNCH_CHECK();
@@ -632,25 +794,67 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
 
 }  // namespace
 
+// B200F_GEMM_PAIR=0 / 1 in the environment forces the single-CTA / CTA-pair shape (testing).
+static int pair_override() {
+    static int v = -2;
+    if (v == -2) {
+        const char* e = getenv("B200F_GEMM_PAIR");
+        v = (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+    }
+    return v;
+}
+
+// CTA pairs that can be resident at once (GPC boundaries may leave a few SMs unpaired).
+static int max_active_pairs(int sm_count) {
+    static int cached = -1;
+    if (cached < 0) {
+        cached = sm_count / 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2), 1, 1);
+        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<true>::SMEM_BYTES) == cudaSuccess &&
+            cudaOccupancyMaxActiveClusters(&n, gemm_topk_kernel<true>, &cfg) == cudaSuccess && n > 0) {
+            if (n < cached) cached = n;
+        } else {
+            (void)cudaGetLastError();
+        }
+    }
+    return cached;
+}
+
 GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
     GemmPlan g;
-    g.nqb = (int)ceil_div64(nq, BM);
+    const int ov = pair_override();
+    g.pair = ov >= 0 ? ov : (nq > BM ? 1 : 0);       // a pair covers 256 query rows
+    const int qb = g.pair ? 2 * BM : BM;
+    const int units = g.pair ? max_active_pairs(sm_count) : sm_count;  // CTAs or CTA pairs that run at once
+    g.nqb = (int)ceil_div64(nq, qb);
     g.ntiles = ceil_div64(ncols, BN);
     if (g.nqb <= 0 || g.ntiles <= 0) {
         g.nqb = 0; g.ntiles = 0; g.P = 0; g.tiles_per_range = 0; g.grid = 0;
         return g;
     }
-    // Number of column ranges: make nqb * P a multiple of the SM count when there is
+    // Number of column ranges: make nqb * P a multiple of the unit count when there is
     // enough work, keep at least ~32 tiles per range so list warm-up stays cheap.
     auto gcd = [](int64_t a, int64_t b) { while (b) { int64_t t = a % b; a = b; b = t; } return a; };
-    int64_t P0 = sm_count / gcd(sm_count, g.nqb);
+    int64_t P0 = units / gcd(units, g.nqb);
     int64_t P;
     if (P0 >= g.ntiles) {
         P = g.ntiles;
     } else {
         int64_t max_mult = g.ntiles / (P0 * 32);
         int64_t want_waves = 8;
-        int64_t mult = (want_waves * sm_count) / (P0 * g.nqb);
+        int64_t mult = (want_waves * units) / (P0 * g.nqb);
         if (mult < 1) mult = 1;
         if (max_mult < 1) max_mult = 1;
         if (mult > max_mult) mult = max_mult;
@@ -660,7 +864,8 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
     g.tiles_per_range = ceil_div64(g.ntiles, P);
     g.P = (int)ceil_div64(g.ntiles, g.tiles_per_range);
     int64_t items = (int64_t)g.nqb * g.P;
-    g.grid = (int)(items < sm_count ? items : sm_count);
+    int64_t u = items < units ? items : units;
+    g.grid = (int)(g.pair ? 2 * u : u);
     return g;
 }
 
