@@ -364,9 +364,25 @@ def run_b200(args, w, rank, world, local_rank):
         if not args.no_e2e:
             assert np.array_equal(l_pin.numpy(), I_host), "end-to-end labels differ from device-resident labels"
 
-    if rank != 0:
+    # every torch tensor that lived on the library's stream must be released before that stream
+    # is destroyed (torch records an event on the allocation stream when it frees a block)
+    D_dev = I_dev = xq_dev = xq_pin = d_pin = l_pin = t = dt = sharded = evs = ev_unused = None  # noqa: F841
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+
+    def teardown():
+        # ordered: index, resources, then the process group
+        torch.cuda.synchronize()
+        index.close()
+        res.close()
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
+
+    if rank != 0:
+        teardown()
         return
 
     nb_local = hi - lo
@@ -411,8 +427,7 @@ def run_b200(args, w, rank, world, local_rank):
         "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    teardown()
 
 
 def main():
