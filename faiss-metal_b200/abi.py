@@ -59,6 +59,8 @@ SIGNATURES = {
     "b200f_load_rows": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_vp]),
     "b200f_search_scratch_bytes": (c_sz, [c_i64, c_i64, c_int, c_int, c_int, c_int]),
     "b200f_search": (c_int, [ctypes.POINTER(SearchArgs)]),
+    "b200f_noalloc_scratch_capacity": (c_sz, []),
+    "b200f_search_small_noalloc": (c_int, [ctypes.POINTER(SearchArgs)]),
     "b200f_pairwise": (c_int, [ctypes.POINTER(SearchArgs), c_vp, c_i64]),
     "b200f_select_scratch_bytes": (c_sz, [c_i64, c_int]),
     "b200f_select_rows": (c_int, [c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_sz, c_vp]),

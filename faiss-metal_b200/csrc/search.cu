@@ -452,3 +452,59 @@ extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64
     B200F_LAUNCH_CHECK();
     return B200F_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Search without any allocation
+// ---------------------------------------------------------------------------------------
+namespace {
+
+// Scratch of b200f_search_small_noalloc: lives in the module image of every GPU that loads
+// the library until the process exits.  1 MiB covers the streaming-scan path for
+// nq <= 4, k <= 32 (query norms + at most 592 partial lists of 32 entries per query).
+constexpr size_t kNoAllocScratchBytes = 1u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+// Device address of the array on the CURRENT device.  In host code the symbol's name is only
+// a stand-in, never an address a kernel may use: the real address is asked for once per device.
+int noalloc_scratch_for_current_device(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return B200F_ERR_CUDA;
+    }
+    std::lock_guard<std::mutex> g(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) {
+            (void)cudaGetLastError();
+            return B200F_ERR_CUDA;
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return B200F_OK;
+}
+
+}  // namespace
+
+extern "C" size_t b200f_noalloc_scratch_capacity(void) { return kNoAllocScratchBytes; }
+
+extern "C" int b200f_search_small_noalloc(const B200FSearchArgs* a) {
+    if (!a) return B200F_ERR_BAD_ARG;
+    if (a->nq < 0 || a->nq > 4 || a->k < 1 || a->k > B200F_FUSED_MAX_K) return B200F_ERR_UNSUPPORTED;
+    B200FSearchArgs c = *a;
+    c.path = B200F_PATH_SCAN;
+    const size_t need = b200f_search_scratch_bytes(c.nq, c.nb, c.d, c.k, c.storage, c.path);
+    if (need == 0) return B200F_ERR_BAD_ARG;
+    if (need > kNoAllocScratchBytes) return B200F_ERR_SCRATCH;  // shape beyond the built-in scratch
+    void* ptr = nullptr;
+    const int rc = noalloc_scratch_for_current_device(&ptr);
+    if (rc != B200F_OK) return rc;
+    c.scratch = ptr;
+    c.scratch_bytes = kNoAllocScratchBytes;
+    return b200f_search(&c);
+}

@@ -157,6 +157,29 @@ size_t b200f_search_scratch_bytes(int64_t nq, int64_t nb, int d, int k, int stor
  * (shaders/warp_select.metal:11-114, shaders/block_select.metal:111-274). */
 int b200f_search(const B200FSearchArgs* args);
 
+/* Shard-local search that allocates nothing.  It has no counterpart in the reference.
+ *
+ * Who needs it: code that may not call cudaMalloc at the point where it searches -- a
+ * latency-critical serving loop that must never take the allocator's lock or trigger an
+ * implicit device synchronisation, a plugin that runs inside somebody else's memory pool
+ * and owns no device memory of its own, or a caller that sized its buffers once at
+ * start-up and has none left to hand over as scratch.  Such a caller still passes the
+ * queries, the stored rows and the output arrays, but no scratch: the intermediate lists
+ * live in a fixed 1 MiB array inside the library image (b200f_noalloc_scratch_capacity()),
+ * present on every GPU that loads the library until the process ends.
+ *
+ * Limits: nq <= 4 and k <= 32 (the streaming-scan path; B200F_ERR_UNSUPPORTED otherwise) and
+ * a shape whose b200f_search_scratch_bytes() fits the array (B200F_ERR_SCRATCH otherwise).
+ * args->scratch / scratch_bytes / path are ignored.  The first call on each device looks up
+ * the array's device address (with that device current); make that first call before any
+ * stream capture begins.  No cudaMalloc, cudaFree or other allocating call is made, provided
+ * profiling (b200f_profile_enable) is off, which is the default.  All calls share the one
+ * array, which keeps whatever the previous call left: this path initialises everything it
+ * reads, so nothing has to be cleared, but two calls whose kernels overlap on the GPU
+ * (different streams, or different threads) race on it -- serialise them. */
+size_t b200f_noalloc_scratch_capacity(void);
+int b200f_search_small_noalloc(const B200FSearchArgs* args);
+
 /* Full nq x nb score matrix (L2: ||q||^2 + ||x||^2 - 2 q.x, IP: q.x), fp32,
  * leading dimension ld_out.  Same operands as b200f_search (k, out_*, label_base
  * ignored).  Scratch: b200f_search_scratch_bytes(nq, nb, d, 1, storage, path).
