@@ -628,16 +628,26 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                         }
                     } else {
-                        if (row_live) {
-                            float* orow = p.out + grow * p.ld + (cbase - p.col0);
+                        // Store mode: thread t holds 32 consecutive columns of ITS row; writing
+                        // them directly would touch 32 different rows per instruction.  The warp
+                        // transposes the 32 x 32 block through shared memory (the list area is
+                        // idle in this mode) and writes one 128-byte row segment per instruction.
+                        float* tbuf = reinterpret_cast<float*>(smem + SM_LKEY) + ew * (32 * 33);
 #pragma unroll
-                            for (int c = 0; c < 32; c++) {
-                                if (cbase + c < p.ncols_end) {
-                                    const float key = -p.kscale * __uint_as_float(r[c]);
-                                    orow[c] = fmaf(p.sign, key, radd);
-                                }
-                            }
+                        for (int c = 0; c < 32; c++) {
+                            const float key = -p.kscale * __uint_as_float(r[c]);
+                            tbuf[lane * 33 + c] = fmaf(p.sign, key, radd);
                         }
+                        __syncwarp();
+                        const int64_t grow0 = grow - lane;  // first row of this warp's 32 rows
+                        const bool col_ok = cbase + lane < p.ncols_end;
+                        float* obase = p.out + (cbase - p.col0) + lane;
+#pragma unroll 8
+                        for (int rr = 0; rr < 32; rr++) {
+                            const float v = tbuf[rr * 33 + lane];
+                            if (col_ok && grow0 + rr < p.nq) obase[(grow0 + rr) * p.ld] = v;
+                        }
+                        __syncwarp();
                     }
                 }
                 tc_fence_before();

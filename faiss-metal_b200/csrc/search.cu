@@ -19,7 +19,7 @@ namespace b200f {
 
 namespace {
 
-constexpr int64_t MATRIX_BUDGET_BYTES = 512ll << 20;
+constexpr int64_t MATRIX_BUDGET_BYTES = 1024ll << 20;  // key-matrix chunk of the k > 32 path
 constexpr int SCAN_GROUP = 4;
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }

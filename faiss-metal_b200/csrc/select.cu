@@ -224,7 +224,8 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
 
     for (int64_t q = blockIdx.x; q < p.nq; q += gridDim.x) {
         __syncthreads();
-        for (int i = tid; i < SS_CAP; i += SS_THREADS) buf[i] = SS_EMPTY;
+        // the buffer is not cleared up front: slots past the live count are set to EMPTY
+        // right before each sort that would read them
         if (tid == 0) {
             s_count = 0;
             s_thr = SS_EMPTY;
@@ -233,7 +234,7 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
         if (p.has_prev) {
             for (int j = tid; j < p.k; j += SS_THREADS) {
                 const int32_t id = p.run_idx[q * p.k + j];
-                if (id >= 0) buf[j] = pack(p.run_key[q * p.k + j], (uint32_t)id);
+                buf[j] = (id >= 0) ? pack(p.run_key[q * p.k + j], (uint32_t)id) : SS_EMPTY;
             }
             __syncthreads();
             if (tid == 0) {
@@ -254,8 +255,14 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
 
         const int64_t total = (SRC == SRC_MATRIX) ? p.ncand : (int64_t)p.P * p.k;
         for (int64_t b0 = 0; b0 < total; b0 += SS_BATCH) {
+            // Every thread must take the same branch below: read the count between two
+            // barriers, so that no thread of the next batch has appended yet.
+            __syncthreads();
+            const int cnt = s_count;
+            __syncthreads();
             // make room: after compaction at most k <= 4096 entries remain
-            if (s_count > SS_CAP - SS_BATCH) {
+            if (cnt > SS_CAP - SS_BATCH) {
+                for (int i = cnt + tid; i < SS_CAP; i += SS_THREADS) buf[i] = SS_EMPTY;
                 bitonic_sort(buf, SS_CAP);
                 for (int i = p.k + tid; i < SS_CAP; i += SS_THREADS) buf[i] = SS_EMPTY;
                 if (tid == 0) {
@@ -290,13 +297,14 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                     }
                 }
             }
-            __syncthreads();
         }
+        __syncthreads();
         // final ordering
         {
             const int cnt = s_count;
             int n = 64;
             while (n < cnt) n <<= 1;
+            for (int i = cnt + tid; i < n; i += SS_THREADS) buf[i] = SS_EMPTY;
             bitonic_sort(buf, n);
         }
         for (int j = tid; j < p.k; j += SS_THREADS) {

@@ -25,7 +25,7 @@ namespace {
 
 constexpr size_t kStageBytes = 64ull << 20;   // fp32 staging chunk for add / reconstruct_n
 constexpr int64_t kFusedBatch = 16384;        // queries per launch, k <= 32
-constexpr int64_t kSelectBatch = 8192;        // queries per launch, k  > 32
+constexpr int64_t kSelectBatch = 1024;        // queries per launch, k > 32: few rows, wide column chunks
 
 void cudaCheck(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {

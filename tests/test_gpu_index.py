@@ -118,3 +118,18 @@ def test_scan_streaming_pipeline(fm, res, metric, storage, nv, nq, d, k):
     D, I = idx.search(xq, k)
     H.check_against_oracle(metric, storage, storage != 0, xb, xq, k, D, I)
     idx.close()
+
+
+@pytest.mark.parametrize("k,storage,metric", [(100, 1, O.METRIC_INNER_PRODUCT), (1024, 0, O.METRIC_L2)])
+def test_large_k_many_queries_deterministic(fm, res, k, storage, metric):
+    # more queries than selection CTAs (each CTA walks several rows) and enough columns for
+    # repeated buffer compaction; two runs must agree bit for bit and match the oracle
+    nv, nq, d = 40_000, 5_000, 32
+    xb = H.gaussian(nv, d, 21)
+    xq = H.gaussian(nq, d, 22)
+    idx = make_index(fm, res, xb, metric, storage, PATH_TENSOR)
+    D1, I1 = idx.search(xq, k)
+    D2, I2 = idx.search(xq, k)
+    assert np.array_equal(I1, I2) and np.array_equal(D1, D2)
+    H.check_against_oracle(metric, storage, True, xb, xq, k, D1, I1, loose=False)
+    idx.close()
