@@ -297,7 +297,11 @@ def run_b200(args, w, rank, world, local_rank):
                 dist.barrier()
             torch.cuda.synchronize()
 
+        single_batch = nq <= (16384 if k <= 32 else 1024)
+
         def step_device():
+            if single_batch:   # queued back to back on one stream, one host sync per step
+                return sharded.search_device(xq_dev, k)
             return sharded.search(xq_dev, k)
 
         def step_e2e():
@@ -305,10 +309,13 @@ def run_b200(args, w, rank, world, local_rank):
             if world == 1:
                 index.search(xq_pin.numpy(), k, d_pin.numpy(), l_pin.numpy())
             else:
-                dd, ll = sharded.search(xq_dev.copy_(xq_pin, non_blocking=True), k)
+                if single_batch:
+                    dd, ll = sharded.search_device(xq_dev.copy_(xq_pin, non_blocking=True), k, sync=False)
+                else:
+                    dd, ll = sharded.search(xq_dev.copy_(xq_pin, non_blocking=True), k)
                 d_pin.copy_(dd, non_blocking=True)
                 l_pin.copy_(ll, non_blocking=True)
-                ext.synchronize()
+                index.synchronize()
 
         # ---- device-resident timing ------------------------------------------------------
         sampler = ClockSampler(local_rank)
@@ -356,6 +363,43 @@ def run_b200(args, w, rank, world, local_rank):
             e2e_s = float(dt.item()) / args.steps
             e2e = {"value": nq / e2e_s, "unit": "queries/s", "ms_per_step": e2e_s * 1e3,
                    "h2d_bytes_per_step": world * nq * d * 4, "d2h_bytes_per_step": world * nq * k * 12}
+
+        # ---- latency distribution of a stream of single searches (small-nq workloads) ------
+        latency = None
+        if nq <= 4 and not args.no_e2e:
+            ncalls = 1000
+            qbank = torch.empty((64 * nq, d), dtype=torch.float32, device="cuda")
+            fm.abi.check_op(L.b200f_fill_synthetic(ctypes.c_void_p(qbank.data_ptr()), 64 * nq, d, 0, 3, w["dist"],
+                                                   w["scale"], ctypes.c_void_p(ext.cuda_stream)), "fill query bank")
+            ext.synchronize()
+            qbank_pin = torch.empty((64 * nq, d), dtype=torch.float32, pin_memory=True)
+            qbank_pin.copy_(qbank)
+            lat = []
+            barrier()
+            for i in range(ncalls):
+                j = (i % 64) * nq
+                t0 = time.perf_counter()
+                if world == 1:
+                    index.search(qbank_pin[j:j + nq].numpy(), k, d_pin.numpy(), l_pin.numpy())
+                else:
+                    dd, ll = sharded.search_device(xq_dev.copy_(qbank_pin[j:j + nq], non_blocking=True), k, sync=False)
+                    d_pin.copy_(dd, non_blocking=True)
+                    l_pin.copy_(ll, non_blocking=True)
+                    index.synchronize()
+                lat.append((time.perf_counter() - t0) * 1e3)
+            lat_t = torch.tensor(lat, dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(lat_t, op=dist.ReduceOp.MAX)   # a call ends when the slowest rank has it
+            lat_s = sorted(lat_t.cpu().tolist())
+            latency = {"calls": ncalls, "p50_ms": lat_s[len(lat_s) // 2], "p99_ms": lat_s[int(len(lat_s) * 0.99)],
+                       "max_ms": lat_s[-1], "what": "host-timed search() with host buffers, one query batch per call"}
+            qbank = qbank_pin = lat_t = None
+            # restore the benchmark queries for the checks below
+            fm.abi.check_op(L.b200f_fill_synthetic(ctypes.c_void_p(xq_dev.data_ptr()), nq, d, 0, 2, w["dist"],
+                                                   w["scale"], ctypes.c_void_p(ext.cuda_stream)), "fill queries")
+            ext.synchronize()
+            D_dev, I_dev = step_device()
+            step_e2e()
 
         # ---- checks outside the timed region ---------------------------------------------
         D_host = D_dev.cpu().numpy()
@@ -428,7 +472,7 @@ def run_b200(args, w, rank, world, local_rank):
                    "seeds": {"database": 1, "queries": 2},
                    "headline": not (args.nb or args.nq)},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches.value),
-        "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
+        "latency": latency, "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
     }
     print(json.dumps(line), flush=True)
     teardown()

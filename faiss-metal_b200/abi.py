@@ -65,6 +65,7 @@ SIGNATURES = {
     "b200f_select_scratch_bytes": (c_sz, [c_i64, c_int]),
     "b200f_select_rows": (c_int, [c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "b200f_merge_lists": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
+    "b200f_merge_lists_strided": (c_int, [c_vp, c_vp, c_i64, c_i64, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "b200f_fill_synthetic": (c_int, [c_vp, c_i64, c_int, c_i64, ctypes.c_uint64, c_int, ctypes.c_float, c_vp]),
     "b200f_profile_enable": (c_int, [c_int]),
     "b200f_profile_read": (c_int, [ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(ctypes.c_double), c_int]),
@@ -78,6 +79,8 @@ SIGNATURES = {
     "b200f_index_destroy": (None, [c_vp]),
     "b200f_index_add": (c_int, [c_vp, c_i64, c_vp]),
     "b200f_index_search": (c_int, [c_vp, c_i64, c_vp, c_i64, c_vp, c_vp]),
+    "b200f_index_search_enqueue": (c_int, [c_vp, c_i64, c_vp, c_i64, c_vp, c_vp]),
+    "b200f_index_synchronize": (c_int, [c_vp]),
     "b200f_index_search_async": (c_int, [c_vp, c_i64, c_vp, c_i64, c_vp, c_vp, ctypes.POINTER(c_vp)]),
     "b200f_token_wait": (c_int, [c_vp]),
     "b200f_token_is_ready": (c_int, [c_vp, ctypes.POINTER(c_int)]),

@@ -81,7 +81,8 @@ template <typename IdT>
 struct MergeSmallParams {
     const float* in_key;
     const IdT* in_id;
-    int64_t q_stride, p_stride;
+    int64_t q_stride, p_stride;   // elements: between queries, between lists (keys)
+    int64_t p_stride_id;          // between lists (ids)
     int P;
     int64_t nq;
     int k;
@@ -108,7 +109,7 @@ __global__ void __launch_bounds__(MS_THREADS) merge_small_kernel(const MergeSmal
         IdT thr_id = (IdT)-1;
         for (int l = warp; l < p.P; l += MS_WARPS) {
             const float* lkey = p.in_key + q * p.q_stride + (int64_t)l * p.p_stride;
-            const IdT* lid = p.in_id + q * p.q_stride + (int64_t)l * p.p_stride;
+            const IdT* lid = p.in_id + q * p.q_stride + (int64_t)l * p.p_stride_id;
             // lane j prefetches entry j, entries are then consumed in order
             float myk = CUDART_INF_F;
             IdT myi = (IdT)-1;
@@ -174,6 +175,8 @@ struct SortSelectParams {
     int64_t ld;
     int64_t ncand;
     int64_t col0;
+    int64_t list_stride_k;   // SRC_LISTS: elements between consecutive lists in keys
+    int64_t list_stride_l;   // SRC_LISTS: elements between consecutive lists in labels
     int P;
     int64_t nq;
     int k;
@@ -285,9 +288,9 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                     } else {
                         const int64_t l = c / p.k;
                         const int64_t j = c - l * p.k;
-                        const int64_t off = (l * p.nq + q) * p.k + j;
-                        key = p.key_sign * __ldg(p.keys + off);
-                        live = __ldg(p.labels + off) >= 0;
+                        const int64_t off = q * p.k + j;
+                        key = p.key_sign * __ldg(p.keys + l * p.list_stride_k + off);
+                        live = __ldg(p.labels + l * p.list_stride_l + off) >= 0;
                         payload = (uint32_t)c;
                     }
                     const uint64_t w = pack(key, payload);
@@ -323,7 +326,7 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                     } else {
                         const int64_t l = payload / p.k;
                         const int64_t jj = payload - l * p.k;
-                        label = p.labels[(l * p.nq + q) * p.k + jj];
+                        label = p.labels[l * p.list_stride_l + q * p.k + jj];
                     }
                 }
                 p.out_dist[q * p.k + j] = dist;
@@ -390,6 +393,7 @@ int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P,
     p.in_id = part_idx;
     p.q_stride = (int64_t)P * k;
     p.p_stride = k;
+    p.p_stride_id = k;
     p.P = P;
     p.nq = nq;
     p.k = k;
@@ -488,14 +492,17 @@ extern "C" int b200f_select_rows(const float* scores, int64_t nq, int64_t ncols,
     return launch_sort_select<SRC_MATRIX>(p, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P, int64_t nq, int k,
-                                 int metric, float* out_dist, int64_t* out_labels, void* stream) {
+extern "C" int b200f_merge_lists_strided(const float* dist, const int64_t* labels,
+                                         int64_t list_stride_dist, int64_t list_stride_labels, int P,
+                                         int64_t nq, int k, int metric, float* out_dist,
+                                         int64_t* out_labels, void* stream) {
     if (P <= 0 || nq < 0 || k <= 0 ||
         (metric != B200F_METRIC_L2 && metric != B200F_METRIC_INNER_PRODUCT))
         return B200F_ERR_BAD_ARG;
     if (k > B200F_MAX_K || (int64_t)P * k > 0x7fffffffLL) return B200F_ERR_UNSUPPORTED;
     if (nq == 0) return B200F_OK;
     if (!dist || !labels || !out_dist || !out_labels) return B200F_ERR_BAD_ARG;
+    if (list_stride_dist < nq * (int64_t)k || list_stride_labels < nq * (int64_t)k) return B200F_ERR_BAD_ARG;
     const bool l2 = metric == B200F_METRIC_L2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (k <= 32) {
@@ -503,7 +510,8 @@ extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P
         p.in_key = dist;
         p.in_id = labels;
         p.q_stride = k;
-        p.p_stride = nq * (int64_t)k;
+        p.p_stride = list_stride_dist;
+        p.p_stride_id = list_stride_labels;
         p.P = P;
         p.nq = nq;
         p.k = k;
@@ -526,6 +534,8 @@ extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P
     SortSelectParams p{};
     p.keys = dist;
     p.labels = labels;
+    p.list_stride_k = list_stride_dist;
+    p.list_stride_l = list_stride_labels;
     p.P = P;
     p.nq = nq;
     p.k = k;
@@ -538,4 +548,10 @@ extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P
     p.out_dist = out_dist;
     p.out_labels = out_labels;
     return launch_sort_select<SRC_LISTS>(p, st);
+}
+
+extern "C" int b200f_merge_lists(const float* dist, const int64_t* labels, int P, int64_t nq, int k,
+                                 int metric, float* out_dist, int64_t* out_labels, void* stream) {
+    return b200f_merge_lists_strided(dist, labels, nq * (int64_t)k, nq * (int64_t)k, P, nq, k, metric,
+                                     out_dist, out_labels, stream);
 }

@@ -437,6 +437,42 @@ void B200IndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k, float
     }
 }
 
+void B200IndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::idx_t k,
+                                        float* distances, faiss::idx_t* labels) const {
+    checkSearchArgs(n, x, k, distances, labels, ntotal);
+    if (n == 0) return;
+    const int64_t batch = k <= B200F_FUSED_MAX_K ? kFusedBatch : kSelectBatch;
+    FAISS_THROW_IF_NOT_MSG(n <= batch, "searchDeviceEnqueue: too many queries for one launch");
+    DeviceGuard g(impl_->res->getDevice());
+    const size_t scratchBytes =
+            b200f_search_scratch_bytes(n, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
+    FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "searchDeviceEnqueue: cannot plan this shape");
+    uint8_t* region = static_cast<uint8_t*>(impl_->res->getScratch(align256(scratchBytes)));
+    B200FSearchArgs a;
+    impl_->fillArgs(a, ntotal);
+    a.queries = x;
+    a.nq = n;
+    a.k = (int)k;
+    a.out_dist = distances;
+    a.out_labels = reinterpret_cast<int64_t*>(labels);
+    a.scratch = region;
+    a.scratch_bytes = align256(scratchBytes);
+    abiCheck(b200f_search(&a), "searchDeviceEnqueue");
+}
+
+void B200IndexFlat::synchronize() const {
+    DeviceGuard g(impl_->res->getDevice());
+    cudaStream_t st = impl_->stream();
+    cudaCheck(cudaMemcpyAsync(impl_->hostStatus, impl_->status, 16, cudaMemcpyDeviceToHost, st),
+              "synchronize: status copy");
+    cudaCheck(cudaStreamSynchronize(st), "synchronize");
+    if (impl_->hostStatus[0] != 0) {
+        impl_->lastStatus = impl_->hostStatus[0];
+        throw std::runtime_error("faiss-b200: search kernel reported device status " +
+                                 std::to_string(impl_->hostStatus[0]));
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // async search
 // ---------------------------------------------------------------------------------------

@@ -144,6 +144,23 @@ int b200f_index_search(const B200FIndex* index, int64_t n, const float* x, int64
     B200F_GUARD_END
 }
 
+int b200f_index_search_enqueue(const B200FIndex* index, int64_t n, const float* x, int64_t k,
+                               float* distances, int64_t* labels) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->searchDeviceEnqueue(n, x, k, distances, reinterpret_cast<faiss::idx_t*>(labels));
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_synchronize(const B200FIndex* index) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->synchronize();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
 int b200f_index_search_async(const B200FIndex* index, int64_t n, const float* x, int64_t k,
                              float* distances, int64_t* labels, B200FToken** out) {
     if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");

@@ -89,6 +89,14 @@ class B200IndexFlat : public faiss::Index {
     void setLabelBase(faiss::idx_t base);
     /// Device pointers of the shard (rows in storage precision).
     const void* getDeviceRows() const;
+    /// Enqueue a search whose queries and outputs are all DEVICE pointers on the resources'
+    /// stream and return without synchronising (single batch: n <= 16384 for k <= 32,
+    /// n <= 1024 otherwise).  The multi-GPU layer chains the candidate exchange and the merge
+    /// behind it on the same stream; call synchronize() before reading results on the host.
+    void searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::idx_t k, float* distances,
+                             faiss::idx_t* labels) const;
+    /// Wait for the resources' stream and throw if a search reported a device-side error.
+    void synchronize() const;
     /// Device status word of the most recent synchronous search (0 = fine).
     int lastDeviceStatus() const;
 

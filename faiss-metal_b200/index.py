@@ -142,6 +142,15 @@ class B200IndexFlat:
                                                 _ptr(distances), _ptr(labels)), "search")
         return distances, labels
 
+    def search_enqueue(self, x, k: int, distances, labels):
+        """Device tensors only; queues the search on the resources' stream without waiting."""
+        n = int(x.shape[0])
+        abi.check(abi.lib().b200f_index_search_enqueue(self._h, n, _ptr(x) if n else None, int(k),
+                                                        _ptr(distances), _ptr(labels)), "search_enqueue")
+
+    def synchronize(self):
+        abi.check(abi.lib().b200f_index_synchronize(self._h), "synchronize")
+
     def search_async(self, x, k: int, distances, labels) -> SearchToken:
         n = int(x.shape[0])
         t = ctypes.c_void_p()

@@ -73,6 +73,52 @@ class ShardedIndexFlat:
             ctypes.c_void_p(stream)), "merge_lists")
         return out_d, out_l
 
+    # -- device path: no allocation, no host synchronisation between the three steps ------
+    def _buffers(self, nq: int, k: int, device):
+        import torch
+        key = (nq, k)
+        b = self._bufs.get(key) if hasattr(self, "_bufs") else None
+        if b is None:
+            if not hasattr(self, "_bufs"):
+                self._bufs = {}
+            dist_bytes = (nq * k * 4 + 15) // 16 * 16
+            rank_bytes = (dist_bytes + nq * k * 8 + 15) // 16 * 16
+            mine = torch.empty(rank_bytes, dtype=torch.uint8, device=device)
+            allb = torch.empty(self.world * rank_bytes, dtype=torch.uint8, device=device)
+            b = {
+                "rank_bytes": rank_bytes, "dist_bytes": dist_bytes, "mine": mine, "all": allb,
+                "d_loc": mine[: nq * k * 4].view(torch.float32).view(nq, k),
+                "l_loc": mine[dist_bytes: dist_bytes + nq * k * 8].view(torch.int64).view(nq, k),
+                "out_d": torch.empty((nq, k), dtype=torch.float32, device=device),
+                "out_l": torch.empty((nq, k), dtype=torch.int64, device=device),
+            }
+            self._bufs[key] = b
+        return b
+
+    def search_device(self, x, k: int, sync: bool = True):
+        """x: fp32 CUDA tensor [nq, d] on this rank's GPU, identical on every rank; torch's current
+        stream must be the resources' stream (wrap it with torch.cuda.ExternalStream).  Shard
+        search, one all-gather of [distances | labels] per rank and the k-way merge are queued
+        back to back; the returned tensors are reused by the next call with the same (nq, k)."""
+        import torch
+        import torch.distributed as dist
+        nq = int(x.shape[0])
+        b = self._buffers(nq, k, x.device)
+        if self.world == 1:
+            self.local.search_enqueue(x, k, b["out_d"], b["out_l"])
+        else:
+            self.local.search_enqueue(x, k, b["d_loc"], b["l_loc"])
+            dist.all_gather_into_tensor(b["all"], b["mine"], group=self.group)
+            base = b["all"].data_ptr()
+            abi.check_op(abi.lib().b200f_merge_lists_strided(
+                ctypes.c_void_p(base), ctypes.c_void_p(base + b["dist_bytes"]),
+                b["rank_bytes"] // 4, b["rank_bytes"] // 8, self.world, nq, k, self.metric_type,
+                ctypes.c_void_p(b["out_d"].data_ptr()), ctypes.c_void_p(b["out_l"].data_ptr()),
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "merge_lists_strided")
+        if sync:
+            self.local.synchronize()
+        return b["out_d"], b["out_l"]
+
     def search(self, x, k: int):
         """x: fp32 queries [nq, d], identical on every rank (torch tensor on this rank's GPU,
         or a CPU tensor / numpy array with a gloo group).  Returns the merged

@@ -206,6 +206,14 @@ int b200f_select_rows(const float* scores, int64_t nq, int64_t ncols, int64_t ld
 int b200f_merge_lists(const float* dist, const int64_t* labels, int P, int64_t nq, int k,
                       int metric, float* out_dist, int64_t* out_labels, void* stream);
 
+/* Same merge for lists that are not packed back to back: list p's distances start at
+ * dist + p * list_stride_dist, its labels at labels + p * list_stride_labels (strides in
+ * elements, each >= nq * k).  Lets the caller all-gather one buffer per rank that holds
+ * [distances | labels] and merge straight out of the gathered buffer. */
+int b200f_merge_lists_strided(const float* dist, const int64_t* labels, int64_t list_stride_dist,
+                              int64_t list_stride_labels, int P, int64_t nq, int k, int metric,
+                              float* out_dist, int64_t* out_labels, void* stream);
+
 /* Deterministic synthetic rows on the device (benchmark inputs): element
  * (row, col) depends only on (seed, row0 + row, col).
  * dist: 0 = U[0,1), 1 = N(0,1) * scale, 2 = N(0,1) then row-normalised.
@@ -250,6 +258,16 @@ int b200f_index_add(B200FIndex* index, int64_t n, const float* x);
  * host or device (src/MetalIndexFlat.mm:313-401). */
 int b200f_index_search(const B200FIndex* index, int64_t n, const float* x, int64_t k,
                        float* distances, int64_t* labels);
+/* Device-only, enqueue-only form of search: x / distances / labels are DEVICE pointers, the
+ * work is queued on the resources' stream (b200f_resources_stream) and the call returns
+ * without synchronising, so a caller can chain its own work (the multi-GPU exchange and
+ * merge) on that stream.  One launch batch only (n <= 16384 for k <= 32, else n <= 1024).
+ * b200f_index_synchronize waits for the stream and reports a device-side error, if any.
+ * The reference's closest relative is the encode-without-wait half of searchAsync
+ * (src/MetalIndexFlat.mm:478-486). */
+int b200f_index_search_enqueue(const B200FIndex* index, int64_t n, const float* x, int64_t k,
+                               float* distances, int64_t* labels);
+int b200f_index_synchronize(const B200FIndex* index);
 /* searchAsync -> token; token wait / isReady / destructor
  * (src/MetalIndexFlat.mm:403-490, :41-78). */
 int b200f_index_search_async(const B200FIndex* index, int64_t n, const float* x, int64_t k,

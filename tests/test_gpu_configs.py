@@ -101,3 +101,45 @@ def test_sharded_emulation_equals_unsharded(fm, res, G, k, storage, metric):
     torch.cuda.synchronize()
     assert np.array_equal(out_l.cpu().numpy(), If)
     assert np.array_equal(out_d.cpu().numpy(), Df)
+
+
+def test_sharded_device_path_single_rank(fm, res):
+    """ShardedIndexFlat.search_device (enqueue-only search + strided merge entry point) against the
+    plain search; world 1 exercises the enqueue path, the strided merge is checked directly."""
+    import torch
+    xb = H.gaussian(30_000, 64, 41, scale=0.05)
+    xq = H.gaussian(50, 64, 42, scale=0.05)
+    idx = fm.B200IndexFlat(res, 64, O.METRIC_L2, 2)
+    idx.add(xb)
+    D, I = idx.search(xq, 10)
+    ext = torch.cuda.ExternalStream(res.stream)
+    with torch.cuda.stream(ext):
+        sh = fm.ShardedIndexFlat(idx, 0, 1)
+        Dd, Id = sh.search_device(torch.from_numpy(xq).cuda(), 10)
+        assert np.array_equal(Id.cpu().numpy(), I) and np.array_equal(Dd.cpu().numpy(), D)
+        # strided merge of two interleaved [distances | labels] rank buffers
+        nq, k = 50, 10
+        dist_bytes = (nq * k * 4 + 15) // 16 * 16
+        rank_bytes = (dist_bytes + nq * k * 8 + 15) // 16 * 16
+        buf = torch.zeros(2 * rank_bytes, dtype=torch.uint8, device="cuda")
+        halves = []
+        for r, (lo, hi) in enumerate([(0, 15_000), (15_000, 30_000)]):
+            s = fm.B200IndexFlat(res, 64, O.METRIC_L2, 2)
+            s.add(xb[lo:hi])
+            s.set_label_base(lo)
+            Ds, Is = s.search(xq, k)
+            halves.append((Ds, Is))
+            off = r * rank_bytes
+            buf[off: off + nq * k * 4].view(torch.float32).copy_(torch.from_numpy(Ds).flatten())
+            buf[off + dist_bytes: off + dist_bytes + nq * k * 8].view(torch.int64).copy_(torch.from_numpy(Is).flatten())
+            s.close()
+        out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+        out_l = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+        fm.abi.check_op(fm.lib().b200f_merge_lists_strided(
+            ctypes.c_void_p(buf.data_ptr()), ctypes.c_void_p(buf.data_ptr() + dist_bytes), rank_bytes // 4,
+            rank_bytes // 8, 2, nq, k, O.METRIC_L2, ctypes.c_void_p(out_d.data_ptr()),
+            ctypes.c_void_p(out_l.data_ptr()), ctypes.c_void_p(ext.cuda_stream)), "merge strided")
+        ext.synchronize()
+        assert np.array_equal(out_l.cpu().numpy(), I) and np.array_equal(out_d.cpu().numpy(), D)
+        del Dd, Id, buf, out_d, out_l, sh
+    idx.close()
