@@ -15,7 +15,7 @@
 //   warps 2-5  epilogue: tcgen05.ld (thread t owns query row t of the tile),
 //              one max per column (the L2 bias -||x||^2/2 is part of the dot product:
 //              8 extra K columns, see rows.cu), threshold filter against the row's current
-//              k-th best, replace-worst insertion into a per-row list in shared memory
+//              k-th best, insertion into a sorted per-row list held in the thread's registers
 // A work item is (query block, column range); every item yields one sorted
 // partial list per query row, merged afterwards by merge_partials.
 //
@@ -266,67 +266,26 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     return desc;
 }
 
-// Per-row candidate list in shared memory (column `row` of lkey/lidx), UNSORTED: the
-// thread keeps the position of its worst entry and overwrites it, then rescans the k
-// entries for the new worst (independent loads, no dependent chain).  "Worst" is the
-// lexicographic maximum of (key, id).  Returns the new worst key; `worst` is updated.
-// Precondition: s < key at `worst` (ids arrive ascending, so an equal key never enters).
-__device__ __noinline__ float list_replace_worst(float* lkey, int32_t* lidx, int row, int k,
-                                                 float s, int32_t id, int& worst) {
-    lkey[worst * BM + row] = s;
-    lidx[worst * BM + row] = id;
-    float mk = lkey[row];
-    int mp = 0;
-    int32_t mi = 0;
-    bool mi_valid = false;
-#pragma unroll 8
-    for (int j = 1; j < k; j++) {
-        const float key = lkey[j * BM + row];
-        if (key > mk) {
-            mk = key;
-            mp = j;
-            mi_valid = false;
-        } else if (key == mk) {
-            if (!mi_valid) {
-                mi = lidx[mp * BM + row];
-                mi_valid = true;
-            }
-            const int32_t ci = lidx[j * BM + row];
-            if ((uint32_t)ci > (uint32_t)mi) {  // empty slots (-1) count as the worst
-                mi = ci;
-                mp = j;
-            }
-        }
-    }
-    worst = mp;
-    return mk;
-}
-
-// Writes the row list best-first: k rounds of "extract the lexicographic minimum".
-__device__ __noinline__ void list_write_sorted(float* lkey, int32_t* lidx, int row, int k,
-                                               float kscale, float* out_key, int32_t* out_idx) {
-    for (int r = 0; r < k; r++) {
-        float bk = lkey[row];
-        int32_t bi = lidx[row];
-        int bp = 0;
-        for (int j = 1; j < k; j++) {
-            const float key = lkey[j * BM + row];
-            if (key < bk) {
-                bk = key;
-                bi = lidx[j * BM + row];
-                bp = j;
-            } else if (key == bk) {
-                const int32_t ci = lidx[j * BM + row];
-                if ((uint32_t)ci < (uint32_t)bi) {
-                    bi = ci;
-                    bp = j;
-                }
-            }
-        }
-        out_key[r] = kscale * bk;  // INF stays INF for empty slots
-        out_idx[r] = bi;
-        lkey[bp * BM + row] = CUDART_INF_F;  // consumed
-        lidx[bp * BM + row] = -1;
+// Per-row candidate list held in REGISTERS by the thread that owns the row: 32 (key, id)
+// pairs sorted ascending by key, every index static so nothing spills.  Inserting s drops
+// the largest element: slot j takes the old slot j-1 if that is greater than s, keeps its
+// value if it is <= s, and takes s otherwise.  Elements equal to s stay in front of it
+// (ids arrive ascending).  For k < 32 the first 32-k slots hold -INF sentinels, so the
+// k-th best key is always slot 31.
+__device__ __forceinline__ void reglist_insert(float (&lk)[KMAX], int32_t (&li)[KMAX], float s,
+                                               int32_t id) {
+    float pk = -CUDART_INF_F;
+    int32_t pi = -1;
+#pragma unroll
+    for (int j = 0; j < KMAX; j++) {
+        const float cur = lk[j];
+        const int32_t ci = li[j];
+        const bool shift = pk > s;
+        const bool keep = cur <= s;
+        lk[j] = shift ? pk : (keep ? cur : s);
+        li[j] = shift ? pi : (keep ? ci : id);
+        pk = cur;
+        pi = ci;
     }
 }
 
@@ -347,8 +306,6 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int64_t unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;  // work is dealt to CTAs / CTA pairs
     const int64_t nunits = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
-    float* lkey = reinterpret_cast<float*>(smem + SM_LKEY);
-    int32_t* lidx = reinterpret_cast<int32_t*>(smem + SM_LIDX);
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + SM_TMEMPTR);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_ABORT);
 
@@ -455,12 +412,25 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
+        // The tensor pipe idles whenever this thread is not issuing, so the loop carries
+        // nothing but the barrier wait, four MMAs and the commit(s) per k-block:
+        // descriptors, barrier addresses and the shape of the last k-block are set up once.
         if (lane == 0 && cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            const uint64_t da0 = make_smem_desc(sbase + SM_A);
+            const uint64_t db0 = make_smem_desc(sbase + SM_B);
+            const uint32_t empty0 = PAIR ? map_to_cta(bar_empty, 0) : bar_empty;
+            const uint32_t empty1 = PAIR ? map_to_cta(bar_empty, 1) : 0;
+            const uint32_t tfull0 = PAIR ? map_to_cta(bar_tfull, 0) : bar_tfull;
+            const uint32_t tfull1 = PAIR ? map_to_cta(bar_tfull, 1) : 0;
+            // the last k-block of a plane product may hold fewer than 64 valid K elements
+            // (TMA zero-fills the rest): skip the all-zero sub-steps
+            const int klast_valid = p.k_extent - (p.kb_per_pass - 1) * BK;
+            const int nk4_last = klast_valid >= BK ? BK / UMMA_K : (klast_valid + UMMA_K - 1) / UMMA_K;
             for (int64_t item = unit; item < nitems && ok; item += nunits) {
                 const int64_t xr = item / p.nqb;
                 const int64_t t0 = xr * p.tiles_per_range;
@@ -472,38 +442,39 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * BN;
+                    int kin = 0;
+                    uint32_t accumulate = 0;
                     for (int kb = 0; kb < kb_total; kb++) {
-                        if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, p.status)) {
+                        if (!mbar_try_wait(bar_full + stage * 8, phase) &&
+                            !mbar_wait(bar_full + stage * 8, phase, abort_flag, p.status)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after();
-                        const uint64_t da = make_smem_desc(sbase + SM_A + stage * A_STAGE_BYTES);
-                        const uint64_t db = make_smem_desc(sbase + SM_B + stage * B_STAGE_BYTES);
-                        // the last k-block of a plane product may hold fewer than 64 valid
-                        // K elements (TMA zero-fills the rest): skip the all-zero sub-steps
-                        const int kin = kb % p.kb_per_pass;
-                        const int kvalid = p.k_extent - kin * BK;
-                        const int nk4 = kvalid >= BK ? BK / UMMA_K : (kvalid + UMMA_K - 1) / UMMA_K;
+                        const uint64_t da = da0 + (uint64_t)(stage * (A_STAGE_BYTES >> 4));
+                        const uint64_t db = db0 + (uint64_t)(stage * (B_STAGE_BYTES >> 4));
+                        const bool last = ++kin == p.kb_per_pass;
+                        if (last) kin = 0;
+                        const int nk4 = last ? nk4_last : BK / UMMA_K;
 #pragma unroll
                         for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
                             // advance 32 bytes (16 elements) along K inside the swizzle row
                             if (k4 < nk4) {
                                 if (PAIR)
                                     tc_mma_f16_pair(d_tmem, da + (uint64_t)(k4 * 2),
-                                                    db + (uint64_t)(k4 * 2), p.idesc,
-                                                    (kb | k4) != 0 ? 1u : 0u);
+                                                    db + (uint64_t)(k4 * 2), p.idesc, accumulate);
                                 else
                                     tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
-                                               p.idesc, (kb | k4) != 0 ? 1u : 0u);
+                                               p.idesc, accumulate);
+                                accumulate = 1;
                             }
                         }
                         // frees the stage (in both CTAs of a pair) when the MMAs retire
                         if (PAIR) {
-                            tc_commit_pair(map_to_cta(bar_empty + stage * 8, 0));
-                            tc_commit_pair(map_to_cta(bar_empty + stage * 8, 1));
+                            tc_commit_pair(empty0 + stage * 8);
+                            tc_commit_pair(empty1 + stage * 8);
                         } else {
-                            tc_commit(bar_empty + stage * 8);
+                            tc_commit(empty0 + stage * 8);
                         }
                         if (++stage == STAGES) {
                             stage = 0;
@@ -512,10 +483,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                     if (!ok) break;
                     if (PAIR) {  // accumulator complete, in both CTAs
-                        tc_commit_pair(map_to_cta(bar_tfull + acc * 8, 0));
-                        tc_commit_pair(map_to_cta(bar_tfull + acc * 8, 1));
+                        tc_commit_pair(tfull0 + acc * 8);
+                        tc_commit_pair(tfull1 + acc * 8);
                     } else {
-                        tc_commit(bar_tfull + acc * 8);
+                        tc_commit(tfull0 + acc * 8);
                     }
                     acc ^= 1;
                     if (acc == 0) acc_phase ^= 1;
@@ -530,6 +501,8 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t acc_phase = 0;
         bool ok = true;
         const int k = p.k;
+        float lk[KMAX];     // this thread's row list (see reglist_insert)
+        int32_t li[KMAX];
         for (int64_t item = unit; item < nitems && ok; item += nunits) {
             const int qb = (int)(item % p.nqb);
             const int64_t xr = item / p.nqb;
@@ -540,12 +513,12 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             float thr = CUDART_INF_F;      // worst key of this thread's list (k-th best of the range)
             float thr_eff = CUDART_INF_F;  // filter: min(thr, bound shared by all ranges of the row)
             float thr_pub = CUDART_INF_F;  // last value published to gthr
-            int worst = 0;
             float radd = 0.f;
             if (p.mode == MODE_TOPK) {
-                for (int j = 0; j < k; j++) {
-                    lkey[j * BM + row] = CUDART_INF_F;
-                    lidx[j * BM + row] = -1;
+#pragma unroll
+                for (int j = 0; j < KMAX; j++) {
+                    lk[j] = (j >= KMAX - k) ? CUDART_INF_F : -CUDART_INF_F;
+                    li[j] = -1;
                 }
             } else if (row_live && p.rowadd) {
                 radd = p.rowadd[grow];
@@ -621,7 +594,8 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                     for (int c = 0; c < 32; c++) bits = (c == cc) ? r[c] : bits;
                                     const float sc = -__uint_as_float(bits);
                                     if (sc < thr_eff) {
-                                        thr = list_replace_worst(lkey, lidx, row, k, sc, id0 + cc, worst);
+                                        reglist_insert(lk, li, sc, id0 + cc);
+                                        thr = lk[KMAX - 1];
                                         thr_eff = fminf(thr_eff, thr);
                                     }
                                 }
@@ -661,8 +635,15 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             if (p.mode == MODE_TOPK && row_live && ok) {
                 if (thr < thr_pub) atomicMin(p.gthr + grow, float_to_ordered(thr));
-                list_write_sorted(lkey, lidx, row, k, p.kscale, p.part_key + (grow * p.P + xr) * k,
-                                  p.part_idx + (grow * p.P + xr) * k);
+                float* okey = p.part_key + (grow * p.P + xr) * k - (KMAX - k);
+                int32_t* oidx = p.part_idx + (grow * p.P + xr) * k - (KMAX - k);
+#pragma unroll
+                for (int j = 0; j < KMAX; j++) {
+                    if (j >= KMAX - k) {
+                        okey[j] = p.kscale * lk[j];  // INF stays INF for empty slots
+                        oidx[j] = li[j];
+                    }
+                }
             }
         }
     }
