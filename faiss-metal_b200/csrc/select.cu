@@ -223,7 +223,12 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
     extern __shared__ __align__(16) uint64_t buf[];  // SS_CAP entries
     __shared__ int s_count;
     __shared__ uint64_t s_thr;
+    __shared__ int s_pending[2];
     const int tid = threadIdx.x;
+    if (tid == 0) {
+        s_pending[0] = 0;
+        s_pending[1] = 0;
+    }
 
     for (int64_t q = blockIdx.x; q < p.nq; q += gridDim.x) {
         __syncthreads();
@@ -232,6 +237,8 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
         if (tid == 0) {
             s_count = 0;
             s_thr = SS_EMPTY;
+            s_pending[0] = 0;
+            s_pending[1] = 0;
         }
         __syncthreads();
         if (p.has_prev) {
@@ -257,7 +264,113 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
         }
 
         const int64_t total = (SRC == SRC_MATRIX) ? p.ncand : (int64_t)p.P * p.k;
-        for (int64_t b0 = 0; b0 < total; b0 += SS_BATCH) {
+        // Wide streaming path (key matrix with 16-byte aligned rows): every thread loads
+        // 8 x float4 = 32 columns up front, counts its hits against the current threshold, and
+        // the CTA appends them after ONE count check per 32,768 columns.  Only when the buffer
+        // could overflow (no threshold yet, or adversarial order) the batch is replayed in
+        // eight 4,096-column steps with a compaction check before each.
+        const bool wide = (SRC == SRC_MATRIX) && ((p.ld & 3) == 0) &&
+                          ((reinterpret_cast<uintptr_t>(p.keys) & 15) == 0);
+        int64_t b_start = 0;
+        if (wide) {
+            constexpr int WV = 8;
+            constexpr int64_t WIDE = (int64_t)SS_THREADS * 4 * WV;
+            const float* rowp = p.keys + q * p.ld;
+            int par = 0;
+            for (int64_t w0 = 0; w0 < total; w0 += WIDE) {
+                float4 v[WV];
+#pragma unroll
+                for (int i = 0; i < WV; i++) {
+                    const int64_t c = w0 + ((int64_t)i * SS_THREADS + tid) * 4;
+                    if (c + 4 <= total) {
+                        v[i] = __ldg(reinterpret_cast<const float4*>(rowp + c));
+                    } else {
+                        float t4[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) t4[e] = (c + e < total) ? __ldg(rowp + c + e) : CUDART_NAN_F;
+                        v[i] = make_float4(t4[0], t4[1], t4[2], t4[3]);
+                    }
+                }
+                const uint64_t thr0 = s_thr;
+                const uint32_t thr_hi = (uint32_t)(thr0 >> 32);
+                uint32_t hits = 0;
+#pragma unroll
+                for (int i = 0; i < WV; i++) {
+                    const float e4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float key = p.key_sign * e4[e];
+                        // NaN (also the out-of-range filler) never qualifies
+                        const bool h = (key == key) && float_to_ordered(key) <= thr_hi;
+                        hits |= (h ? 1u : 0u) << (i * 4 + e);
+                    }
+                }
+                if (hits) atomicAdd(&s_pending[par], __popc(hits));
+                __syncthreads();
+                const int cnt = s_count;
+                const int pend = s_pending[par];
+                // the other counter belongs to the next batch: its last readers are behind the
+                // previous batch's second barrier, its next writers behind the one below
+                if (tid == 0) s_pending[par ^ 1] = 0;
+                __syncthreads();
+                if (cnt + pend <= SS_CAP) {
+                    // fast path: room for every hit
+                    while (hits) {
+                        const int b = __ffs(hits) - 1;
+                        hits &= hits - 1;
+                        const int i = b >> 2, e = b & 3;
+                        float val = 0.f;
+#pragma unroll
+                        for (int ii = 0; ii < WV; ii++) {
+                            const float e4[4] = {v[ii].x, v[ii].y, v[ii].z, v[ii].w};
+#pragma unroll
+                            for (int ee = 0; ee < 4; ee++) val = (ii == i && ee == e) ? e4[ee] : val;
+                        }
+                        const int64_t c = w0 + ((int64_t)i * SS_THREADS + tid) * 4 + e;
+                        const uint64_t w = pack(p.key_sign * val, (uint32_t)(p.col0 + c));
+                        if (w < thr0) {
+                            const int pos = atomicAdd(&s_count, 1);
+                            buf[pos] = w;
+                        }
+                    }
+                } else {
+                    // replay in 4,096-column steps (vector i of every thread), compacting as needed
+#pragma unroll
+                    for (int i = 0; i < WV; i++) {
+                        __syncthreads();
+                        const int cnt2 = s_count;
+                        __syncthreads();
+                        if (cnt2 > SS_CAP - SS_BATCH) {
+                            for (int j = cnt2 + tid; j < SS_CAP; j += SS_THREADS) buf[j] = SS_EMPTY;
+                            bitonic_sort(buf, SS_CAP);
+                            for (int j = p.k + tid; j < SS_CAP; j += SS_THREADS) buf[j] = SS_EMPTY;
+                            if (tid == 0) {
+                                s_count = p.k;
+                                s_thr = buf[p.k - 1];
+                            }
+                            __syncthreads();
+                        }
+                        const uint64_t thr = s_thr;
+                        const float e4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int64_t c = w0 + ((int64_t)i * SS_THREADS + tid) * 4 + e;
+                            const float key = p.key_sign * e4[e];
+                            if (c < total && key == key) {
+                                const uint64_t w = pack(key, (uint32_t)(p.col0 + c));
+                                if (w < thr) {
+                                    const int pos = atomicAdd(&s_count, 1);
+                                    buf[pos] = w;  // at most 4,096 appends per step
+                                }
+                            }
+                        }
+                    }
+                }
+                par ^= 1;
+            }
+            b_start = total;  // everything consumed
+        }
+        for (int64_t b0 = b_start; b0 < total; b0 += SS_BATCH) {
             // Every thread must take the same branch below: read the count between two
             // barriers, so that no thread of the next batch has appended yet.
             __syncthreads();
