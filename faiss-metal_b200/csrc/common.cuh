@@ -93,7 +93,7 @@ struct GemmOperands {
     int64_t nq, nb;
     int d_pad;                 // K extent (multiple of 8), norm columns included
 };
-// Fused top-k (k <= 32): partial lists part_key/part_idx [nq][P][k].
+// Fused top-k (k <= 32): partial lists part_key/part_idx [nq][2 * P][k] (two per column range).
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
                      float kscale, int k, float* part_key, int32_t* part_idx,
                      uint32_t* gthr, int32_t* status, cudaStream_t stream);

@@ -43,8 +43,8 @@ constexpr int BK = 64;  // 16-bit elements: 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int KMAX = B200F_FUSED_MAX_K;
-constexpr int NUM_THREADS = 192;
-constexpr int NUM_EPI_THREADS = 128;
+constexpr int NUM_EPI_WARPS = 8;   // two per TMEM lane quarter: each takes half of the tile's columns
+constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
@@ -55,16 +55,25 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 //                shared-memory fill per FLOP is halved; the MMA is issued by the even CTA.
 template <bool PAIR>
 struct Cfg {
-    static constexpr int STAGES = PAIR ? 6 : 4;
-    static constexpr int B_ROWS = PAIR ? 128 : 256;        // rows of X staged by this CTA
-    static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;  // 16 / 32 KiB
+    static constexpr int STAGES = 4;
+    static constexpr int B_ROWS = PAIR ? 128 : 256;        // rows of X this CTA stages per sub-tile
+    // A dependent chain of MMAs on ONE accumulator runs at about half the tensor rate (each
+    // MMA waits out the read-modify-write turnaround of the one before it); two chains on two
+    // accumulators, issued alternately by the same thread, reach the full rate.  The pair shape
+    // therefore computes two 256-column sub-tiles at once (same query k-block, two X k-blocks,
+    // both TMEM halves); the price is that the epilogue no longer overlaps the next tile's MMAs.
+    static constexpr int NSUB = PAIR ? 2 : 1;              // 256-column sub-tiles per tile
+    static constexpr int TILE_N = NSUB * BN;               // columns of X per tile: 512 / 256
+    static constexpr int ACC_BUFS = PAIR ? 1 : 2;          // TMEM accumulator buffers of TILE_N columns
+    static constexpr int B_SUB_BYTES = B_ROWS * BK * 2;    // 16 / 32 KiB
+    static constexpr int B_STAGE_BYTES = NSUB * B_SUB_BYTES;  // 32 KiB either way
     static constexpr int QB = PAIR ? 256 : 128;            // query rows per work item
     // shared memory map (bytes from the 1024-aligned dynamic base)
     static constexpr int SM_A = 0;
     static constexpr int SM_B = SM_A + STAGES * A_STAGE_BYTES;
     static constexpr int SM_LKEY = SM_B + STAGES * B_STAGE_BYTES;
-    static constexpr int SM_LIDX = SM_LKEY + KMAX * BM * 4;
-    static constexpr int SM_BAR = SM_LIDX + KMAX * BM * 4;
+    // store mode transposes 32 x 32 blocks per epilogue warp here (32 x 33 floats each)
+    static constexpr int SM_BAR = SM_LKEY + ((NUM_EPI_WARPS * 32 * 33 * 4 + 127) / 128) * 128;
     // barriers: full[STAGES] empty[STAGES] tfull[2] tempty[2]
     static constexpr int SM_TMEMPTR = SM_BAR + (2 * STAGES + 4) * 8;
     static constexpr int SM_ABORT = SM_TMEMPTR + 4;
@@ -296,7 +305,8 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
     using C = Cfg<PAIR>;
     constexpr int STAGES = C::STAGES;
     constexpr int B_STAGE_BYTES = C::B_STAGE_BYTES;
-    constexpr int SM_A = C::SM_A, SM_B = C::SM_B, SM_LKEY = C::SM_LKEY, SM_LIDX = C::SM_LIDX;
+    constexpr int TILE_N = C::TILE_N;
+    constexpr int SM_A = C::SM_A, SM_B = C::SM_B, SM_LKEY = C::SM_LKEY;
     constexpr int SM_BAR = C::SM_BAR, SM_TMEMPTR = C::SM_TMEMPTR, SM_ABORT = C::SM_ABORT;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -327,7 +337,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(bar_tfull + s * 8, 1);
-            mbar_init(bar_tempty + s * 8, PAIR ? 8 : 4);  // epilogue warps of one / both CTAs
+            mbar_init(bar_tempty + s * 8, PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);  // epilogue warps of one / both CTAs
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -367,7 +377,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int64_t t0 = xr * p.tiles_per_range;
                 const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
                 for (int64_t t = t0; t < t1 && ok; t++) {
-                    const int xrow = (int)(p.col0 + t * BN);
+                    const int xrow = (int)(p.col0 + t * TILE_N);
                     for (int kb = 0; kb < kb_total; kb++) {
                         if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status)) {
                             ok = false;
@@ -385,8 +395,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                       2 * (A_STAGE_BYTES + B_STAGE_BYTES));
                             tma_load_3d_pair(sbase + SM_A + stage * A_STAGE_BYTES, &tmap_a, fb, kk,
                                              qb * C::QB + (int)cta_rank * BM, pa);
-                            tma_load_3d_pair(sbase + SM_B + stage * B_STAGE_BYTES, &tmap_b, fb, kk,
-                                             xrow + (int)cta_rank * C::B_ROWS, pb);
+#pragma unroll
+                            for (int sub = 0; sub < C::NSUB; sub++)
+                                tma_load_3d_pair(sbase + SM_B + stage * B_STAGE_BYTES + sub * C::B_SUB_BYTES,
+                                                 &tmap_b, fb, kk, xrow + sub * BN + (int)cta_rank * C::B_ROWS, pb);
                         } else {
                             mbar_arrive_expect_tx(bar_full + stage * 8, A_STAGE_BYTES + B_STAGE_BYTES);
                             tma_load_3d(sbase + SM_A + stage * A_STAGE_BYTES, &tmap_a,
@@ -441,7 +453,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const uint32_t d_tmem = tmem_base + acc * TILE_N;
                     int kin = 0;
                     uint32_t accumulate = 0;
                     for (int kb = 0; kb < kb_total; kb++) {
@@ -450,7 +462,6 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             ok = false;
                             break;
                         }
-                        tc_fence_after();
                         const uint64_t da = da0 + (uint64_t)(stage * (A_STAGE_BYTES >> 4));
                         const uint64_t db = db0 + (uint64_t)(stage * (B_STAGE_BYTES >> 4));
                         const bool last = ++kin == p.kb_per_pass;
@@ -460,12 +471,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
                             // advance 32 bytes (16 elements) along K inside the swizzle row
                             if (k4 < nk4) {
-                                if (PAIR)
-                                    tc_mma_f16_pair(d_tmem, da + (uint64_t)(k4 * 2),
-                                                    db + (uint64_t)(k4 * 2), p.idesc, accumulate);
-                                else
+                                if (PAIR) {
+                                    // two independent accumulator chains, issued alternately
+#pragma unroll
+                                    for (int sub = 0; sub < C::NSUB; sub++)
+                                        tc_mma_f16_pair(d_tmem + sub * BN, da + (uint64_t)(k4 * 2),
+                                                        db + (uint64_t)(sub * (C::B_SUB_BYTES >> 4) + k4 * 2),
+                                                        p.idesc, accumulate);
+                                } else {
                                     tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
                                                p.idesc, accumulate);
+                                }
                                 accumulate = 1;
                             }
                         }
@@ -488,14 +504,20 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     } else {
                         tc_commit(tfull0 + acc * 8);
                     }
-                    acc ^= 1;
-                    if (acc == 0) acc_phase ^= 1;
+                    if (C::ACC_BUFS == 2) {
+                        acc ^= 1;
+                        if (acc == 0) acc_phase ^= 1;
+                    } else {
+                        acc_phase ^= 1;
+                    }
                 }
             }
         }
     } else {
         // ------------------------------ epilogue -----------------------------------
         const int ew = warp & 3;              // TMEM lane quarter this warp may read
+        const int eh = (warp - 2) >> 2;       // which half of the tile's columns this warp scans
+        constexpr int CH_PER_HALF = TILE_N / 64;
         const int row = ew * 32 + lane;       // row of the tile owned by this thread
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -524,7 +546,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 radd = p.rowadd[grow];
             }
             for (int64_t t = t0; t < t1 && ok; t++) {
-                const int64_t c_tile = p.col0 + t * BN;
+                const int64_t c_tile = p.col0 + t * TILE_N;
                 {
                     const bool w = mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag, p.status);
                     if (!__all_sync(0xffffffffu, w)) {  // keep the warp converged for tcgen05.ld
@@ -548,10 +570,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // The accumulator holds t = q.x (- ||x||^2/2 for L2): larger is better; the
                 // lists keep s = -t (smaller is better).  Rows of X beyond the last valid
                 // column are zero-filled by TMA (t = 0) and must be masked out.
-                const bool partial = c_tile + BN > p.ncols_end;
-                const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * BN;
+                const bool partial = c_tile + TILE_N > p.ncols_end;
+                const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * TILE_N;
 #pragma unroll 1
-                for (int ch = 0; ch < BN / 32; ch++) {
+                for (int ch = eh * CH_PER_HALF; ch < (eh + 1) * CH_PER_HALF; ch++) {
                     uint32_t r[32];
                     tc_ld32(taddr + ch * 32, r);
                     tc_wait_ld();
@@ -606,7 +628,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         // them directly would touch 32 different rows per instruction.  The warp
                         // transposes the 32 x 32 block through shared memory (the list area is
                         // idle in this mode) and writes one 128-byte row segment per instruction.
-                        float* tbuf = reinterpret_cast<float*>(smem + SM_LKEY) + ew * (32 * 33);
+                        float* tbuf = reinterpret_cast<float*>(smem + SM_LKEY) + (warp - 2) * (32 * 33);
 #pragma unroll
                         for (int c = 0; c < 32; c++) {
                             const float key = -p.kscale * __uint_as_float(r[c]);
@@ -630,13 +652,18 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + acc * 8, 0));
                     else mbar_arrive(bar_tempty + acc * 8);
                 }
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1;
+                if (C::ACC_BUFS == 2) {
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1;
+                } else {
+                    acc_phase ^= 1;
+                }
             }
             if (p.mode == MODE_TOPK && row_live && ok) {
                 if (thr < thr_pub) atomicMin(p.gthr + grow, float_to_ordered(thr));
-                float* okey = p.part_key + (grow * p.P + xr) * k - (KMAX - k);
-                int32_t* oidx = p.part_idx + (grow * p.P + xr) * k - (KMAX - k);
+                // two lists per (row, column range): one per column half
+                float* okey = p.part_key + (grow * (2 * p.P) + 2 * xr + eh) * k - (KMAX - k);
+                int32_t* oidx = p.part_idx + (grow * (2 * p.P) + 2 * xr + eh) * k - (KMAX - k);
 #pragma unroll
                 for (int j = 0; j < KMAX; j++) {
                     if (j >= KMAX - k) {
@@ -830,7 +857,7 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
     const int qb = g.pair ? 2 * BM : BM;
     const int units = g.pair ? max_active_pairs(sm_count) : sm_count;  // CTAs or CTA pairs that run at once
     g.nqb = (int)ceil_div64(nq, qb);
-    g.ntiles = ceil_div64(ncols, BN);
+    g.ntiles = ceil_div64(ncols, g.pair ? Cfg<true>::TILE_N : Cfg<false>::TILE_N);
     if (g.nqb <= 0 || g.ntiles <= 0) {
         g.nqb = 0; g.ntiles = 0; g.P = 0; g.tiles_per_range = 0; g.grid = 0;
         return g;

@@ -79,7 +79,7 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         int64_t P;
         if (pl.path == B200F_PATH_TENSOR) {
             pl.gemm = plan_gemm(nq, nb, sm);
-            P = pl.gemm.P;
+            P = 2 * pl.gemm.P;  // the tensor kernel writes two lists per column range
         } else {
             pl.scan = plan_scan(nq, nb, d, storage, sm);
             // room for either scan kernel: the streaming one writes one list per SM
@@ -354,7 +354,7 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         int32_t* part_idx = reinterpret_cast<int32_t*>(scratch + pl.off_part_idx);
         int P;
         if (pl.path == B200F_PATH_TENSOR) {
-            P = pl.gemm.P;
+            P = 2 * pl.gemm.P;
             rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, a->k, part_key, part_idx,
                                   reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
             if (rc != B200F_OK) return rc;
