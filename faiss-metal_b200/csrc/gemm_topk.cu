@@ -44,7 +44,8 @@ constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int KMAX = B200F_FUSED_MAX_K;
 constexpr int NUM_EPI_WARPS = 8;   // two per TMEM lane quarter: each takes half of the tile's columns
-constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr int MMA2_WARP = 2 + NUM_EPI_WARPS;   // second MMA issuer (pair shape): one thread per accumulator chain
+constexpr int NUM_THREADS = 32 * (3 + NUM_EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
@@ -107,6 +108,7 @@ struct GemmParams {
     float* out;
     int64_t ld;
     int32_t* status;
+    int issuers;         // pair shape: 1 = one thread issues both accumulator chains, 2 = one thread each
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------
@@ -333,10 +335,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         *abort_flag = 0;
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, 1);
+            mbar_init(bar_empty + s * 8, PAIR ? p.issuers : 1);   // one commit per issuing thread
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(bar_tfull + s * 8, 1);
+            mbar_init(bar_tfull + s * 8, PAIR ? p.issuers : 1);
             mbar_init(bar_tempty + s * 8, PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);  // epilogue warps of one / both CTAs
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -422,12 +424,16 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == MMA2_WARP) {
         // ------------------------------ MMA issuer --------------------------------
         // The tensor pipe idles whenever this thread is not issuing, so the loop carries
         // nothing but the barrier wait, four MMAs and the commit(s) per k-block:
         // descriptors, barrier addresses and the shape of the last k-block are set up once.
-        if (lane == 0 && cta_rank == 0) {
+        // One thread sustains about one MMA per 190 cycles, and a chain of MMAs on one
+        // accumulator about one per 290; in the pair shape the two accumulator chains of a tile
+        // are therefore issued by two threads (warp 1: columns 0-255, warp MMA2_WARP: 256-511).
+        const int chain = (warp == 1) ? 0 : 1;
+        if (lane == 0 && cta_rank == 0 && (chain == 0 || (PAIR && p.issuers == 2))) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -472,12 +478,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             // advance 32 bytes (16 elements) along K inside the swizzle row
                             if (k4 < nk4) {
                                 if (PAIR) {
-                                    // two independent accumulator chains, issued alternately
-#pragma unroll
-                                    for (int sub = 0; sub < C::NSUB; sub++)
-                                        tc_mma_f16_pair(d_tmem + sub * BN, da + (uint64_t)(k4 * 2),
-                                                        db + (uint64_t)(sub * (C::B_SUB_BYTES >> 4) + k4 * 2),
+                                    if (p.issuers == 2) {
+                                        tc_mma_f16_pair(d_tmem + chain * BN, da + (uint64_t)(k4 * 2),
+                                                        db + (uint64_t)(chain * (C::B_SUB_BYTES >> 4) + k4 * 2),
                                                         p.idesc, accumulate);
+                                    } else {
+#pragma unroll
+                                        for (int sub = 0; sub < C::NSUB; sub++)
+                                            tc_mma_f16_pair(d_tmem + sub * BN, da + (uint64_t)(k4 * 2),
+                                                            db + (uint64_t)(sub * (C::B_SUB_BYTES >> 4) + k4 * 2),
+                                                            p.idesc, accumulate);
+                                    }
                                 } else {
                                     tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
                                                p.idesc, accumulate);
@@ -513,7 +524,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             }
         }
-    } else {
+    } else if (warp >= 2 && warp < 2 + NUM_EPI_WARPS) {
         // ------------------------------ epilogue -----------------------------------
         const int ew = warp & 3;              // TMEM lane quarter this warp may read
         const int eh = (warp - 2) >> 2;       // which half of the tile's columns this warp scans
@@ -756,6 +767,11 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
     p.P = plan.P;
     p.kb_per_pass = (int)ceil_div64(op.d_pad, BK);
     p.k_extent = op.d_pad;
+    {
+        static int issuers = 0;
+        if (!issuers) { const char* e = getenv("B200F_GEMM_ISSUERS"); issuers = (e && e[0] == '1') ? 1 : 2; }
+        p.issuers = issuers;
+    }
     if (op.npl == 1) {
         p.npass = 1;
         p.pass_a = 0;
