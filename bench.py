@@ -200,7 +200,10 @@ def run_reference(args, w, rank, world):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "desc": w["desc"], "nb": w["nb"], "nq": w["nq"], "d": w["d"],
-                   "k": w["k"], "note": "CPU FAISS is not installed; this is the oracle's sgemm port"},
+                   "k": w["k"], "seeds": {"database": 1, "queries": 2}, "headline": not (args.nb or args.nq),
+                   "note": "the reference's own CPU comparison is CPU FAISS, which is not installed and whose "
+                           "Metal shaders cannot run here; this arm times the oracle's sgemm + partial-select "
+                           "port (the algorithm CPU FAISS uses for query batches) on all host cores"},
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
