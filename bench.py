@@ -172,10 +172,16 @@ def cpu_time_steps(w, steps, warmup):
     import numpy as np
 
     from oracle import flat_oracle as O
+    # torchrun exports OMP_NUM_THREADS=1: give BLAS all host cores back
+    cores = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=cores)
+    except Exception:
+        pass
     nb_s, nq_s = cpu_sample_shape(w)
     xb, xq = cpu_make_data(w, nb_s, nq_s)
     norms = np.einsum("ij,ij->i", xb, xb) if w["metric"] == 1 else None
-    cores = os.cpu_count() or 1
     for _ in range(max(1, warmup)):
         O.blas_search(w["metric"], xb, xq, w["k"], xb_norms=norms)
     t0 = time.perf_counter()
