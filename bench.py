@@ -44,7 +44,7 @@ WORKLOADS = {
                desc="IndexFlatIP FP16 nb=1M nq=10000 d=768 k=100"),
     "c1": dict(nb=100_000, nq=1000, d=128, k=10, storage=0, metric=1, dist=0, scale=1.0,
                desc="IndexFlatL2 FP32 nb=100k nq=1000 d=128 k=10"),
-    "c4": dict(nb=5_000_000, nq=2048, d=96, k=1024, storage=0, metric=1, dist=1, scale=1.0,
+    "c4": dict(nb=5_000_000, nq=2048, d=96, k=1024, storage=0, metric=1, dist=3, scale=0.1,
                desc="IndexFlatL2 FP32 nb=5M nq=2048 d=96 k=1024"),
     "c5": dict(nb=50_000_000, nq=1, d=128, k=10, storage=1, metric=1, dist=0, scale=1.0,
                desc="IndexFlatL2 FP16 nb=50M nq=1 d=128 k=10"),
@@ -155,6 +155,10 @@ def cpu_make_data(w, nb_s, nq_s):
     if w["dist"] == 0:
         xb = rng.random((nb_s, w["d"]), dtype=np.float32)
         xq = rng.random((nq_s, w["d"]), dtype=np.float32)
+    elif w["dist"] == 3:
+        centres = rng.uniform(-1.0, 1.0, size=(1000, w["d"])).astype(np.float32)
+        xb = centres[rng.integers(0, 1000, size=nb_s)] + np.float32(w["scale"]) * rng.standard_normal((nb_s, w["d"]), dtype=np.float32)
+        xq = centres[rng.integers(0, 1000, size=nq_s)] + np.float32(w["scale"]) * rng.standard_normal((nq_s, w["d"]), dtype=np.float32)
     else:
         xb = rng.standard_normal((nb_s, w["d"]), dtype=np.float32)
         xq = rng.standard_normal((nq_s, w["d"]), dtype=np.float32)

@@ -92,10 +92,13 @@ struct GemmOperands {
     int is_bf16;               // element format of both operands
     int64_t nq, nb;
     int d_pad;                 // K extent (multiple of 8), norm columns included
+    const int* nq_dev;         // optional: live rows of A (<= nq) left in device memory by a kernel
 };
 // Fused top-k (k <= 32): partial lists part_key/part_idx [nq][2 * P][k] (two per column range).
+// gthr holds nq * gslots words; with gslots = s the shared filter bounds the (32 * s)-th best
+// key of a row, so lists of k = 32 entries can feed a later selection of up to 32 * s results.
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                     float kscale, int k, float* part_key, int32_t* part_idx,
+                     float kscale, int k, int gslots, float* part_key, int32_t* part_idx,
                      uint32_t* gthr, int32_t* status, cudaStream_t stream);
 // Store mode: out[row*ld + (col-col0)] = sign*(-kscale*t) + rowadd[row], t = q.x (- ||x||^2/2).
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
@@ -110,12 +113,29 @@ int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P,
                           int64_t* out_labels, cudaStream_t stream);
 // Running top-k over a key matrix chunk: run lists [nq][k] (key, int32 id) are read
 // (if has_prev) and rewritten with the best k of (previous list U chunk columns).
+// nq_dev (optional): number of live rows, read on the device.
 int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int64_t col0,
-                        int k, int has_prev, float* run_key, int32_t* run_idx, int32_t* status,
+                        int k, int has_prev, float* run_key, int32_t* run_idx, const int* nq_dev,
                         cudaStream_t stream);
+// row_map (optional): list j belongs to query row_map[j] (output row and query norm).
 int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t nq, int k,
                           int metric, const float* qnorm, int64_t label_base, float* out_dist,
-                          int64_t* out_labels, cudaStream_t stream);
+                          int64_t* out_labels, const int* nq_dev, const int32_t* row_map,
+                          cudaStream_t stream);
+// Selection of k > 32 results from nlists sorted 32-entry lists per query (the fused kernel's
+// output).  A list that is full may have dropped candidates; when its worst entry is not
+// behind the k-th selected one the row's result is not proven exact and dirty[q] is set to 1
+// (else 0).  Results are written for every row.
+int launch_select_parts(const float* part_key, const int32_t* part_idx, int nlists, int64_t nq,
+                        int k, int metric, const float* qnorm, int64_t label_base, float* out_dist,
+                        int64_t* out_labels, int32_t* dirty, cudaStream_t stream);
+// rows[0 .. *count) = ascending indices q with dirty[q] != 0; *count also goes to *count_copy.
+int launch_compact_rows(const int32_t* dirty, int64_t nq, int32_t* rows, int32_t* count,
+                        int32_t* count_copy, cudaStream_t stream);
+// out[pl][j][:] = a[pl][rows[j]][:] for j < *count (16-bit elements, pitch a multiple of 8).
+int launch_gather_rows(const uint16_t* a, int npl, int64_t plane_stride, int64_t pitch,
+                       const int32_t* rows, const int32_t* count, int64_t nq_max, uint16_t* out,
+                       cudaStream_t stream);
 
 int cached_sm_count();
 

@@ -104,7 +104,10 @@ struct GemmParams {
     const float* rowadd; // per query row, may be null (0)
     float* part_key;
     int32_t* part_idx;
-    uint32_t* gthr;      // per query row: ordered-float upper bound of the k-th best key so far
+    uint32_t* gthr;      // [nq][gslots] ordered-float 32nd-best keys published by the lists of a row
+    int gslots;          // lists publish to slot (list number % gslots); the row's bound is the
+                         // largest slot: gslots full lists hold 32 * gslots distinct candidates
+    const int* nq_dev;   // when set: the number of live query rows is read from device memory
     float* out;
     int64_t ld;
     int32_t* status;
@@ -364,7 +367,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
 
-    const int64_t nitems = (int64_t)p.nqb * p.P;
+    // live query rows: known to the host, or left in device memory by an earlier kernel
+    const int64_t nq_live = p.nq_dev ? min((int64_t)*p.nq_dev, p.nq) : p.nq;
+    const int nqb = p.nq_dev ? (int)((nq_live + C::QB - 1) / C::QB) : p.nqb;
+    const int64_t nitems = (int64_t)nqb * p.P;
     const int kb_total = p.kb_per_pass * p.npass;
 
     if (warp == 0) {
@@ -374,8 +380,8 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t phase = 0;
             bool ok = true;
             for (int64_t item = unit; item < nitems && ok; item += nunits) {
-                const int qb = (int)(item % p.nqb);
-                const int64_t xr = item / p.nqb;
+                const int qb = (int)(item % nqb);
+                const int64_t xr = item / nqb;
                 const int64_t t0 = xr * p.tiles_per_range;
                 const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
                 for (int64_t t = t0; t < t1 && ok; t++) {
@@ -450,7 +456,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int klast_valid = p.k_extent - (p.kb_per_pass - 1) * BK;
             const int nk4_last = klast_valid >= BK ? BK / UMMA_K : (klast_valid + UMMA_K - 1) / UMMA_K;
             for (int64_t item = unit; item < nitems && ok; item += nunits) {
-                const int64_t xr = item / p.nqb;
+                const int64_t xr = item / nqb;
                 const int64_t t0 = xr * p.tiles_per_range;
                 const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
                 for (int64_t t = t0; t < t1 && ok; t++) {
@@ -537,12 +543,14 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         float lk[KMAX];     // this thread's row list (see reglist_insert)
         int32_t li[KMAX];
         for (int64_t item = unit; item < nitems && ok; item += nunits) {
-            const int qb = (int)(item % p.nqb);
-            const int64_t xr = item / p.nqb;
+            const int qb = (int)(item % nqb);
+            const int64_t xr = item / nqb;
             const int64_t t0 = xr * p.tiles_per_range;
             const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
             const int64_t grow = (int64_t)qb * C::QB + (int64_t)cta_rank * BM + row;
-            const bool row_live = grow < p.nq;
+            const bool row_live = grow < nq_live;
+            // slot of the row's bound array this list publishes to
+            uint32_t* const gslot = p.gthr ? p.gthr + grow * p.gslots + (int)((2 * xr + eh) % p.gslots) : nullptr;
             float thr = CUDART_INF_F;      // worst key of this thread's list (k-th best of the range)
             float thr_eff = CUDART_INF_F;  // filter: min(thr, bound shared by all ranges of the row)
             float thr_pub = CUDART_INF_F;  // last value published to gthr
@@ -567,14 +575,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 tc_fence_after();
                 if (p.mode == MODE_TOPK && row_live) {
-                    // Any range's k-th best key bounds the row's global k-th best from above:
-                    // publish ours, adopt the smallest seen.  A key equal to the bound may
-                    // still win a tie on the id, so the filter admits s <= bound.
+                    // A full list's worst key bounds the row's 32nd best from above; the largest
+                    // of gslots such keys (distinct lists) bounds the (32 * gslots)-th best, which
+                    // is at or beyond the k-th.  Publish ours, adopt the bound.  A key equal to
+                    // the bound may still win a tie on the id, so the filter admits s <= bound.
                     if (thr < thr_pub) {
-                        atomicMin(p.gthr + grow, float_to_ordered(thr));
+                        atomicMin(gslot, float_to_ordered(thr));
                         thr_pub = thr;
                     }
-                    const uint32_t g = *reinterpret_cast<volatile uint32_t*>(p.gthr + grow);
+                    uint32_t g = 0;
+                    for (int sidx = 0; sidx < p.gslots; sidx++)
+                        g = max(g, __ldcg(p.gthr + grow * p.gslots + sidx));
                     const float gnext = (g >= 0xff800000u) ? CUDART_INF_F : ordered_to_float(g + 1u);
                     thr_eff = fminf(thr, gnext);
                 }
@@ -652,7 +663,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 8
                         for (int rr = 0; rr < 32; rr++) {
                             const float v = tbuf[rr * 33 + lane];
-                            if (col_ok && grow0 + rr < p.nq) obase[(grow0 + rr) * p.ld] = v;
+                            if (col_ok && grow0 + rr < nq_live) obase[(grow0 + rr) * p.ld] = v;
                         }
                         __syncwarp();
                     }
@@ -671,7 +682,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             }
             if (p.mode == MODE_TOPK && row_live && ok) {
-                if (thr < thr_pub) atomicMin(p.gthr + grow, float_to_ordered(thr));
+                if (thr < thr_pub) atomicMin(gslot, float_to_ordered(thr));
                 // two lists per (row, column range): one per column half
                 float* okey = p.part_key + (grow * (2 * p.P) + 2 * xr + eh) * k - (KMAX - k);
                 int32_t* oidx = p.part_idx + (grow * (2 * p.P) + 2 * xr + eh) * k - (KMAX - k);
@@ -759,6 +770,7 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
     if (rc != B200F_OK) return rc;
 
     p.nq = op.nq;
+    p.nq_dev = op.nq_dev;
     p.col0 = col0;
     p.ncols_end = col0 + ncols;
     p.ntiles = plan.ntiles;
@@ -904,14 +916,15 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
 }
 
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                     float kscale, int k, float* part_key, int32_t* part_idx,
+                     float kscale, int k, int gslots, float* part_key, int32_t* part_idx,
                      uint32_t* gthr, int32_t* status, cudaStream_t stream) {
-    if (k <= 0 || k > KMAX) return B200F_ERR_UNSUPPORTED;
+    if (k <= 0 || k > KMAX || gslots < 1) return B200F_ERR_UNSUPPORTED;
     if (!gthr) return B200F_ERR_BAD_ARG;
     // all-ones is above every ordered float: no bound yet
-    B200F_CUDA_TRY(cudaMemsetAsync(gthr, 0xff, (size_t)op.nq * sizeof(uint32_t), stream));
+    B200F_CUDA_TRY(cudaMemsetAsync(gthr, 0xff, (size_t)op.nq * gslots * sizeof(uint32_t), stream));
     GemmParams p{};
     p.mode = MODE_TOPK;
+    p.gslots = gslots;
     p.k = k;
     p.kscale = kscale;
     p.sign = 1.f;

@@ -302,6 +302,13 @@ __global__ void fill_synthetic_kernel(float* __restrict__ dst, int64_t n, int d,
             s = warp_sum(s);
             const float inv = s > 0.f ? rsqrtf(s) : 0.f;
             for (int j = lane; j < d; j += 32) row[j] = synth_value(seed, row0 + r, j, 1) * inv;
+        } else if (dist == 3) {
+            // mixture of 1,000 gaussians: the centres (uniform in [-1,1]^d) are the same for
+            // every seed, so that rows and queries of different seeds share them
+            const uint64_t c = mix64(seed * 0x9e3779b97f4a7c15ULL + (uint64_t)(row0 + r) * 0xd1342543de82ef95ULL) % 1000u;
+            for (int j = lane; j < d; j += 32)
+                row[j] = 2.f * synth_value(0x6d697874ULL, (int64_t)c, j, 0) - 1.f +
+                         scale * synth_value(seed, row0 + r, j, 1);
         } else {
             for (int j = lane; j < d; j += 32)
                 row[j] = synth_value(seed, row0 + r, j, dist) * (dist == 1 ? scale : 1.f);
@@ -436,7 +443,7 @@ extern "C" int b200f_load_rows(const void* rows, int storage, int64_t n, int d, 
 
 extern "C" int b200f_fill_synthetic(float* dst, int64_t n, int d, int64_t row0, uint64_t seed,
                                     int dist, float scale, void* stream) {
-    if (n < 0 || d <= 0 || dist < 0 || dist > 2 || (n > 0 && !dst)) return B200F_ERR_BAD_ARG;
+    if (n < 0 || d <= 0 || dist < 0 || dist > 3 || (n > 0 && !dst)) return B200F_ERR_BAD_ARG;
     if (n == 0) return B200F_OK;
     fill_synthetic_kernel<<<grid_for_rows(n), ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
             dst, n, d, row0, seed, dist, scale);

@@ -6,8 +6,13 @@
 //   nq <= 4            streaming scan (scan.cu)
 //   nq  > 4            tensor-core GEMM (gemm_topk.cu)
 //   k  <= 32           top-k fused into the distance kernel, partial lists merged after
-//   k   > 32           distance keys written per column chunk, running sort-select
+//   32 < k <= 1024     (tensor path, enough column ranges) the fused kernel keeps 32 entries
+//                      per list, the k best of all lists are selected, and a row is redone
+//                      through the key matrix only when a full list could have dropped one of
+//                      its k results (rows counted and compacted on the device, no host sync)
+//   k   > 32 otherwise distance keys written per column chunk, running sort-select
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <utility>
@@ -38,6 +43,8 @@ std::mutex g_prof_mu;
 struct SearchPlan {
     int path;         // B200F_PATH_SCAN or B200F_PATH_TENSOR
     bool fused;       // k <= 32
+    bool lists;       // k > 32 selected from the fused kernel's 32-entry lists, matrix fallback per row
+    int gslots;       // words per query row in the shared bound array
     int npl;
     int64_t a_pitch, a_plane_stride;
     GemmPlan gemm;    // tensor path (fused: whole shard; chunked: per chunk)
@@ -45,8 +52,19 @@ struct SearchPlan {
     int64_t chunk_cols;
     int64_t ngroups;  // scan path: query groups of SCAN_GROUP
     size_t off_qnorm, off_gthr, off_a, off_part_key, off_part_idx, off_matrix, off_run_key, off_run_idx;
+    size_t off_dirty, off_rows, off_count, off_a2;
     size_t total;
 };
+
+// B200F_NO_LISTS=1 in the environment sends every k > 32 search through the key matrix (testing).
+bool lists_disabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200F_NO_LISTS");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
 
 bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool pairwise,
                SearchPlan& pl) {
@@ -64,8 +82,18 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     size_t off = 0;
     pl.off_qnorm = off;
     off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+    pl.gslots = 1;
+    if (!pl.fused && !pairwise && pl.path == B200F_PATH_TENSOR && k <= B200F_LIST_MAX_K &&
+        !lists_disabled()) {
+        // lists must be able to hold the result four times over, else the fallback would be the rule
+        const GemmPlan g = plan_gemm(nq, nb, sm);
+        if ((int64_t)2 * g.P * B200F_FUSED_MAX_K >= 4 * (int64_t)k) {
+            pl.lists = true;
+            pl.gslots = (k + B200F_FUSED_MAX_K - 1) / B200F_FUSED_MAX_K;
+        }
+    }
     pl.off_gthr = off;
-    off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+    off += align256((size_t)(nq > 0 ? nq : 1) * pl.gslots * 4);
     if (pl.path == B200F_PATH_TENSOR) {
         pl.off_a = off;
         off += align256((size_t)pl.npl * pl.a_plane_stride * 2);
@@ -75,7 +103,8 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         pl.total = off;
         return true;
     }
-    if (pl.fused) {
+    if (pl.fused || pl.lists) {
+        const int kl = pl.fused ? k : B200F_FUSED_MAX_K;  // entries per list
         int64_t P;
         if (pl.path == B200F_PATH_TENSOR) {
             pl.gemm = plan_gemm(nq, nb, sm);
@@ -87,17 +116,28 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         }
         if (P < 1) P = 1;
         pl.off_part_key = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * P * k * 4);
+        off += align256((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
         pl.off_part_idx = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * P * k * 4);
-    } else {
+        off += align256((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
+    }
+    if (pl.lists) {
+        pl.off_dirty = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+        pl.off_rows = off;
+        off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+        pl.off_count = off;
+        off += 256;
+        pl.off_a2 = off;
+        off += align256((size_t)pl.npl * pl.a_plane_stride * 2);
+    }
+    if (!pl.fused) {
         int64_t cols = MATRIX_BUDGET_BYTES / (4 * (nq > 0 ? nq : 1));
         cols &= ~(int64_t)255;
         if (cols < 1024) cols = 1024;
         const int64_t nb_pad = round_up64(nb > 0 ? nb : 1, 256);
         if (cols > nb_pad) cols = nb_pad;
         pl.chunk_cols = cols;
-        pl.gemm = plan_gemm(nq, cols, sm);
+        if (!pl.lists) pl.gemm = plan_gemm(nq, cols, sm);
         pl.off_matrix = off;
         off += align256((size_t)(nq > 0 ? nq : 1) * cols * 4);
         pl.off_run_key = off;
@@ -355,7 +395,7 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         int P;
         if (pl.path == B200F_PATH_TENSOR) {
             P = 2 * pl.gemm.P;
-            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, a->k, part_key, part_idx,
+            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, a->k, 1, part_key, part_idx,
                                   reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
@@ -375,6 +415,35 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         }
         return launch_merge_partials(part_key, part_idx, P, a->nq, a->k, a->metric, qnorm,
                                      a->label_base, a->out_dist, a->out_labels, st);
+    }
+
+    // k > 32 from 32-entry lists: select, find the rows that are not proven exact, and send only
+    // those (gathered into a second query operand, counted on the device) through the key matrix
+    const int* nq_dev = nullptr;
+    const int32_t* row_map = nullptr;
+    if (pl.lists) {
+        float* part_key = reinterpret_cast<float*>(scratch + pl.off_part_key);
+        int32_t* part_idx = reinterpret_cast<int32_t*>(scratch + pl.off_part_idx);
+        int32_t* dirty = reinterpret_cast<int32_t*>(scratch + pl.off_dirty);
+        int32_t* rows = reinterpret_cast<int32_t*>(scratch + pl.off_rows);
+        int32_t* count = reinterpret_cast<int32_t*>(scratch + pl.off_count);
+        uint16_t* a2 = reinterpret_cast<uint16_t*>(scratch + pl.off_a2);
+        rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, B200F_FUSED_MAX_K, pl.gslots, part_key,
+                              part_idx, reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
+        if (rc != B200F_OK) return rc;
+        rc = launch_select_parts(part_key, part_idx, 2 * pl.gemm.P, a->nq, a->k, a->metric, qnorm,
+                                 a->label_base, a->out_dist, a->out_labels, dirty, st);
+        if (rc != B200F_OK) return rc;
+        // the number of redone rows is left in status word 1 for whoever wants to know
+        rc = launch_compact_rows(dirty, a->nq, rows, count, a->status ? a->status + 1 : nullptr, st);
+        if (rc != B200F_OK) return rc;
+        rc = launch_gather_rows(op.a_planes, op.npl, op.a_plane_stride, op.a_pitch, rows, count, a->nq,
+                                a2, st);
+        if (rc != B200F_OK) return rc;
+        op.a_planes = a2;
+        op.nq_dev = count;
+        nq_dev = count;
+        row_map = rows;
     }
 
     // k > 32: distance keys per column chunk + running selection
@@ -400,12 +469,12 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
             }
         }
         rc = launch_select_chunk(matrix, a->nq, nc, pl.chunk_cols, c0, a->k, has_prev, run_key,
-                                 run_idx, a->status, st);
+                                 run_idx, nq_dev, st);
         if (rc != B200F_OK) return rc;
         has_prev = 1;
     }
     return launch_finalize_lists(run_key, run_idx, a->nq, a->k, a->metric, qnorm, a->label_base,
-                                 a->out_dist, a->out_labels, st);
+                                 a->out_dist, a->out_labels, nq_dev, row_map, st);
 }
 
 extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64_t ld_out) {

@@ -165,11 +165,12 @@ constexpr int SS_ITEMS = 4;
 constexpr int SS_BATCH = SS_THREADS * SS_ITEMS;  // 4096 candidates per batch
 constexpr uint64_t SS_EMPTY = ~0ull;
 
-enum { SRC_MATRIX = 0, SRC_LISTS = 1 };
+enum { SRC_MATRIX = 0, SRC_LISTS = 1, SRC_PARTS = 2 };
 
 struct SortSelectParams {
     // SRC_MATRIX: keys[q*ld + c], c in [0, ncand); payload = col0 + c
     // SRC_LISTS : keys[(l*nq + q)*k + j] over l in [0, P); payload = l*k + j; labels != -1 live
+    // SRC_PARTS : keys[(q*P + l)*32 + j], ids part_idx[same] (-1 = empty); payload = id
     const float* keys;
     const int64_t* labels;
     int64_t ld;
@@ -179,6 +180,9 @@ struct SortSelectParams {
     int64_t list_stride_l;   // SRC_LISTS: elements between consecutive lists in labels
     int P;
     int64_t nq;
+    const int* nq_dev;    // optional: live rows (<= nq), read on the device
+    const int32_t* part_idx;  // SRC_PARTS
+    int32_t* dirty;       // SRC_PARTS: per row, 1 when a full list might have dropped a result
     int k;
     float key_sign;       // key = key_sign * input
     int has_prev;
@@ -230,7 +234,8 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
         s_pending[1] = 0;
     }
 
-    for (int64_t q = blockIdx.x; q < p.nq; q += gridDim.x) {
+    const int64_t nq_live = p.nq_dev ? min((int64_t)*p.nq_dev, p.nq) : p.nq;
+    for (int64_t q = blockIdx.x; q < nq_live; q += gridDim.x) {
         __syncthreads();
         // the buffer is not cleared up front: slots past the live count are set to EMPTY
         // right before each sort that would read them
@@ -263,7 +268,8 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
             __syncthreads();
         }
 
-        const int64_t total = (SRC == SRC_MATRIX) ? p.ncand : (int64_t)p.P * p.k;
+        const int64_t total = (SRC == SRC_MATRIX) ? p.ncand
+                              : (SRC == SRC_LISTS) ? (int64_t)p.P * p.k : (int64_t)p.P * 32;
         // Wide streaming path (key matrix with 16-byte aligned rows): every thread loads
         // 8 x float4 = 32 columns up front, counts its hits against the current threshold, and
         // the CTA appends them after ONE count check per 32,768 columns.  Only when the buffer
@@ -398,6 +404,12 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                     if (SRC == SRC_MATRIX) {
                         key = p.key_sign * __ldg(p.keys + q * p.ld + c);
                         payload = (uint32_t)(p.col0 + c);
+                    } else if (SRC == SRC_PARTS) {
+                        const int64_t off = q * (int64_t)p.P * 32 + c;
+                        const int32_t id = __ldg(p.part_idx + off);
+                        key = p.key_sign * __ldg(p.keys + off);
+                        live = id >= 0;
+                        payload = (uint32_t)id;
                     } else {
                         const int64_t l = c / p.k;
                         const int64_t j = c - l * p.k;
@@ -434,7 +446,7 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                 if (live) {
                     dist = p.out_sign * key + (p.qnorm ? p.qnorm[q] : 0.f);
                     if (p.clamp && dist < 0.f) dist = 0.f;
-                    if (SRC == SRC_MATRIX) {
+                    if (SRC != SRC_LISTS) {
                         label = (int64_t)payload + p.label_base;
                     } else {
                         const int64_t l = payload / p.k;
@@ -448,6 +460,64 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                 p.run_key[q * p.k + j] = live ? key : CUDART_INF_F;
                 p.run_idx[q * p.k + j] = live ? (int32_t)payload : -1;
             }
+        }
+        if (SRC == SRC_PARTS && p.dirty) {
+            // Entries a list dropped sort behind its worst kept entry.  They cannot belong to
+            // the result when that entry itself sorts behind the k-th selected candidate.
+            const uint64_t kth = (s_count >= p.k) ? buf[p.k - 1] : SS_EMPTY;
+            int bad = 0;
+            for (int l = tid; l < p.P; l += SS_THREADS) {
+                const int64_t off = (q * (int64_t)p.P + l) * 32 + 31;
+                const int32_t id = __ldg(p.part_idx + off);
+                if (id >= 0 && pack(p.key_sign * __ldg(p.keys + off), (uint32_t)id) <= kth) bad = 1;
+            }
+            bad = __syncthreads_or(bad);
+            if (tid == 0) p.dirty[q] = bad ? 1 : 0;
+        }
+    }
+}
+
+// rows[0 .. n) = ascending q with flag[q] != 0, n -> *count (one CTA)
+__global__ void __launch_bounds__(1024) compact_rows_kernel(const int32_t* __restrict__ flag, int64_t nq,
+                                                            int32_t* __restrict__ rows,
+                                                            int32_t* __restrict__ count,
+                                                            int32_t* __restrict__ count_copy) {
+    __shared__ int s_warp[32];
+    __shared__ int s_base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+    for (int64_t q0 = 0; q0 < nq; q0 += 1024) {
+        const int64_t q = q0 + tid;
+        const bool f = q < nq && flag[q] != 0;
+        const unsigned b = __ballot_sync(FULL, f);
+        if (lane == 0) s_warp[warp] = __popc(b);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; w++) before += s_warp[w];
+        const int base = s_base;
+        if (f) rows[base + before + __popc(b & ((1u << lane) - 1u))] = (int32_t)q;
+        __syncthreads();
+        if (tid == 1023) s_base = base + before + __popc(b);
+        __syncthreads();
+    }
+    if (tid == 0) {
+        *count = s_base;
+        if (count_copy) *count_copy = s_base;
+    }
+}
+
+__global__ void gather_rows_kernel(const uint16_t* __restrict__ a, int npl, int64_t plane_stride,
+                                   int64_t pitch, const int32_t* __restrict__ rows,
+                                   const int32_t* __restrict__ count, uint16_t* __restrict__ out) {
+    const int n = *count;
+    const int64_t vec_per_row = pitch / 8;  // 16-byte vectors
+    for (int64_t j = blockIdx.x; j < n; j += gridDim.x) {
+        const int64_t src = rows[j];
+        for (int pl = 0; pl < npl; pl++) {
+            const uint4* s4 = reinterpret_cast<const uint4*>(a + pl * plane_stride + src * pitch);
+            uint4* d4 = reinterpret_cast<uint4*>(out + pl * plane_stride + j * pitch);
+            for (int64_t v = threadIdx.x; v < vec_per_row; v += blockDim.x) d4[v] = s4[v];
         }
     }
 }
@@ -466,6 +536,8 @@ int launch_sort_select(const SortSelectParams& p, cudaStream_t stream) {
     int64_t g = p.nq;
     const int64_t cap = (int64_t)cached_sm_count() * 2 * 8;
     if (g > cap) g = cap;
+    // rows counted on the device are usually few or none: idle CTAs leave at once
+    if (p.nq_dev && g > cached_sm_count()) g = cached_sm_count();
     sort_select_kernel<SRC><<<(int)g, SS_THREADS, smem, stream>>>(p);
     count_launch();
     B200F_LAUNCH_CHECK();
@@ -476,21 +548,25 @@ __global__ void finalize_lists_kernel(const float* __restrict__ run_key,
                                       const int32_t* __restrict__ run_idx, int64_t nq, int k,
                                       float out_sign, const float* __restrict__ qnorm, int clamp,
                                       float pad, int64_t label_base, float* __restrict__ out_dist,
-                                      int64_t* __restrict__ out_labels) {
+                                      int64_t* __restrict__ out_labels,
+                                      const int* __restrict__ nq_dev,
+                                      const int32_t* __restrict__ row_map) {
+    if (nq_dev) nq = min((int64_t)*nq_dev, nq);
     const int64_t total = nq * k;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t q = i / k;
+        const int64_t qo = row_map ? (int64_t)row_map[q] : q;  // output row
         const int32_t id = run_idx[i];
         float dist = pad;
         int64_t label = -1;
         if (id >= 0) {
-            dist = out_sign * run_key[i] + (qnorm ? qnorm[q] : 0.f);
+            dist = out_sign * run_key[i] + (qnorm ? qnorm[qo] : 0.f);
             if (clamp && dist < 0.f) dist = 0.f;
             label = (int64_t)id + label_base;
         }
-        out_dist[i] = dist;
-        out_labels[i] = label;
+        out_dist[qo * k + (i - q * k)] = dist;
+        out_labels[qo * k + (i - q * k)] = label;
     }
 }
 
@@ -529,10 +605,10 @@ int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P,
 }
 
 int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int64_t col0,
-                        int k, int has_prev, float* run_key, int32_t* run_idx, int32_t* status,
+                        int k, int has_prev, float* run_key, int32_t* run_idx, const int* nq_dev,
                         cudaStream_t stream) {
-    (void)status;
     SortSelectParams p{};
+    p.nq_dev = nq_dev;
     p.keys = keys;
     p.ld = ld;
     p.ncand = ncols;
@@ -547,9 +623,55 @@ int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld
     return launch_sort_select<SRC_MATRIX>(p, stream);
 }
 
+int launch_select_parts(const float* part_key, const int32_t* part_idx, int nlists, int64_t nq,
+                        int k, int metric, const float* qnorm, int64_t label_base, float* out_dist,
+                        int64_t* out_labels, int32_t* dirty, cudaStream_t stream) {
+    if (nlists < 1 || (int64_t)nlists * 32 > 0x7fffffffLL) return B200F_ERR_UNSUPPORTED;
+    const bool l2 = metric == B200F_METRIC_L2;
+    SortSelectParams p{};
+    p.keys = part_key;
+    p.part_idx = part_idx;
+    p.P = nlists;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = 1.f;
+    p.has_prev = 0;
+    p.out_sign = l2 ? 1.f : -1.f;
+    p.qnorm = l2 ? qnorm : nullptr;
+    p.clamp = l2 ? 1 : 0;
+    p.pad = l2 ? kHostInf : -kHostInf;
+    p.label_base = label_base;
+    p.out_dist = out_dist;
+    p.out_labels = out_labels;
+    p.dirty = dirty;
+    return launch_sort_select<SRC_PARTS>(p, stream);
+}
+
+int launch_compact_rows(const int32_t* dirty, int64_t nq, int32_t* rows, int32_t* count,
+                        int32_t* count_copy, cudaStream_t stream) {
+    if (nq <= 0) return B200F_OK;
+    compact_rows_kernel<<<1, 1024, 0, stream>>>(dirty, nq, rows, count, count_copy);
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+int launch_gather_rows(const uint16_t* a, int npl, int64_t plane_stride, int64_t pitch,
+                       const int32_t* rows, const int32_t* count, int64_t nq_max, uint16_t* out,
+                       cudaStream_t stream) {
+    if (nq_max <= 0) return B200F_OK;
+    if ((pitch % 8) != 0 || (plane_stride % 8) != 0) return B200F_ERR_BAD_ARG;
+    int64_t g = nq_max < 2 * (int64_t)cached_sm_count() ? nq_max : 2 * (int64_t)cached_sm_count();
+    gather_rows_kernel<<<(int)g, 128, 0, stream>>>(a, npl, plane_stride, pitch, rows, count, out);
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
 int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t nq, int k,
                           int metric, const float* qnorm, int64_t label_base, float* out_dist,
-                          int64_t* out_labels, cudaStream_t stream) {
+                          int64_t* out_labels, const int* nq_dev, const int32_t* row_map,
+                          cudaStream_t stream) {
     if (nq <= 0) return B200F_OK;
     const bool l2 = metric == B200F_METRIC_L2;
     int64_t g = ceil_div64(nq * k, 256);
@@ -558,7 +680,7 @@ int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t 
     finalize_lists_kernel<<<(int)g, 256, 0, stream>>>(run_key, run_idx, nq, k, l2 ? 1.f : -1.f,
                                                       l2 ? qnorm : nullptr, l2 ? 1 : 0,
                                                       l2 ? kHostInf : -kHostInf, label_base,
-                                                      out_dist, out_labels);
+                                                      out_dist, out_labels, nq_dev, row_map);
     count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;

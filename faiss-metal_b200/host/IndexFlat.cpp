@@ -24,8 +24,8 @@ namespace faiss_b200 {
 namespace {
 
 constexpr size_t kStageBytes = 64ull << 20;   // fp32 staging chunk for add / reconstruct_n
-constexpr int64_t kFusedBatch = 16384;        // queries per launch, k <= 32
-constexpr int64_t kSelectBatch = 1024;        // queries per launch, k > 32: few rows, wide column chunks
+constexpr int64_t kFusedBatch = 16384;        // queries per launch, k <= 1024 (fused kernel, lists)
+constexpr int64_t kSelectBatch = 1024;        // queries per launch beyond: few rows, wide column chunks
 
 void cudaCheck(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
@@ -387,7 +387,7 @@ void B200IndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k, float
     const bool qOnDevice = isDevicePointer(x);
     const bool dOnDevice = isDevicePointer(distances);
     const bool lOnDevice = isDevicePointer(labels);
-    const int64_t batch = std::min<int64_t>(n, k <= B200F_FUSED_MAX_K ? kFusedBatch : kSelectBatch);
+    const int64_t batch = std::min<int64_t>(n, k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch);
     const size_t scratchBytes =
             b200f_search_scratch_bytes(batch, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
     FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "search: cannot plan this shape");
@@ -441,7 +441,7 @@ void B200IndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::i
                                         float* distances, faiss::idx_t* labels) const {
     checkSearchArgs(n, x, k, distances, labels, ntotal);
     if (n == 0) return;
-    const int64_t batch = k <= B200F_FUSED_MAX_K ? kFusedBatch : kSelectBatch;
+    const int64_t batch = k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch;
     FAISS_THROW_IF_NOT_MSG(n <= batch, "searchDeviceEnqueue: too many queries for one launch");
     DeviceGuard g(impl_->res->getDevice());
     const size_t scratchBytes =
@@ -580,7 +580,7 @@ B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss
     t->distOnDevice = isDevicePointer(distances);
     t->labelsOnDevice = isDevicePointer(labels);
     const bool qOnDevice = isDevicePointer(x);
-    const int64_t batch = std::min<int64_t>(n, k <= B200F_FUSED_MAX_K ? kFusedBatch : kSelectBatch);
+    const int64_t batch = std::min<int64_t>(n, k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch);
     t->nbatches = (int)((n + batch - 1) / batch);
     const size_t scratchBytes =
             b200f_search_scratch_bytes(batch, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);

@@ -55,6 +55,10 @@ extern "C" {
 /* Largest k served by the fused (no distance matrix) epilogue and scan kernels
  * (src/MetalDistance.mm:346-354: k <= 32). */
 #define B200F_FUSED_MAX_K 32
+/* Largest k the tensor path serves from the fused kernel's 32-entry lists (no distance
+ * matrix unless a row's lists overflow; no counterpart in the reference, whose k > 32 path
+ * always writes the matrix, src/MetalIndexFlat.mm:358-378). */
+#define B200F_LIST_MAX_K 1024
 
 /* Path override for tests, the analogue of MetalIndexFlat::setForceMPS
  * (include/faiss-metal/MetalIndexFlat.h:106): 0 = choose by (nq, k). */
@@ -216,7 +220,8 @@ int b200f_merge_lists_strided(const float* dist, const int64_t* labels, int64_t 
 
 /* Deterministic synthetic rows on the device (benchmark inputs): element
  * (row, col) depends only on (seed, row0 + row, col).
- * dist: 0 = U[0,1), 1 = N(0,1) * scale, 2 = N(0,1) then row-normalised.
+ * dist: 0 = U[0,1), 1 = N(0,1) * scale, 2 = N(0,1) then row-normalised,
+ * 3 = mixture of 1,000 gaussians (centres uniform in [-1,1]^d, shared by all seeds; sigma = scale).
  * No counterpart in the reference (its bench fills host arrays with
  * std::mt19937, tests/bench_metal_flat.mm:27-33). */
 int b200f_fill_synthetic(float* dst, int64_t n, int d, int64_t row0, uint64_t seed, int dist,

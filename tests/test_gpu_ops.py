@@ -190,7 +190,7 @@ def test_merge_lists(fm, res, metric, P, nq, k):
     assert np.array_equal(out_d.cpu().numpy(), want_d)
 
 
-@pytest.mark.parametrize("dist_kind", [0, 1, 2])
+@pytest.mark.parametrize("dist_kind", [0, 1, 2, 3])
 def test_fill_synthetic(fm, res, dist_kind):
     n, d = 4096, 96
     a = torch.empty((n, d), dtype=torch.float32, device="cuda:0")
@@ -205,5 +205,87 @@ def test_fill_synthetic(fm, res, dist_kind):
         assert x.min() >= 0 and x.max() < 1 and abs(x.mean() - 0.5) < 0.01 and abs(x.var() - 1 / 12) < 0.005
     elif dist_kind == 1:
         assert abs(x.mean()) < 1e-3 and abs(x.std() - 0.05) < 1e-3
-    else:
+    elif dist_kind == 2:
         np.testing.assert_allclose(np.linalg.norm(x, axis=1), 1.0, rtol=1e-5)
+    else:
+        # sigma = 0 leaves the bare centres: at most 1,000 distinct rows inside [-1,1]^d, the same
+        # set for every seed; with sigma = 0.05 the rows scatter around them by N(0, 0.05^2)
+        c7 = torch.empty((n, d), dtype=torch.float32, device="cuda:0")
+        c8 = torch.empty((n, d), dtype=torch.float32, device="cuda:0")
+        fm.abi.check_op(L.b200f_fill_synthetic(vp(c7), n, d, 0, 7, dist_kind, 0.0, cur_stream()), "fill")
+        fm.abi.check_op(L.b200f_fill_synthetic(vp(c8), n, d, 0, 8, dist_kind, 0.0, cur_stream()), "fill")
+        torch.cuda.synchronize()
+        u7 = {r.tobytes() for r in c7.cpu().numpy()}
+        u8 = {r.tobytes() for r in c8.cpu().numpy()}
+        assert 900 < len(u7) <= 1000 and 900 < len(u8) <= 1000 and len(u7 & u8) > 850
+        assert len(u7 | u8) <= 1000
+        assert float(c7.abs().max()) <= 1.0
+        noise = x - c7.cpu().numpy().astype(np.float64)
+        assert abs(noise.mean()) < 1e-3 and abs(noise.std() - 0.05) < 1e-3
+
+
+def run_search(fm, st, xq, metric, k, path):
+    xq_dev = torch.from_numpy(xq).cuda()
+    nq = xq.shape[0]
+    out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda:0")
+    out_l = torch.empty((nq, k), dtype=torch.int64, device="cuda:0")
+    a = st.args(fm, xq_dev, metric, k, path, out_d, out_l)
+    fm.abi.check_op(fm.lib().b200f_search(ctypes.byref(a)), "search")
+    torch.cuda.synchronize()
+    status = st.status.cpu().numpy()
+    assert status[0] == 0
+    return out_d.cpu().numpy(), out_l.cpu().numpy(), int(status[1])
+
+
+@pytest.mark.parametrize("storage,metric,k,nq", [(2, O.METRIC_L2, 100, 300), (1, O.METRIC_INNER_PRODUCT, 100, 130),
+                                                 (0, O.METRIC_L2, 1024, 40), (2, O.METRIC_L2, 33, 257),
+                                                 (1, O.METRIC_INNER_PRODUCT, 500, 9)])
+def test_list_selection_random_rows(fm, res, storage, metric, k, nq):
+    # 32 < k <= 1024 on the tensor path: results come from the fused kernel's 32-entry lists; with
+    # rows in random order no list overflows, so no row is redone (status word 1 counts them)
+    nb, d = 70_000, 64
+    xb = H.gaussian(nb, d, 51)
+    xq = H.gaussian(nq, d, 52)
+    st = Stored(fm, xb, storage)
+    D, I, redone = run_search(fm, st, xq, metric, k, 2)
+    assert redone == 0
+    H.check_against_oracle(metric, storage, True, xb, xq, k, D, I, loose=False)
+
+
+@pytest.mark.parametrize("storage,metric,k", [(2, O.METRIC_L2, 100), (0, O.METRIC_L2, 200),
+                                              (1, O.METRIC_INNER_PRODUCT, 64)])
+@pytest.mark.parametrize("nq,near", [(300, 150), (700, 700), (130, 1)])
+def test_list_selection_redoes_overflowing_rows(fm, res, storage, metric, k, nq, near):
+    # the k nearest rows of `near` queries sit next to each other in the database, so one list
+    # would have to keep more than 32 of a row's results: exactly such rows must be found and
+    # redone through the key matrix; the others keep the list result
+    nb, d = 70_000, 32
+    rng = np.random.default_rng(61)
+    xb = H.gaussian(nb, d, 62)
+    # a cluster far from everything else, wide enough that ||q||^2 + ||x||^2 - 2 q.x does not
+    # cancel to nothing inside it
+    centre = np.full(d, 2.0, dtype=np.float32)
+    xb[20_000:20_400] = centre + 0.3 * rng.standard_normal((400, d)).astype(np.float32)
+    xq = H.gaussian(nq, d, 63)
+    rows = rng.permutation(nq)[:near]
+    xq[rows] = centre + 0.3 * rng.standard_normal((near, d)).astype(np.float32)
+    st = Stored(fm, xb, storage)
+    D, I, redone = run_search(fm, st, xq, metric, k, 2)
+    if metric == O.METRIC_L2:
+        assert redone == near
+    else:
+        assert redone >= near  # a long query also favours the cluster's direction
+    H.check_against_oracle(metric, storage, True, xb, xq, k, D, I, loose=False)
+    # the redone rows are counted and compacted on the device: a second run agrees bit for bit
+    D2, I2, _ = run_search(fm, st, xq, metric, k, 2)
+    assert np.array_equal(I, I2) and np.array_equal(D, D2)
+
+
+def test_list_selection_small_shard_uses_matrix(fm, res):
+    # too few column ranges for lists to hold 4 k candidates: plain key-matrix path, nothing redone
+    xb = H.gaussian(3_000, 48, 71)
+    xq = H.gaussian(20, 48, 72)
+    st = Stored(fm, xb, 2)
+    D, I, redone = run_search(fm, st, xq, O.METRIC_L2, 500, 2)
+    assert redone == 0
+    H.check_against_oracle(O.METRIC_L2, 2, True, xb, xq, 500, D, I, loose=False)
