@@ -77,7 +77,8 @@ int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, flo
 struct GemmPlan {
     int pair;            // 1: CTA pairs (cta_group::2), query blocks of 256 rows
     int nqb;             // query blocks of 128 (256) rows
-    int64_t ntiles;      // column tiles of 256 rows in the launch
+    int tile_n;          // columns of X per tile: 256, or 512 for pairs
+    int64_t ntiles;      // column tiles in the launch
     int P;               // column ranges == partial lists per query
     int64_t tiles_per_range;
     int grid;
@@ -97,9 +98,16 @@ struct GemmOperands {
 // Fused top-k (k <= 32): partial lists part_key/part_idx [nq][2 * P][k] (two per column range).
 // gthr holds nq * gslots words; with gslots = s the shared filter bounds the (32 * s)-th best
 // key of a row, so lists of k = 32 entries can feed a later selection of up to 32 * s results.
+// tile_stride > 1 visits only every tile_stride-th column tile (plan made for that many tiles).
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                     float kscale, int k, int gslots, float* part_key, int32_t* part_idx,
-                     uint32_t* gthr, int32_t* status, cudaStream_t stream);
+                     int64_t tile_stride, float kscale, int k, int gslots, float* part_key,
+                     int32_t* part_idx, uint32_t* gthr, int32_t* status, cudaStream_t stream);
+// Threshold filter over the whole shard: column c of row q with scaled key <= thr[q * thr_stride +
+// thr_pos] is appended to the row's candidate buffer cand_key/cand_idx [nq][cand_cap] in any
+// order; cand_cnt[q] counts every hit, also those beyond cand_cap, which are not stored.
+int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscale, const float* thr,
+                       int thr_stride, int thr_pos, float* cand_key, int32_t* cand_idx,
+                       int32_t* cand_cnt, int cand_cap, int32_t* status, cudaStream_t stream);
 // Store mode: out[row*ld + (col-col0)] = sign*(-kscale*t) + rowadd[row], t = q.x (- ||x||^2/2).
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
                       float kscale, float sign, const float* rowadd, float* out,
@@ -108,11 +116,17 @@ int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0
 // select.cu
 // Merge P sorted partial lists (key smaller=better, int32 local ids; -1 = empty) per
 // query and finalise: L2 dist = max(key + qnorm, 0), IP dist = -key; labels = id + base.
+// nq_dev / row_map (optional): live rows counted on the device; lists of row j belong to query
+// row_map[j].  out_labels may be null (keys only).
 int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
                           int metric, const float* qnorm, int64_t label_base, float* out_dist,
-                          int64_t* out_labels, cudaStream_t stream);
+                          int64_t* out_labels, const int* nq_dev, const int32_t* row_map,
+                          cudaStream_t stream);
 // Running top-k over a key matrix chunk: run lists [nq][k] (key, int32 id) are read
 // (if has_prev) and rewritten with the best k of (previous list U chunk columns).
+// Merged raw keys only: out_key[q][k], best first, +INF where fewer than k entries exist.
+int launch_merge_keys(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
+                      float* out_key, cudaStream_t stream);
 // nq_dev (optional): number of live rows, read on the device.
 int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int64_t col0,
                         int k, int has_prev, float* run_key, int32_t* run_idx, const int* nq_dev,
@@ -129,6 +143,13 @@ int launch_finalize_lists(const float* run_key, const int32_t* run_idx, int64_t 
 int launch_select_parts(const float* part_key, const int32_t* part_idx, int nlists, int64_t nq,
                         int k, int metric, const float* qnorm, int64_t label_base, float* out_dist,
                         int64_t* out_labels, int32_t* dirty, cudaStream_t stream);
+// Selection of the k best of a row's threshold-filtered candidates (unordered buffer of
+// min(cand_cnt[q], cap) entries).  dirty[q] = 1 when entries were lost to overflow or fewer than
+// k candidates were found although the shard has more rows.
+int launch_select_candidates(const float* cand_key, const int32_t* cand_idx, const int32_t* cand_cnt,
+                             int cap, int64_t nb, int64_t nq, int k, int metric, const float* qnorm,
+                             int64_t label_base, float* out_dist, int64_t* out_labels, int32_t* dirty,
+                             cudaStream_t stream);
 // rows[0 .. *count) = ascending indices q with dirty[q] != 0; *count also goes to *count_copy.
 int launch_compact_rows(const int32_t* dirty, int64_t nq, int32_t* rows, int32_t* count,
                         int32_t* count_copy, cudaStream_t stream);

@@ -81,7 +81,7 @@ struct Cfg {
     static constexpr int SMEM_BYTES = SM_ABORT + 4 + 8;
 };
 
-enum { MODE_TOPK = 0, MODE_STORE = 1 };
+enum { MODE_TOPK = 0, MODE_STORE = 1, MODE_FILTER = 2 };
 
 struct GemmParams {
     int64_t nq;
@@ -108,6 +108,15 @@ struct GemmParams {
     int gslots;          // lists publish to slot (list number % gslots); the row's bound is the
                          // largest slot: gslots full lists hold 32 * gslots distinct candidates
     const int* nq_dev;   // when set: the number of live query rows is read from device memory
+    int64_t tile_stride; // tile t of the launch is tile t * tile_stride of X (sampling passes)
+    // MODE_FILTER: every column whose key is <= the row's threshold is appended to the row's
+    // candidate buffer (position from an atomic counter; entries past cand_cap are only counted)
+    const float* fthr;   // threshold of row q in scaled key units: fthr[q * fthr_stride + fthr_pos]
+    int fthr_stride, fthr_pos;
+    float* cand_key;     // [nq][cand_cap]
+    int32_t* cand_idx;
+    int32_t* cand_cnt;   // [nq]
+    int cand_cap;
     float* out;
     int64_t ld;
     int32_t* status;
@@ -303,6 +312,40 @@ __device__ __forceinline__ void reglist_insert(float (&lk)[KMAX], int32_t (&li)[
     }
 }
 
+// Hits of the tile in flight are staged per thread in shared memory (entry i of a thread at
+// [i * STAGE_LD]: raw key s = -t and column) and worked off AFTER the accumulator has been handed
+// back to the MMA issuers, so that list insertion and buffer appends run beside the next
+// tile's MMAs instead of in front of them.  Only a thread whose stage fills up inside one
+// tile (list warm-up, massive ties) drains it on the spot.
+constexpr int STAGE_N = 16;
+constexpr int STAGE_LD = 32 * NUM_EPI_WARPS;
+
+__device__ __forceinline__ void drain_to_list(float (&lk)[KMAX], int32_t (&li)[KMAX], const float* sk,
+                                              const int32_t* si, int n, float& thr, float& thr_eff) {
+    for (int i = 0; i < n; i++) {
+        const float sc = sk[i * STAGE_LD];
+        if (sc < thr_eff) {  // the list may have tightened since the entry was staged
+            reglist_insert(lk, li, sc, si[i * STAGE_LD]);
+            thr = lk[KMAX - 1];
+            thr_eff = fminf(thr_eff, thr);
+        }
+    }
+}
+
+// MODE_FILTER: one atomic takes n slots of the row's candidate buffer; the counter also counts
+// entries that no longer fit.
+__device__ __forceinline__ void drain_to_buffer(int32_t* cnt, float* ck, int32_t* ci, int cap,
+                                                float kscale, const float* sk, const int32_t* si, int n) {
+    if (n <= 0) return;
+    const int base = atomicAdd(cnt, n);
+    for (int i = 0; i < n; i++) {
+        if (base + i < cap) {
+            ck[base + i] = kscale * sk[i * STAGE_LD];
+            ci[base + i] = si[i * STAGE_LD];
+        }
+    }
+}
+
 template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -385,7 +428,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int64_t t0 = xr * p.tiles_per_range;
                 const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
                 for (int64_t t = t0; t < t1 && ok; t++) {
-                    const int xrow = (int)(p.col0 + t * TILE_N);
+                    const int xrow = (int)(p.col0 + t * p.tile_stride * TILE_N);
                     for (int kb = 0; kb < kb_total; kb++) {
                         if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status)) {
                             ok = false;
@@ -542,6 +585,11 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int k = p.k;
         float lk[KMAX];     // this thread's row list (see reglist_insert)
         int32_t li[KMAX];
+        // this thread's stage (see drain_to_list); the area serves the transposes in store mode
+        float* const stage_key = reinterpret_cast<float*>(smem + SM_LKEY) + (threadIdx.x - 64);
+        int32_t* const stage_idx =
+                reinterpret_cast<int32_t*>(smem + SM_LKEY) + STAGE_N * STAGE_LD + (threadIdx.x - 64);
+        int nstaged = 0;
         for (int64_t item = unit; item < nitems && ok; item += nunits) {
             const int qb = (int)(item % nqb);
             const int64_t xr = item / nqb;
@@ -561,11 +609,20 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     lk[j] = (j >= KMAX - k) ? CUDART_INF_F : -CUDART_INF_F;
                     li[j] = -1;
                 }
+            } else if (p.mode == MODE_FILTER) {
+                // keys <= threshold pass: the filter below is exclusive, so take the next float up
+                // (+INF, the threshold of a row whose sample was too small, stays; -INF passes nothing)
+                thr_eff = -CUDART_INF_F;
+                if (row_live) {
+                    const float t = p.fthr[grow * p.fthr_stride + p.fthr_pos] / p.kscale;
+                    const uint32_t o = float_to_ordered(t);
+                    thr_eff = (o >= 0xff800000u) ? t : ordered_to_float(o + 1u);
+                }
             } else if (row_live && p.rowadd) {
                 radd = p.rowadd[grow];
             }
             for (int64_t t = t0; t < t1 && ok; t++) {
-                const int64_t c_tile = p.col0 + t * TILE_N;
+                const int64_t c_tile = p.col0 + t * p.tile_stride * TILE_N;
                 {
                     const bool w = mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag, p.status);
                     if (!__all_sync(0xffffffffu, w)) {  // keep the warp converged for tcgen05.ld
@@ -600,7 +657,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     tc_ld32(taddr + ch * 32, r);
                     tc_wait_ld();
                     const int64_t cbase = c_tile + ch * 32;
-                    if (p.mode == MODE_TOPK) {
+                    if (p.mode != MODE_STORE) {
                         if (partial) {
 #pragma unroll
                             for (int c = 0; c < 32; c++)
@@ -616,34 +673,35 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                             for (int c = 0; c < w2; c++) m[c] = fmaxf(m[c], m[c + w2]);
                         // Slow path, entered by the whole warp when any row has a candidate in
-                        // this chunk.  Every lane first marks its own hit columns; the lanes then
-                        // insert in lock-step (round j = each lane's j-th hit, ascending column),
-                        // so the number of rounds is the largest hit count of a lane, not the
-                        // number of distinct hit columns of the warp.
-                        const bool any_hit = (-m[0] < thr_eff) && row_live;
+                        // this chunk: a lane marks its hit columns and moves them to its stage.
+                        const bool any_hit = row_live && (-m[0] < thr_eff);
                         if (__any_sync(0xffffffffu, any_hit)) {
-                            uint32_t mask = 0;
                             if (any_hit) {
+                                uint32_t mask = 0;
 #pragma unroll
                                 for (int c = 0; c < 32; c++)
                                     mask |= (-__uint_as_float(r[c]) < thr_eff ? 1u : 0u) << c;
-                            }
-                            const int32_t id0 = (int32_t)cbase;
-                            while (__any_sync(0xffffffffu, mask != 0)) {
-                                if (mask != 0) {
+                                while (mask != 0) {
                                     const int cc = __ffs(mask) - 1;
                                     mask &= mask - 1;
                                     uint32_t bits = 0;
 #pragma unroll
                                     for (int c = 0; c < 32; c++) bits = (c == cc) ? r[c] : bits;
-                                    const float sc = -__uint_as_float(bits);
-                                    if (sc < thr_eff) {
-                                        reglist_insert(lk, li, sc, id0 + cc);
-                                        thr = lk[KMAX - 1];
-                                        thr_eff = fminf(thr_eff, thr);
+                                    if (nstaged == STAGE_N) {  // rare: list warm-up, massive ties
+                                        if (p.mode == MODE_TOPK)
+                                            drain_to_list(lk, li, stage_key, stage_idx, nstaged, thr, thr_eff);
+                                        else
+                                            drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
+                                                            p.cand_idx + grow * p.cand_cap, p.cand_cap, p.kscale,
+                                                            stage_key, stage_idx, nstaged);
+                                        nstaged = 0;
                                     }
+                                    stage_key[nstaged * STAGE_LD] = -__uint_as_float(bits);
+                                    stage_idx[nstaged * STAGE_LD] = (int32_t)cbase + cc;
+                                    nstaged++;
                                 }
                             }
+                            __syncwarp();
                         }
                     } else {
                         // Store mode: thread t holds 32 consecutive columns of ITS row; writing
@@ -674,6 +732,17 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + acc * 8, 0));
                     else mbar_arrive(bar_tempty + acc * 8);
                 }
+                // the accumulator is back with the MMA issuers: now work off the staged hits
+                if (nstaged > 0) {
+                    if (p.mode == MODE_TOPK)
+                        drain_to_list(lk, li, stage_key, stage_idx, nstaged, thr, thr_eff);
+                    else
+                        drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
+                                        p.cand_idx + grow * p.cand_cap, p.cand_cap, p.kscale, stage_key,
+                                        stage_idx, nstaged);
+                    nstaged = 0;
+                }
+                __syncwarp();
                 if (C::ACC_BUFS == 2) {
                     acc ^= 1;
                     if (acc == 0) acc_phase ^= 1;
@@ -771,6 +840,7 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
 
     p.nq = op.nq;
     p.nq_dev = op.nq_dev;
+    if (p.tile_stride < 1) p.tile_stride = 1;
     p.col0 = col0;
     p.ncols_end = col0 + ncols;
     p.ntiles = plan.ntiles;
@@ -885,7 +955,8 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
     const int qb = g.pair ? 2 * BM : BM;
     const int units = g.pair ? max_active_pairs(sm_count) : sm_count;  // CTAs or CTA pairs that run at once
     g.nqb = (int)ceil_div64(nq, qb);
-    g.ntiles = ceil_div64(ncols, g.pair ? Cfg<true>::TILE_N : Cfg<false>::TILE_N);
+    g.tile_n = g.pair ? Cfg<true>::TILE_N : Cfg<false>::TILE_N;
+    g.ntiles = ceil_div64(ncols, g.tile_n);
     if (g.nqb <= 0 || g.ntiles <= 0) {
         g.nqb = 0; g.ntiles = 0; g.P = 0; g.tiles_per_range = 0; g.grid = 0;
         return g;
@@ -916,14 +987,15 @@ GemmPlan plan_gemm(int64_t nq, int64_t ncols, int sm_count) {
 }
 
 int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                     float kscale, int k, int gslots, float* part_key, int32_t* part_idx,
-                     uint32_t* gthr, int32_t* status, cudaStream_t stream) {
+                     int64_t tile_stride, float kscale, int k, int gslots, float* part_key,
+                     int32_t* part_idx, uint32_t* gthr, int32_t* status, cudaStream_t stream) {
     if (k <= 0 || k > KMAX || gslots < 1) return B200F_ERR_UNSUPPORTED;
     if (!gthr) return B200F_ERR_BAD_ARG;
     // all-ones is above every ordered float: no bound yet
     B200F_CUDA_TRY(cudaMemsetAsync(gthr, 0xff, (size_t)op.nq * gslots * sizeof(uint32_t), stream));
     GemmParams p{};
     p.mode = MODE_TOPK;
+    p.tile_stride = tile_stride;
     p.gslots = gslots;
     p.k = k;
     p.kscale = kscale;
@@ -936,6 +1008,26 @@ int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0,
     p.ld = 0;
     p.status = status;
     return launch_common(op, plan, p, col0, ncols, stream);
+}
+
+int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscale, const float* thr,
+                       int thr_stride, int thr_pos, float* cand_key, int32_t* cand_idx,
+                       int32_t* cand_cnt, int cand_cap, int32_t* status, cudaStream_t stream) {
+    if (!thr || !cand_key || !cand_idx || !cand_cnt || cand_cap < 1) return B200F_ERR_BAD_ARG;
+    B200F_CUDA_TRY(cudaMemsetAsync(cand_cnt, 0, (size_t)op.nq * sizeof(int32_t), stream));
+    GemmParams p{};
+    p.mode = MODE_FILTER;
+    p.kscale = kscale;
+    p.sign = 1.f;
+    p.fthr = thr;
+    p.fthr_stride = thr_stride;
+    p.fthr_pos = thr_pos;
+    p.cand_key = cand_key;
+    p.cand_idx = cand_idx;
+    p.cand_cnt = cand_cnt;
+    p.cand_cap = cand_cap;
+    p.status = status;
+    return launch_common(op, plan, p, 0, op.nb, stream);
 }
 
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,

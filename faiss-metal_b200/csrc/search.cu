@@ -6,12 +6,19 @@
 //   nq <= 4            streaming scan (scan.cu)
 //   nq  > 4            tensor-core GEMM (gemm_topk.cu)
 //   k  <= 32           top-k fused into the distance kernel, partial lists merged after
+//   k  <= 1024         (tensor path, shard of >= 64k / 128k rows) threshold filter: a pilot pass
+//                      over every 64th / 128th column tile gives each query a key threshold
+//                      that admits a few times k rows; the full pass appends every column under
+//                      the threshold to the query's candidate buffer (no lists, no matrix);
+//                      the k best candidates are selected.  A row whose buffer overflowed or
+//                      holds fewer than k candidates is redone by the paths below.
 //   32 < k <= 1024     (tensor path, enough column ranges) the fused kernel keeps 32 entries
 //                      per list, the k best of all lists are selected, and a row is redone
 //                      through the key matrix only when a full list could have dropped one of
 //                      its k results (rows counted and compacted on the device, no host sync)
 //   k   > 32 otherwise distance keys written per column chunk, running sort-select
 #include <cstdio>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -45,6 +52,11 @@ struct SearchPlan {
     bool fused;       // k <= 32
     bool lists;       // k > 32 selected from the fused kernel's 32-entry lists, matrix fallback per row
     int gslots;       // words per query row in the shared bound array
+    bool filter;      // pilot threshold + candidate buffers, fused / matrix fallback per row
+    int fstride;      // pilot pass: every fstride-th column tile
+    int frank;        // threshold = frank-th best key of the pilot sample
+    int fcap;         // candidate buffer entries per query
+    GemmPlan pilot;
     int npl;
     int64_t a_pitch, a_plane_stride;
     GemmPlan gemm;    // tensor path (fused: whole shard; chunked: per chunk)
@@ -53,17 +65,21 @@ struct SearchPlan {
     int64_t ngroups;  // scan path: query groups of SCAN_GROUP
     size_t off_qnorm, off_gthr, off_a, off_part_key, off_part_idx, off_matrix, off_run_key, off_run_idx;
     size_t off_dirty, off_rows, off_count, off_a2;
+    size_t off_pilot_key, off_pilot_idx, off_thr, off_cand_key, off_cand_idx, off_cand_cnt;
     size_t total;
 };
 
-// B200F_NO_LISTS=1 in the environment sends every k > 32 search through the key matrix (testing).
+// B200F_NO_FILTER=1 in the environment switches the threshold-filter path off (same use).
+bool filter_disabled() {
+    const char* e = getenv("B200F_NO_FILTER");
+    return e && e[0] == '1';
+}
+
+// B200F_NO_LISTS=1 in the environment sends every k > 32 search through the key matrix.  Read at
+// every call, so that a test can switch between the paths inside one process.
 bool lists_disabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("B200F_NO_LISTS");
-        v = (e && e[0] == '1') ? 1 : 0;
-    }
-    return v == 1;
+    const char* e = getenv("B200F_NO_LISTS");
+    return e && e[0] == '1';
 }
 
 bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool pairwise,
@@ -83,7 +99,25 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     pl.off_qnorm = off;
     off += align256((size_t)(nq > 0 ? nq : 1) * 4);
     pl.gslots = 1;
-    if (!pl.fused && !pairwise && pl.path == B200F_PATH_TENSOR && k <= B200F_LIST_MAX_K &&
+    if (!pairwise && pl.path == B200F_PATH_TENSOR && k <= B200F_LIST_MAX_K && !filter_disabled()) {
+        // The pilot sample holds nb / stride rows and, on average, e = k / stride of a query's k
+        // best.  The threshold is the sample's r-th best key with r = e + 4.5 sqrt(e) + 3: fewer
+        // than k rows of the shard lie under it only if the sample caught r of the k best, which
+        // is about one row in a million; about r * stride rows do lie under it.
+        const int stride = k <= 128 ? 64 : 128;
+        if (nb >= (int64_t)stride * 1024) {
+            const double e = (double)k / stride;
+            int r = (int)(e + 4.5 * std::sqrt(e) + 3.0 + 0.999);
+            if (r > B200F_FUSED_MAX_K) r = B200F_FUSED_MAX_K;
+            int cap = 1024;
+            while (cap < 4 * r * stride && cap < 8192) cap <<= 1;
+            pl.filter = true;
+            pl.fstride = stride;
+            pl.frank = r;
+            pl.fcap = cap;
+        }
+    }
+    if (!pl.filter && !pl.fused && !pairwise && pl.path == B200F_PATH_TENSOR && k <= B200F_LIST_MAX_K &&
         !lists_disabled()) {
         // lists must be able to hold the result four times over, else the fallback would be the rule
         const GemmPlan g = plan_gemm(nq, nb, sm);
@@ -120,7 +154,24 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         pl.off_part_idx = off;
         off += align256((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
     }
-    if (pl.lists) {
+    if (pl.filter) {
+        const int64_t n1 = nq > 0 ? nq : 1;
+        if (!pl.fused) pl.gemm = plan_gemm(nq, nb, sm);
+        pl.pilot = plan_gemm(nq, ceil_div64(pl.gemm.ntiles, pl.fstride) * pl.gemm.tile_n, sm);
+        pl.off_pilot_key = off;
+        off += align256((size_t)n1 * 2 * (pl.pilot.P > 0 ? pl.pilot.P : 1) * pl.frank * 4);
+        pl.off_pilot_idx = off;
+        off += align256((size_t)n1 * 2 * (pl.pilot.P > 0 ? pl.pilot.P : 1) * pl.frank * 4);
+        pl.off_thr = off;
+        off += align256((size_t)n1 * pl.frank * 4);
+        pl.off_cand_key = off;
+        off += align256((size_t)n1 * pl.fcap * 4);
+        pl.off_cand_idx = off;
+        off += align256((size_t)n1 * pl.fcap * 4);
+        pl.off_cand_cnt = off;
+        off += align256((size_t)n1 * 4);
+    }
+    if (pl.lists || pl.filter) {
         pl.off_dirty = off;
         off += align256((size_t)(nq > 0 ? nq : 1) * 4);
         pl.off_rows = off;
@@ -137,7 +188,7 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         const int64_t nb_pad = round_up64(nb > 0 ? nb : 1, 256);
         if (cols > nb_pad) cols = nb_pad;
         pl.chunk_cols = cols;
-        if (!pl.lists) pl.gemm = plan_gemm(nq, cols, sm);
+        if (!pl.lists && !pl.filter) pl.gemm = plan_gemm(nq, cols, sm);
         pl.off_matrix = off;
         off += align256((size_t)(nq > 0 ? nq : 1) * cols * 4);
         pl.off_run_key = off;
@@ -389,14 +440,58 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
     }
     if (rc != B200F_OK) return rc;
 
+    // rows (counted and listed on the device) that an optimistic stage could not prove exact
+    const int* nq_dev = nullptr;
+    const int32_t* row_map = nullptr;
+    uint32_t* gthr = reinterpret_cast<uint32_t*>(scratch + pl.off_gthr);
+    auto redo_setup = [&](int32_t* dirty) -> int {
+        int32_t* rows = reinterpret_cast<int32_t*>(scratch + pl.off_rows);
+        int32_t* count = reinterpret_cast<int32_t*>(scratch + pl.off_count);
+        uint16_t* a2 = reinterpret_cast<uint16_t*>(scratch + pl.off_a2);
+        // the number of redone rows is left in status word 1 for whoever wants to know
+        int r2 = launch_compact_rows(dirty, a->nq, rows, count, a->status ? a->status + 1 : nullptr, st);
+        if (r2 != B200F_OK) return r2;
+        r2 = launch_gather_rows(op.a_planes, op.npl, op.a_plane_stride, op.a_pitch, rows, count, a->nq,
+                                a2, st);
+        if (r2 != B200F_OK) return r2;
+        op.a_planes = a2;
+        op.nq_dev = count;
+        nq_dev = count;
+        row_map = rows;
+        return B200F_OK;
+    };
+
+    if (pl.filter) {
+        float* pkey = reinterpret_cast<float*>(scratch + pl.off_pilot_key);
+        int32_t* pidx = reinterpret_cast<int32_t*>(scratch + pl.off_pilot_idx);
+        float* thr = reinterpret_cast<float*>(scratch + pl.off_thr);
+        float* ckey = reinterpret_cast<float*>(scratch + pl.off_cand_key);
+        int32_t* cidx = reinterpret_cast<int32_t*>(scratch + pl.off_cand_idx);
+        int32_t* ccnt = reinterpret_cast<int32_t*>(scratch + pl.off_cand_cnt);
+        int32_t* dirty = reinterpret_cast<int32_t*>(scratch + pl.off_dirty);
+        rc = launch_gemm_topk(op, pl.pilot, 0, a->nb, pl.fstride, kscale, pl.frank, 1, pkey, pidx, gthr,
+                              a->status, st);
+        if (rc != B200F_OK) return rc;
+        rc = launch_merge_keys(pkey, pidx, 2 * pl.pilot.P, a->nq, pl.frank, thr, st);
+        if (rc != B200F_OK) return rc;
+        rc = launch_gemm_filter(op, pl.gemm, kscale, thr, pl.frank, pl.frank - 1, ckey, cidx, ccnt,
+                                pl.fcap, a->status, st);
+        if (rc != B200F_OK) return rc;
+        rc = launch_select_candidates(ckey, cidx, ccnt, pl.fcap, a->nb, a->nq, a->k, a->metric, qnorm,
+                                      a->label_base, a->out_dist, a->out_labels, dirty, st);
+        if (rc != B200F_OK) return rc;
+        rc = redo_setup(dirty);
+        if (rc != B200F_OK) return rc;
+    }
+
     if (pl.fused) {
         float* part_key = reinterpret_cast<float*>(scratch + pl.off_part_key);
         int32_t* part_idx = reinterpret_cast<int32_t*>(scratch + pl.off_part_idx);
         int P;
         if (pl.path == B200F_PATH_TENSOR) {
             P = 2 * pl.gemm.P;
-            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, a->k, 1, part_key, part_idx,
-                                  reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
+            rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, 1, kscale, a->k, 1, part_key, part_idx, gthr,
+                                  a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
             // every group of <= 4 queries writes the same number of lists (same shard, same
@@ -414,36 +509,23 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
             }
         }
         return launch_merge_partials(part_key, part_idx, P, a->nq, a->k, a->metric, qnorm,
-                                     a->label_base, a->out_dist, a->out_labels, st);
+                                     a->label_base, a->out_dist, a->out_labels, nq_dev, row_map, st);
     }
 
     // k > 32 from 32-entry lists: select, find the rows that are not proven exact, and send only
     // those (gathered into a second query operand, counted on the device) through the key matrix
-    const int* nq_dev = nullptr;
-    const int32_t* row_map = nullptr;
     if (pl.lists) {
         float* part_key = reinterpret_cast<float*>(scratch + pl.off_part_key);
         int32_t* part_idx = reinterpret_cast<int32_t*>(scratch + pl.off_part_idx);
         int32_t* dirty = reinterpret_cast<int32_t*>(scratch + pl.off_dirty);
-        int32_t* rows = reinterpret_cast<int32_t*>(scratch + pl.off_rows);
-        int32_t* count = reinterpret_cast<int32_t*>(scratch + pl.off_count);
-        uint16_t* a2 = reinterpret_cast<uint16_t*>(scratch + pl.off_a2);
-        rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, kscale, B200F_FUSED_MAX_K, pl.gslots, part_key,
-                              part_idx, reinterpret_cast<uint32_t*>(scratch + pl.off_gthr), a->status, st);
+        rc = launch_gemm_topk(op, pl.gemm, 0, a->nb, 1, kscale, B200F_FUSED_MAX_K, pl.gslots, part_key,
+                              part_idx, gthr, a->status, st);
         if (rc != B200F_OK) return rc;
         rc = launch_select_parts(part_key, part_idx, 2 * pl.gemm.P, a->nq, a->k, a->metric, qnorm,
                                  a->label_base, a->out_dist, a->out_labels, dirty, st);
         if (rc != B200F_OK) return rc;
-        // the number of redone rows is left in status word 1 for whoever wants to know
-        rc = launch_compact_rows(dirty, a->nq, rows, count, a->status ? a->status + 1 : nullptr, st);
+        rc = redo_setup(dirty);
         if (rc != B200F_OK) return rc;
-        rc = launch_gather_rows(op.a_planes, op.npl, op.a_plane_stride, op.a_pitch, rows, count, a->nq,
-                                a2, st);
-        if (rc != B200F_OK) return rc;
-        op.a_planes = a2;
-        op.nq_dev = count;
-        nq_dev = count;
-        row_map = rows;
     }
 
     // k > 32: distance keys per column chunk + running selection

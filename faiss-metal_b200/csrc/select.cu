@@ -85,6 +85,8 @@ struct MergeSmallParams {
     int64_t p_stride_id;          // between lists (ids)
     int P;
     int64_t nq;
+    const int* nq_dev;        // optional: live rows (<= nq), read on the device
+    const int32_t* row_map;   // optional: lists of row j belong to query row_map[j]
     int k;
     float key_sign;
     float out_sign;
@@ -102,7 +104,8 @@ __global__ void __launch_bounds__(MS_THREADS) merge_small_kernel(const MergeSmal
     __shared__ IdT si[MS_WARPS][32];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    for (int64_t q = blockIdx.x; q < p.nq; q += gridDim.x) {
+    const int64_t nq_live = p.nq_dev ? min((int64_t)*p.nq_dev, p.nq) : p.nq;
+    for (int64_t q = blockIdx.x; q < nq_live; q += gridDim.x) {
         float lk = CUDART_INF_F;
         IdT li = (IdT)-1;
         float thr = CUDART_INF_F;
@@ -142,15 +145,16 @@ __global__ void __launch_bounds__(MS_THREADS) merge_small_kernel(const MergeSmal
                 }
             }
             if (lane < p.k) {
+                const int64_t qo = p.row_map ? (int64_t)p.row_map[q] : q;
                 float dist = p.pad;
                 int64_t label = -1;
                 if (li >= 0) {
-                    dist = p.out_sign * lk + (p.qnorm ? p.qnorm[q] : 0.f);
+                    dist = p.out_sign * lk + (p.qnorm ? p.qnorm[qo] : 0.f);
                     if (p.clamp && dist < 0.f) dist = 0.f;
                     label = (int64_t)li + p.label_base;
                 }
-                p.out_dist[q * p.k + lane] = dist;
-                p.out_labels[q * p.k + lane] = label;
+                p.out_dist[qo * p.k + lane] = dist;
+                if (p.out_labels) p.out_labels[qo * p.k + lane] = label;
             }
         }
     }
@@ -170,7 +174,9 @@ enum { SRC_MATRIX = 0, SRC_LISTS = 1, SRC_PARTS = 2 };
 struct SortSelectParams {
     // SRC_MATRIX: keys[q*ld + c], c in [0, ncand); payload = col0 + c
     // SRC_LISTS : keys[(l*nq + q)*k + j] over l in [0, P); payload = l*k + j; labels != -1 live
-    // SRC_PARTS : keys[(q*P + l)*32 + j], ids part_idx[same] (-1 = empty); payload = id
+    // SRC_PARTS : keys[q*ld + c], ids part_idx[same] (-1 = empty); payload = id.  Either P
+    //             sorted lists of 32 entries (ld = 32 P), or, with cand_cnt, an unordered
+    //             candidate buffer of min(cand_cnt[q], ld) entries
     const float* keys;
     const int64_t* labels;
     int64_t ld;
@@ -182,7 +188,9 @@ struct SortSelectParams {
     int64_t nq;
     const int* nq_dev;    // optional: live rows (<= nq), read on the device
     const int32_t* part_idx;  // SRC_PARTS
-    int32_t* dirty;       // SRC_PARTS: per row, 1 when a full list might have dropped a result
+    const int32_t* cand_cnt;  // SRC_PARTS: candidates counted per row (may exceed ld: overflow)
+    int64_t nb_total;     // SRC_PARTS with cand_cnt: rows in the shard
+    int32_t* dirty;       // SRC_PARTS: per row, 1 when the result is not proven exact
     int k;
     float key_sign;       // key = key_sign * input
     int has_prev;
@@ -268,8 +276,8 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
             __syncthreads();
         }
 
-        const int64_t total = (SRC == SRC_MATRIX) ? p.ncand
-                              : (SRC == SRC_LISTS) ? (int64_t)p.P * p.k : (int64_t)p.P * 32;
+        int64_t total = (SRC == SRC_MATRIX) ? p.ncand : (SRC == SRC_LISTS) ? (int64_t)p.P * p.k : p.ld;
+        if (SRC == SRC_PARTS && p.cand_cnt) total = min((int64_t)__ldg(p.cand_cnt + q), p.ld);
         // Wide streaming path (key matrix with 16-byte aligned rows): every thread loads
         // 8 x float4 = 32 columns up front, counts its hits against the current threshold, and
         // the CTA appends them after ONE count check per 32,768 columns.  Only when the buffer
@@ -405,7 +413,7 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                         key = p.key_sign * __ldg(p.keys + q * p.ld + c);
                         payload = (uint32_t)(p.col0 + c);
                     } else if (SRC == SRC_PARTS) {
-                        const int64_t off = q * (int64_t)p.P * 32 + c;
+                        const int64_t off = q * p.ld + c;
                         const int32_t id = __ldg(p.part_idx + off);
                         key = p.key_sign * __ldg(p.keys + off);
                         live = id >= 0;
@@ -466,10 +474,17 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
             // the result when that entry itself sorts behind the k-th selected candidate.
             const uint64_t kth = (s_count >= p.k) ? buf[p.k - 1] : SS_EMPTY;
             int bad = 0;
-            for (int l = tid; l < p.P; l += SS_THREADS) {
-                const int64_t off = (q * (int64_t)p.P + l) * 32 + 31;
-                const int32_t id = __ldg(p.part_idx + off);
-                if (id >= 0 && pack(p.key_sign * __ldg(p.keys + off), (uint32_t)id) <= kth) bad = 1;
+            if (p.cand_cnt) {
+                // threshold-filtered candidates: exact when nothing overflowed and either k of
+                // them were found or every row of the shard is a candidate
+                const int64_t cnt = __ldg(p.cand_cnt + q);
+                bad = (cnt > p.ld) || (cnt < p.k && cnt < p.nb_total);
+            } else {
+                for (int l = tid; l < p.P; l += SS_THREADS) {
+                    const int64_t off = q * p.ld + (int64_t)l * 32 + 31;
+                    const int32_t id = __ldg(p.part_idx + off);
+                    if (id >= 0 && pack(p.key_sign * __ldg(p.keys + off), (uint32_t)id) <= kth) bad = 1;
+                }
             }
             bad = __syncthreads_or(bad);
             if (tid == 0) p.dirty[q] = bad ? 1 : 0;
@@ -574,10 +589,13 @@ __global__ void finalize_lists_kernel(const float* __restrict__ run_key,
 
 int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
                           int metric, const float* qnorm, int64_t label_base, float* out_dist,
-                          int64_t* out_labels, cudaStream_t stream) {
+                          int64_t* out_labels, const int* nq_dev, const int32_t* row_map,
+                          cudaStream_t stream) {
     if (nq <= 0) return B200F_OK;
     if (k < 1 || k > 32 || P < 1) return B200F_ERR_UNSUPPORTED;
     MergeSmallParams<int32_t> p{};
+    p.nq_dev = nq_dev;
+    p.row_map = row_map;
     p.in_key = part_key;
     p.in_id = part_idx;
     p.q_stride = (int64_t)P * k;
@@ -595,6 +613,34 @@ int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P,
     p.label_base = label_base;
     p.out_dist = out_dist;
     p.out_labels = out_labels;
+    int64_t g = nq;
+    const int64_t cap = (int64_t)cached_sm_count() * 32;
+    if (g > cap) g = cap;
+    if (nq_dev && g > cached_sm_count()) g = cached_sm_count();
+    merge_small_kernel<int32_t><<<(int)g, MS_THREADS, 0, stream>>>(p);
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+int launch_merge_keys(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
+                      float* out_key, cudaStream_t stream) {
+    if (nq <= 0) return B200F_OK;
+    if (k < 1 || k > 32 || P < 1) return B200F_ERR_UNSUPPORTED;
+    MergeSmallParams<int32_t> p{};
+    p.in_key = part_key;
+    p.in_id = part_idx;
+    p.q_stride = (int64_t)P * k;
+    p.p_stride = k;
+    p.p_stride_id = k;
+    p.P = P;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = 1.f;
+    p.out_sign = 1.f;
+    p.pad = kHostInf;
+    p.out_dist = out_key;
+    p.out_labels = nullptr;
     int64_t g = nq;
     const int64_t cap = (int64_t)cached_sm_count() * 32;
     if (g > cap) g = cap;
@@ -632,6 +678,34 @@ int launch_select_parts(const float* part_key, const int32_t* part_idx, int nlis
     p.keys = part_key;
     p.part_idx = part_idx;
     p.P = nlists;
+    p.ld = (int64_t)nlists * 32;
+    p.nq = nq;
+    p.k = k;
+    p.key_sign = 1.f;
+    p.has_prev = 0;
+    p.out_sign = l2 ? 1.f : -1.f;
+    p.qnorm = l2 ? qnorm : nullptr;
+    p.clamp = l2 ? 1 : 0;
+    p.pad = l2 ? kHostInf : -kHostInf;
+    p.label_base = label_base;
+    p.out_dist = out_dist;
+    p.out_labels = out_labels;
+    p.dirty = dirty;
+    return launch_sort_select<SRC_PARTS>(p, stream);
+}
+
+int launch_select_candidates(const float* cand_key, const int32_t* cand_idx, const int32_t* cand_cnt,
+                             int cap, int64_t nb, int64_t nq, int k, int metric, const float* qnorm,
+                             int64_t label_base, float* out_dist, int64_t* out_labels, int32_t* dirty,
+                             cudaStream_t stream) {
+    if (cap < 1 || !cand_cnt) return B200F_ERR_BAD_ARG;
+    const bool l2 = metric == B200F_METRIC_L2;
+    SortSelectParams p{};
+    p.keys = cand_key;
+    p.part_idx = cand_idx;
+    p.cand_cnt = cand_cnt;
+    p.nb_total = nb;
+    p.ld = cap;
     p.nq = nq;
     p.k = k;
     p.key_sign = 1.f;

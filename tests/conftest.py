@@ -32,3 +32,27 @@ def res(fm):
     r = fm.StandardB200Resources(0)
     yield r
     r.close()
+
+
+SELECT_MODES = {
+    # which optimistic selection stages of the tensor path are allowed (environment switches of
+    # the library, read at every call)
+    "auto": {},
+    "no_filter": {"B200F_NO_FILTER": "1"},
+    "matrix_or_fused": {"B200F_NO_FILTER": "1", "B200F_NO_LISTS": "1"},
+}
+
+
+@pytest.fixture(params=list(SELECT_MODES))
+def select_mode(request):
+    import os
+    env = SELECT_MODES[request.param]
+    old = {k: os.environ.get(k) for k in ("B200F_NO_FILTER", "B200F_NO_LISTS")}
+    for k in old:
+        os.environ.pop(k, None)
+    os.environ.update(env)
+    yield request.param
+    for k, v in old.items():
+        os.environ.pop(k, None)
+        if v is not None:
+            os.environ[k] = v

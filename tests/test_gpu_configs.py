@@ -24,7 +24,7 @@ def run_case(fm, res, xb, xq, metric, storage, k, path=0):
     return r
 
 
-def test_config1_l2_fp32_full_size(fm, res):
+def test_config1_l2_fp32_full_size(fm, res, select_mode):
     # IndexFlatL2 FP32, nb=100,000, nq=1,000, d=128, U[0,1), k=10 -- full size
     xb = H.uniform01(100_000, 128, 1)
     xq = H.uniform01(1_000, 128, 2)
@@ -32,21 +32,21 @@ def test_config1_l2_fp32_full_size(fm, res):
     assert r["loose"]["max_rel_dist_err"] < 1e-4
 
 
-def test_config2_ip_fp16_scaled(fm, res):
+def test_config2_ip_fp16_scaled(fm, res, select_mode):
     # IndexFlatIP FP16, d=768, unit-norm gaussian rows, k=100 (nb, nq scaled down)
-    xb = H.gaussian(60_000, 768, 3, normalise=True)
+    xb = H.gaussian(70_000, 768, 3, normalise=True)
     xq = H.gaussian(200, 768, 4, normalise=True)
     run_case(fm, res, xb, xq, O.METRIC_INNER_PRODUCT, 1, 100)
 
 
-def test_config3_l2_bf16_scaled(fm, res):
+def test_config3_l2_bf16_scaled(fm, res, select_mode):
     # IndexFlatL2 BF16, d=1536, N(0,1)*0.05, k=32 (nb, nq scaled down); fused GEMM + top-k
-    xb = H.gaussian(60_000, 1536, 5, scale=0.05)
+    xb = H.gaussian(70_000, 1536, 5, scale=0.05)
     xq = H.gaussian(300, 1536, 6, scale=0.05)
     run_case(fm, res, xb, xq, O.METRIC_L2, 2, 32)
 
 
-def test_config4_l2_fp32_large_k_scaled(fm, res):
+def test_config4_l2_fp32_large_k_scaled(fm, res, select_mode):
     # IndexFlatL2 FP32, d=96, mixture of 1,000 gaussians, k=1024 (nb, nq scaled down)
     rng = np.random.default_rng(7)
     centres = rng.uniform(-1, 1, size=(1000, 96)).astype(np.float32)

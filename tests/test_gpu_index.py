@@ -61,7 +61,7 @@ def test_flat_more_shapes(fm, res, path, nv, nq, d, k, storage, metric):
 @pytest.mark.parametrize("path", [PATH_SCAN, PATH_TENSOR])
 @pytest.mark.parametrize("k", [33, 100, 1024, 4096])
 @pytest.mark.parametrize("storage,metric", [(0, O.METRIC_L2), (1, O.METRIC_INNER_PRODUCT)])
-def test_large_k(fm, res, path, k, storage, metric):
+def test_large_k(fm, res, select_mode, path, k, storage, metric):
     # block_select range of the reference (k up to 4096, src/MetalSelect.mm:65-70), which its
     # tests never check
     nv, nq, d = 6000, 6, 48
@@ -121,7 +121,7 @@ def test_scan_streaming_pipeline(fm, res, metric, storage, nv, nq, d, k):
 
 
 @pytest.mark.parametrize("k,storage,metric", [(100, 1, O.METRIC_INNER_PRODUCT), (1024, 0, O.METRIC_L2)])
-def test_large_k_many_queries_deterministic(fm, res, k, storage, metric):
+def test_large_k_many_queries_deterministic(fm, res, select_mode, k, storage, metric):
     # more queries than selection CTAs (each CTA walks several rows) and enough columns for
     # repeated buffer compaction; two runs must agree bit for bit and match the oracle
     nv, nq, d = 40_000, 5_000, 32

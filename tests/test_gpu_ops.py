@@ -237,13 +237,21 @@ def run_search(fm, st, xq, metric, k, path):
     return out_d.cpu().numpy(), out_l.cpu().numpy(), int(status[1])
 
 
-@pytest.mark.parametrize("storage,metric,k,nq", [(2, O.METRIC_L2, 100, 300), (1, O.METRIC_INNER_PRODUCT, 100, 130),
-                                                 (0, O.METRIC_L2, 1024, 40), (2, O.METRIC_L2, 33, 257),
-                                                 (1, O.METRIC_INNER_PRODUCT, 500, 9)])
-def test_list_selection_random_rows(fm, res, storage, metric, k, nq):
-    # 32 < k <= 1024 on the tensor path: results come from the fused kernel's 32-entry lists; with
-    # rows in random order no list overflows, so no row is redone (status word 1 counts them)
-    nb, d = 70_000, 64
+@pytest.mark.parametrize("storage,metric,k,nq,nb", [(2, O.METRIC_L2, 100, 300, 70_000),
+                                                    (1, O.METRIC_INNER_PRODUCT, 100, 130, 70_000),
+                                                    (0, O.METRIC_L2, 1024, 40, 70_000),
+                                                    (2, O.METRIC_L2, 33, 257, 70_000),
+                                                    (1, O.METRIC_INNER_PRODUCT, 500, 9, 70_000),
+                                                    (2, O.METRIC_L2, 10, 600, 70_000),
+                                                    (0, O.METRIC_L2, 32, 100, 70_000),
+                                                    (1, O.METRIC_L2, 1024, 300, 140_000),
+                                                    (2, O.METRIC_INNER_PRODUCT, 200, 50, 140_000)])
+def test_optimistic_selection_random_rows(fm, res, select_mode, storage, metric, k, nq, nb):
+    # Tensor path, k <= 1024.  auto: threshold filter from 64k rows (k <= 128) / 128k rows up,
+    # else selection from the fused kernel's 32-entry lists; no_filter: lists (fused kernel for
+    # k <= 32); matrix_or_fused: key matrix.  With rows in random order no stage has to give up,
+    # so no row is redone (status word 1 counts them), and all modes agree with the oracle.
+    d = 64
     xb = H.gaussian(nb, d, 51)
     xq = H.gaussian(nq, d, 52)
     st = Stored(fm, xb, storage)
@@ -253,25 +261,29 @@ def test_list_selection_random_rows(fm, res, storage, metric, k, nq):
 
 
 @pytest.mark.parametrize("storage,metric,k", [(2, O.METRIC_L2, 100), (0, O.METRIC_L2, 200),
-                                              (1, O.METRIC_INNER_PRODUCT, 64)])
+                                              (1, O.METRIC_INNER_PRODUCT, 64), (2, O.METRIC_L2, 20)])
 @pytest.mark.parametrize("nq,near", [(300, 150), (700, 700), (130, 1)])
-def test_list_selection_redoes_overflowing_rows(fm, res, storage, metric, k, nq, near):
-    # the k nearest rows of `near` queries sit next to each other in the database, so one list
-    # would have to keep more than 32 of a row's results: exactly such rows must be found and
-    # redone through the key matrix; the others keep the list result
+def test_optimistic_selection_redoes_rows(fm, res, select_mode, storage, metric, k, nq, near):
+    # The k nearest rows of `near` queries are the first rows of the database.  They sit next
+    # to each other (one 32-entry list cannot hold them all) and inside the first column tile,
+    # which the pilot pass samples (its threshold then admits fewer than k rows): exactly these
+    # queries must be found and redone; the others keep the optimistic result.
     nb, d = 70_000, 32
     rng = np.random.default_rng(61)
     xb = H.gaussian(nb, d, 62)
     # a cluster far from everything else, wide enough that ||q||^2 + ||x||^2 - 2 q.x does not
     # cancel to nothing inside it
     centre = np.full(d, 2.0, dtype=np.float32)
-    xb[20_000:20_400] = centre + 0.3 * rng.standard_normal((400, d)).astype(np.float32)
+    xb[:250] = centre + 0.3 * rng.standard_normal((250, d)).astype(np.float32)
     xq = H.gaussian(nq, d, 63)
     rows = rng.permutation(nq)[:near]
     xq[rows] = centre + 0.3 * rng.standard_normal((near, d)).astype(np.float32)
     st = Stored(fm, xb, storage)
     D, I, redone = run_search(fm, st, xq, metric, k, 2)
-    if metric == O.METRIC_L2:
+    optimistic = select_mode == "auto" or (select_mode == "no_filter" and k > 32)
+    if not optimistic:
+        assert redone == 0
+    elif metric == O.METRIC_L2:
         assert redone == near
     else:
         assert redone >= near  # a long query also favours the cluster's direction
@@ -279,6 +291,23 @@ def test_list_selection_redoes_overflowing_rows(fm, res, storage, metric, k, nq,
     # the redone rows are counted and compacted on the device: a second run agrees bit for bit
     D2, I2, _ = run_search(fm, st, xq, metric, k, 2)
     assert np.array_equal(I, I2) and np.array_equal(D, D2)
+
+
+@pytest.mark.parametrize("k", [10, 100])
+def test_threshold_filter_overflow_is_redone(fm, res, k):
+    # 30,000 copies of one row: for a query next to it every copy lies under any threshold, the
+    # candidate buffer overflows, and the row must be redone (ties resolved by the lower label)
+    nb, d = 80_000, 32
+    xb = H.gaussian(nb, d, 81)
+    xb[10_000:40_000] = xb[7]
+    xq = H.gaussian(40, d, 82)
+    xq[3] = xb[7] + 0.01
+    xq[17] = xb[7] - 0.01
+    st = Stored(fm, xb, 2)
+    D, I, redone = run_search(fm, st, xq, O.METRIC_L2, k, 2)
+    assert 2 <= redone < 10  # a random query may also have the copied row among its k best
+    H.check_against_oracle(O.METRIC_L2, 2, True, xb, xq, k, D, I, loose=False)
+    assert I[3, 0] == 7 and list(I[3, 1:k]) == list(range(10_000, 10_000 + k - 1))
 
 
 def test_list_selection_small_shard_uses_matrix(fm, res):
