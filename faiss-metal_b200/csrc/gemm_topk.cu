@@ -7,17 +7,30 @@
 // their host dispatch (src/MetalDistance.mm:225-323) and, through the fused
 // epilogue, fused_l2_topk_* (shaders/fused_l2_topk.metal:19-444).
 //
-// Shape of one CTA (192 threads, one CTA per SM, persistent over work items):
-//   warp 0     TMA producer: Q tile (128 x 64) and X tile (256 x 64) per k-block,
-//              128-byte swizzle, 4-stage mbarrier ring
-//   warp 1     MMA issuer: tcgen05.mma kind::f16, M=128 N=256 K=16, fp32 accumulators
-//              in TMEM, two accumulator buffers (2 x 256 columns)
-//   warps 2-5  epilogue: tcgen05.ld (thread t owns query row t of the tile),
-//              one max per column (the L2 bias -||x||^2/2 is part of the dot product:
-//              8 extra K columns, see rows.cu), threshold filter against the row's current
-//              k-th best, insertion into a sorted per-row list held in the thread's registers
-// A work item is (query block, column range); every item yields one sorted
-// partial list per query row, merged afterwards by merge_partials.
+// Two shapes of one kernel (352 threads, one CTA per SM, persistent over work items):
+//  * single CTA (up to 128 queries): tile 128 x 256, cta_group::1, two TMEM accumulators;
+//  * CTA pair (more queries): a cluster of two CTAs computes a 256 x 512 tile with
+//    cta_group::2 MMAs (M = 256); each CTA stages its own 128 query rows and half of the X
+//    rows of every k-block, and holds two 256-column accumulators (all 512 TMEM columns).
+// Roles of the warps:
+//   warp 0      TMA producer: Q tile (128 x 64) and X tile per k-block, 128-byte swizzle,
+//               4-stage mbarrier ring
+//   warps 1,10  MMA issuers: tcgen05.mma kind::f16, N = 256, K = 16, fp32 accumulators in
+//               TMEM.  A chain of MMAs on one accumulator runs at about half the tensor rate,
+//               so the pair shape runs two chains (columns 0-255 and 256-511 of the tile),
+//               one issuing thread each.
+//   warps 2-9   epilogue: tcgen05.ld (thread t owns query row t of the tile, two warps per
+//               TMEM lane quarter, half of the tile's columns each), one max per column (the
+//               L2 bias -||x||^2/2 is part of the dot product: 8 extra K columns, see
+//               rows.cu), filter against the row's bound, hits staged in shared memory and
+//               worked off after the accumulator has been released.
+// Epilogue modes:
+//   top-k   a sorted list of up to 32 entries per (row, column range, column half) in the
+//           thread's registers; every item yields partial lists, merged afterwards
+//   filter  a fixed per-row threshold; every column under it is appended to the row's
+//           candidate buffer in global memory
+//   store   the keys are written out as a matrix (k beyond the list paths, pairwise distances)
+// A work item is (query block, column range).
 //
 // FP32 storage: both operands are split into three bf16 planes
 // (x = x0 + x1 + x2 exactly to 24 bits) and six plane products
@@ -60,9 +73,11 @@ struct Cfg {
     static constexpr int B_ROWS = PAIR ? 128 : 256;        // rows of X this CTA stages per sub-tile
     // A dependent chain of MMAs on ONE accumulator runs at about half the tensor rate (each
     // MMA waits out the read-modify-write turnaround of the one before it); two chains on two
-    // accumulators, issued alternately by the same thread, reach the full rate.  The pair shape
+    // accumulators, one issuing thread each, come close to the full rate.  The pair shape
     // therefore computes two 256-column sub-tiles at once (same query k-block, two X k-blocks,
-    // both TMEM halves); the price is that the epilogue no longer overlaps the next tile's MMAs.
+    // both TMEM halves); the price is that a chain's epilogue no longer overlaps its next MMAs.
+    // Each chain has its own accumulator-full / accumulator-free barriers and its own four
+    // epilogue warps per CTA, so one chain's MMAs do run beside the other chain's epilogue.
     static constexpr int NSUB = PAIR ? 2 : 1;              // 256-column sub-tiles per tile
     static constexpr int TILE_N = NSUB * BN;               // columns of X per tile: 512 / 256
     static constexpr int ACC_BUFS = PAIR ? 1 : 2;          // TMEM accumulator buffers of TILE_N columns
@@ -120,7 +135,6 @@ struct GemmParams {
     float* out;
     int64_t ld;
     int32_t* status;
-    int issuers;         // pair shape: 1 = one thread issues both accumulator chains, 2 = one thread each
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------
@@ -381,11 +395,13 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         *abort_flag = 0;
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, PAIR ? p.issuers : 1);   // one commit per issuing thread
+            mbar_init(bar_empty + s * 8, PAIR ? 2 : 1);   // one commit per issuing thread
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(bar_tfull + s * 8, PAIR ? p.issuers : 1);
-            mbar_init(bar_tempty + s * 8, PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);  // epilogue warps of one / both CTAs
+            // single CTA: barrier s = accumulator buffer s, all epilogue warps;
+            // pair: barrier s = chain s, the warps of that column half in both CTAs
+            mbar_init(bar_tfull + s * 8, 1);
+            mbar_init(bar_tempty + s * 8, NUM_EPI_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -482,7 +498,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // accumulator about one per 290; in the pair shape the two accumulator chains of a tile
         // are therefore issued by two threads (warp 1: columns 0-255, warp MMA2_WARP: 256-511).
         const int chain = (warp == 1) ? 0 : 1;
-        if (lane == 0 && cta_rank == 0 && (chain == 0 || (PAIR && p.issuers == 2))) {
+        if (lane == 0 && cta_rank == 0 && (chain == 0 || PAIR)) {
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -503,7 +519,8 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int64_t t0 = xr * p.tiles_per_range;
                 const int64_t t1 = min(t0 + p.tiles_per_range, p.ntiles);
                 for (int64_t t = t0; t < t1 && ok; t++) {
-                    if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1, abort_flag, p.status)) {
+                    const int bi = PAIR ? chain : acc;  // barrier pair of this chain / buffer
+                    if (!mbar_wait(bar_tempty + bi * 8, acc_phase ^ 1, abort_flag, p.status)) {
                         ok = false;
                         break;
                     }
@@ -527,17 +544,9 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             // advance 32 bytes (16 elements) along K inside the swizzle row
                             if (k4 < nk4) {
                                 if (PAIR) {
-                                    if (p.issuers == 2) {
-                                        tc_mma_f16_pair(d_tmem + chain * BN, da + (uint64_t)(k4 * 2),
-                                                        db + (uint64_t)(chain * (C::B_SUB_BYTES >> 4) + k4 * 2),
-                                                        p.idesc, accumulate);
-                                    } else {
-#pragma unroll
-                                        for (int sub = 0; sub < C::NSUB; sub++)
-                                            tc_mma_f16_pair(d_tmem + sub * BN, da + (uint64_t)(k4 * 2),
-                                                            db + (uint64_t)(sub * (C::B_SUB_BYTES >> 4) + k4 * 2),
-                                                            p.idesc, accumulate);
-                                    }
+                                    tc_mma_f16_pair(d_tmem + chain * BN, da + (uint64_t)(k4 * 2),
+                                                    db + (uint64_t)(chain * (C::B_SUB_BYTES >> 4) + k4 * 2),
+                                                    p.idesc, accumulate);
                                 } else {
                                     tc_mma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2),
                                                p.idesc, accumulate);
@@ -558,9 +567,9 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                     }
                     if (!ok) break;
-                    if (PAIR) {  // accumulator complete, in both CTAs
-                        tc_commit_pair(tfull0 + acc * 8);
-                        tc_commit_pair(tfull1 + acc * 8);
+                    if (PAIR) {  // this chain's accumulator complete, in both CTAs
+                        tc_commit_pair(tfull0 + chain * 8);
+                        tc_commit_pair(tfull1 + chain * 8);
                     } else {
                         tc_commit(tfull0 + acc * 8);
                     }
@@ -624,7 +633,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int64_t t = t0; t < t1 && ok; t++) {
                 const int64_t c_tile = p.col0 + t * p.tile_stride * TILE_N;
                 {
-                    const bool w = mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag, p.status);
+                    const bool w = mbar_wait(bar_tfull + (PAIR ? eh : acc) * 8, acc_phase, abort_flag, p.status);
                     if (!__all_sync(0xffffffffu, w)) {  // keep the warp converged for tcgen05.ld
                         ok = false;
                         break;
@@ -729,7 +738,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + acc * 8, 0));
+                    if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + eh * 8, 0));
                     else mbar_arrive(bar_tempty + acc * 8);
                 }
                 // the accumulator is back with the MMA issuers: now work off the staged hits
@@ -849,11 +858,6 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
     p.P = plan.P;
     p.kb_per_pass = (int)ceil_div64(op.d_pad, BK);
     p.k_extent = op.d_pad;
-    {
-        static int issuers = 0;
-        if (!issuers) { const char* e = getenv("B200F_GEMM_ISSUERS"); issuers = (e && e[0] == '1') ? 1 : 2; }
-        p.issuers = issuers;
-    }
     if (op.npl == 1) {
         p.npass = 1;
         p.pass_a = 0;
