@@ -104,6 +104,24 @@ def test_ties_lower_label_first(fm, res, path):
             idx.close()
 
 
+@pytest.mark.parametrize("k", [10, 32, 100])
+def test_ties_lower_label_first_large_shard(fm, res, select_mode, k):
+    # shard large enough for the threshold filter: every row appears three times, values are
+    # small integers (exact in every storage format), so equal keys are common inside the k best
+    rng = np.random.default_rng(5)
+    base = rng.integers(-3, 4, size=(25_000, 24)).astype(np.float32)
+    xb = np.concatenate([base, base, base])
+    xq = base[rng.permutation(25_000)[:150]].copy()
+    for storage in (0, 2):
+        for metric in (O.METRIC_L2, O.METRIC_INNER_PRODUCT):
+            idx = make_index(fm, res, xb, metric, storage, PATH_TENSOR)
+            D, I = idx.search(xq, k)
+            _, ref_i, ref_d = O.search(metric, xb, xq, k)
+            assert np.array_equal(I, ref_i)
+            np.testing.assert_allclose(D, ref_d, rtol=1e-6, atol=1e-6)
+            idx.close()
+
+
 @pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
 @pytest.mark.parametrize("storage", [0, 1, 2])
 @pytest.mark.parametrize("nv,nq,d,k", [(40_000, 1, 64, 10), (40_000, 4, 128, 32), (40_001, 3, 200, 7),
