@@ -443,6 +443,16 @@ def run_b200(args, w, rank, world, local_rank):
         return
 
     nb_local = hi - lo
+    # DRAM bytes of the dominant kernel from ncu captures on smaller shards of the same workload
+    # (dram__bytes_read.sum + dram__bytes_write.sum of one launch), scaled by the rows a full
+    # launch scans: the traffic of both kernels grows in proportion to the rows of the shard.
+    #   c3: filter-mode gemm_topk_kernel, 1,250,000 rows: 4,694.8 MB + 25.2 MB
+    #   c5: scan_mma_kernel, 8,000,000 rows: 2,176 MB + 3.7 MB
+    traffic = None
+    if args.workload == "c3" and w["nq"] == WORKLOADS["c3"]["nq"]:
+        traffic = (4694.8e6 + 25.2e6) / 1_250_000 * nb_local
+    elif args.workload == "c5":
+        traffic = (2176.0e6 + 3.7e6) / 8_000_000 * nb_local
     flops_per_launch = 2.0 * nq * nb_local * d
     bytes_per_launch = nb_local * d * ELEM_BYTES[w["storage"]] + nq * d * 4 + nq * k * 12
     n_main = max(1, main_launches.value)
@@ -455,7 +465,7 @@ def run_b200(args, w, rank, world, local_rank):
         achieved = flops_per_launch / (main_avg_ms * launches_per_step * 1e-3) / 1e12 if main_avg_ms > 0 else 0.0
         peak = peaks["bf16_tflops_sustained"] if ms_step * args.steps > 1000 else peaks["bf16_tflops"]
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                    "frac": achieved / peak, "traffic": None, "kernel": "gemm_topk_kernel",
+                    "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per step (scaled from an ncu capture)", "kernel": "gemm_topk_kernel",
                     "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
                     "kernel_launches_per_step": launches_per_step,
                     "peak_source": peaks["source"] + (" sustained" if peak == peaks["bf16_tflops_sustained"] else " burst"),
@@ -464,7 +474,7 @@ def run_b200(args, w, rank, world, local_rank):
     else:
         achieved = bytes_per_launch / (main_avg_ms * 1e-3) / 1e9 if main_avg_ms > 0 else 0.0
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "scan_mma_kernel",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "traffic_unit": "bytes per launch (scaled from an ncu capture)", "kernel": "scan_mma_kernel",
                     "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
                     "peak_source": peaks["source"], "frac_of_nominal_8000": achieved / 8000.0}
 
