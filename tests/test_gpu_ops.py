@@ -318,3 +318,35 @@ def test_list_selection_small_shard_uses_matrix(fm, res):
     D, I, redone = run_search(fm, st, xq, O.METRIC_L2, 500, 2)
     assert redone == 0
     H.check_against_oracle(O.METRIC_L2, 2, True, xb, xq, 500, D, I, loose=False)
+
+
+@pytest.mark.parametrize("nq,nb,k,path", [(300, 70_000, 10, 2), (40, 70_000, 100, 2), (1, 200_000, 10, 1),
+                                          (20, 5_000, 64, 2)])
+def test_search_is_enqueue_only_cuda_graph(fm, res, nq, nb, k, path):
+    # b200f_search only enqueues work (rows to redo are counted on the device, nothing is read
+    # back): the whole search can be captured into a CUDA graph and replayed on new queries
+    d = 64
+    xb = H.gaussian(nb, d, 91)
+    st = Stored(fm, xb, 2)
+    xq_dev = torch.from_numpy(H.gaussian(nq, d, 92)).cuda()
+    out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda:0")
+    out_l = torch.empty((nq, k), dtype=torch.int64, device="cuda:0")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        a = st.args(fm, xq_dev, O.METRIC_L2, k, path, out_d, out_l)
+        a.stream = side.cuda_stream
+        fm.abi.check_op(fm.lib().b200f_search(ctypes.byref(a)), "warm-up search")  # one-time attribute calls
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            fm.abi.check_op(fm.lib().b200f_search(ctypes.byref(a)), "captured search")
+        for seed in (93, 94):
+            xq = H.gaussian(nq, d, seed)
+            xq_dev.copy_(torch.from_numpy(xq))
+            out_l.fill_(-7)
+            g.replay()
+            side.synchronize()
+            assert int(st.status[0]) == 0
+            H.check_against_oracle(O.METRIC_L2, 2, True, xb, xq, k, out_d.cpu().numpy(), out_l.cpu().numpy(),
+                                   loose=False)
+    torch.cuda.synchronize()
