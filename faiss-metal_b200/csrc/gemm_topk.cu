@@ -386,6 +386,10 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t bar_tfull = bar_empty + STAGES * 8;
     const uint32_t bar_tempty = bar_tfull + 2 * 8;
 
+    // A launch that redoes rows counted on the device usually finds none: leave before any
+    // barrier or TMEM allocation (the value is the same for every thread of every CTA).
+    if (p.nq_dev && *p.nq_dev <= 0) return;
+
     if ((sbase & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base (same in both CTAs)
         if (threadIdx.x == 0 && p.status) atomicOr(p.status, kDevErrSmemAlign);
         return;
