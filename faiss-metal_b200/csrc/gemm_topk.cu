@@ -45,6 +45,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200f {
 
@@ -60,7 +61,6 @@ constexpr int NUM_EPI_WARPS = 8;   // two per TMEM lane quarter: each takes half
 constexpr int MMA2_WARP = 2 + NUM_EPI_WARPS;   // second MMA issuer (pair shape): one thread per accumulator chain
 constexpr int NUM_THREADS = 32 * (3 + NUM_EPI_WARPS);
 constexpr int TMEM_COLS = 512;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
 // Two shapes of the same kernel:
 //  PAIR = false  one CTA per tile: M = 128 queries, N = 256 rows of X, cta_group::1
@@ -137,57 +137,11 @@ struct GemmParams {
     int32_t* status;
 };
 
-// ---- PTX wrappers --------------------------------------------------------------------
+// ---- PTX wrappers (mbarrier and bounded-wait helpers come from ptx.cuh) -----------------
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t"
-            "}\n"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-    return done;
-}
-
-// Bounded wait.  Returns false when the wait ran out or another thread of the CTA
-// already aborted; the caller must then leave its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int32_t* status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    long long t0 = clock64();
-    int spins = 0;
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 255) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                if (status) atomicOr(status, kDevErrBarrierWait);
-                return false;
-            }
-        }
-    }
+    return mbar_wait_bounded(bar, parity, abort_flag, status, kDevErrBarrierWait);
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -407,7 +361,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             mbar_init(bar_tfull + s * 8, 1);
             mbar_init(bar_tempty + s * 8, NUM_EPI_WARPS);
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 1) {
         if (PAIR) {

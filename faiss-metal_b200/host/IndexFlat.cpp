@@ -490,17 +490,24 @@ struct B200SearchToken::Impl {
     cudaEvent_t done = nullptr;
     bool waited = false;
 
+    // Buffers go back to the resources' pools, where the next token may take them at once:
+    // nothing queued may still use them.  `finished` is set once the token's event was waited for.
+    bool finished = false;
     void release() {
         if (res) {
             int prev = -1;
             (void)cudaGetDevice(&prev);
             (void)cudaSetDevice(res->getDevice());
+            if (!finished && (region || status || host))
+                (void)cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(res->getDefaultStream()));
             if (done) (void)cudaEventDestroy(done);
-            if (region) res->deallocBuffer(region);
-            if (status) res->deallocBuffer(status);
+            if (region) res->releaseDeviceTemp(region);
+            if (status) res->releaseDeviceTemp(status);
+            if (host) res->releasePinnedTemp(host);
             if (prev >= 0) (void)cudaSetDevice(prev);
+        } else {
+            free_pinned(host);
         }
-        free_pinned(host);
         done = nullptr;
         region = nullptr;
         status = nullptr;
@@ -535,6 +542,7 @@ void B200SearchToken::wait() {
     if (impl_->done) {
         DeviceGuard g(impl_->res->getDevice());
         cudaCheck(cudaEventSynchronize(impl_->done), "token wait");
+        impl_->finished = true;
         if (!impl_->distOnDevice)
             std::memcpy(impl_->userDist, impl_->host + impl_->hostDistOff, (size_t)impl_->n * impl_->k * 4);
         if (!impl_->labelsOnDevice)
@@ -587,8 +595,8 @@ B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss
     FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "searchAsync: cannot plan this shape");
     // per-call buffers: the token owns them (src/MetalIndexFlat.mm:441-476)
     CallLayout L = makeLayout(n, batch, d, k, !qOnDevice, n, true, scratchBytes);
-    t->region = impl_->res->allocBuffer(L.total);
-    t->status = static_cast<int32_t*>(impl_->res->allocBuffer(align256((size_t)t->nbatches * 16)));
+    t->region = impl_->res->acquireDeviceTemp(L.total);
+    t->status = static_cast<int32_t*>(impl_->res->acquireDeviceTemp(align256((size_t)t->nbatches * 16)));
     size_t hoff = 0;
     const size_t hostQOff = hoff;
     if (!qOnDevice) hoff += align256((size_t)n * d * 4);
@@ -598,7 +606,7 @@ B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss
     hoff += align256((size_t)n * k * 8);
     t->hostStatusOff = hoff;
     hoff += align256((size_t)t->nbatches * 16);
-    t->host = static_cast<uint8_t*>(alloc_pinned(hoff));
+    t->host = static_cast<uint8_t*>(impl_->res->acquirePinnedTemp(hoff));
     if (!t->host) throw std::runtime_error("faiss-b200: pinned allocation failed");
     uint8_t* region = static_cast<uint8_t*>(t->region);
 

@@ -3,9 +3,12 @@
 // src/MetalDeviceCapabilities.mm:8-124.
 #include <cuda_runtime.h>
 
+#include <mutex>
 #include <sstream>
 #include <stdexcept>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "../../include/b200_flat.h"
 #include "../include/faiss-b200/StandardB200Resources.h"
@@ -80,6 +83,88 @@ std::string describeCapabilities(const B200DeviceCapabilities& caps) {
     return os.str();
 }
 
+namespace {
+
+// Blocks handed out and taken back whole; idle blocks are kept for the next request of a
+// similar size.  `Alloc` / `Free` are the raw allocator of the memory kind.
+class BlockPool {
+   public:
+    static constexpr size_t kMaxIdle = 8;
+    static constexpr size_t kGranule = 1u << 20;
+
+    template <typename Alloc>
+    void* acquire(size_t size, Alloc alloc) {
+        const size_t need = ((size ? size : 1) + kGranule - 1) / kGranule * kGranule;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            int best = -1;
+            for (size_t i = 0; i < idle_.size(); i++)
+                if (idle_[i].second >= need && idle_[i].second <= 2 * need &&
+                    (best < 0 || idle_[i].second < idle_[(size_t)best].second))
+                    best = (int)i;
+            if (best >= 0) {
+                std::pair<void*, size_t> blk = idle_[(size_t)best];
+                idle_.erase(idle_.begin() + best);
+                busy_.push_back(blk);
+                hits_++;
+                return blk.first;
+            }
+            misses_++;
+        }
+        void* p = alloc(need);
+        if (p) {
+            std::lock_guard<std::mutex> g(mu_);
+            busy_.emplace_back(p, need);
+        }
+        return p;
+    }
+
+    template <typename Free>
+    void release(void* p, Free free_fn) {
+        if (!p) return;
+        void* evict = nullptr;
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            size_t size = 0;
+            for (size_t i = 0; i < busy_.size(); i++)
+                if (busy_[i].first == p) {
+                    size = busy_[i].second;
+                    busy_.erase(busy_.begin() + (long)i);
+                    break;
+                }
+            if (size == 0) {  // not ours: hand it straight back
+                evict = p;
+            } else {
+                idle_.emplace_back(p, size);
+                if (idle_.size() > kMaxIdle) {  // drop the block that has been idle longest
+                    evict = idle_.front().first;
+                    idle_.erase(idle_.begin());
+                }
+            }
+        }
+        if (evict) free_fn(evict);
+    }
+
+    template <typename Free>
+    void clear(Free free_fn) {
+        std::lock_guard<std::mutex> g(mu_);
+        for (auto& b : idle_) free_fn(b.first);
+        for (auto& b : busy_) free_fn(b.first);
+        idle_.clear();
+        busy_.clear();
+    }
+
+    size_t hits() const { return hits_; }
+    size_t misses() const { return misses_; }
+
+   private:
+    std::mutex mu_;
+    std::vector<std::pair<void*, size_t>> idle_, busy_;
+    size_t hits_ = 0, misses_ = 0;
+};
+
+}  // namespace
+
 struct StandardB200Resources::Impl {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -88,6 +173,7 @@ struct StandardB200Resources::Impl {
     size_t scratchBytes = 0;
     void* pinned = nullptr;
     size_t pinnedBytes = 0;
+    BlockPool devicePool, pinnedPool;
 };
 
 StandardB200Resources::StandardB200Resources(int device) : impl_(new Impl) {
@@ -119,6 +205,8 @@ StandardB200Resources::~StandardB200Resources() {
     }
     if (impl_->scratch) (void)cudaFree(impl_->scratch);
     if (impl_->pinned) (void)cudaFreeHost(impl_->pinned);
+    impl_->devicePool.clear([](void* p) { (void)cudaFree(p); });
+    impl_->pinnedPool.clear([](void* p) { (void)cudaFreeHost(p); });
     if (prev >= 0) (void)cudaSetDevice(prev);
     (void)cudaGetLastError();
 }
@@ -143,6 +231,41 @@ void StandardB200Resources::deallocBuffer(void* buf) {
     if (!buf) return;
     DeviceGuard g(impl_->device);
     (void)cudaFree(buf);
+}
+
+void* StandardB200Resources::acquireDeviceTemp(size_t size) {
+    DeviceGuard g(impl_->device);
+    void* p = impl_->devicePool.acquire(size, [](size_t n) -> void* {
+        void* q = nullptr;
+        if (cudaMalloc(&q, n) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        return q;
+    });
+    if (!p)
+        throw std::runtime_error("faiss-b200: failed to allocate device buffer of " + std::to_string(size) +
+                                 " bytes");
+    return p;
+}
+
+void StandardB200Resources::releaseDeviceTemp(void* buf) {
+    if (!buf) return;
+    DeviceGuard g(impl_->device);
+    impl_->devicePool.release(buf, [](void* p) { (void)cudaFree(p); });
+}
+
+void* StandardB200Resources::acquirePinnedTemp(size_t size) {
+    return impl_->pinnedPool.acquire(size, [](size_t n) -> void* { return alloc_pinned(n); });
+}
+
+void StandardB200Resources::releasePinnedTemp(void* buf) {
+    impl_->pinnedPool.release(buf, [](void* p) { free_pinned(p); });
+}
+
+size_t StandardB200Resources::tempPoolHits() const { return impl_->devicePool.hits() + impl_->pinnedPool.hits(); }
+size_t StandardB200Resources::tempPoolMisses() const {
+    return impl_->devicePool.misses() + impl_->pinnedPool.misses();
 }
 
 void* StandardB200Resources::getScratch(size_t bytes) {

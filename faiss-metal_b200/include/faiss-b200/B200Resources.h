@@ -33,6 +33,16 @@ class B200Resources {
     virtual void* allocBuffer(size_t size) = 0;
     virtual void deallocBuffer(void* buf) = 0;
 
+    /// Buffers of in-flight asynchronous searches (device memory and pinned host memory).  Same
+    /// contract as allocBuffer / alloc_pinned, but an implementation may recycle them: a
+    /// released buffer must no longer be in use by any queued work.  The reference allocates
+    /// fresh MTLBuffers per searchAsync call (src/MetalIndexFlat.mm:441-476); on CUDA that would
+    /// put a cudaMalloc / cudaFree (a device-wide synchronisation) into every call.
+    virtual void* acquireDeviceTemp(size_t size) { return allocBuffer(size); }
+    virtual void releaseDeviceTemp(void* buf) { deallocBuffer(buf); }
+    virtual void* acquirePinnedTemp(size_t size) { return alloc_pinned(size); }  ///< nullptr on failure
+    virtual void releasePinnedTemp(void* buf) { free_pinned(buf); }
+
     /// Grow-only scratch region shared by the synchronous searches of every index
     /// that uses these resources (src/MetalIndexFlat.mm:102-142 kept one per index).
     /// The pointer stays valid until the next call with a larger size; work using it

@@ -22,6 +22,16 @@ class StandardB200Resources : public B200Resources {
     size_t getScratchSize() const override;
     void* getPinnedStaging(size_t bytes) override;
 
+    /// Recycling pools (at most 8 idle blocks each; a request takes the smallest idle block of
+    /// at least its size and at most twice its size, else allocates).
+    void* acquireDeviceTemp(size_t size) override;
+    void releaseDeviceTemp(void* buf) override;
+    void* acquirePinnedTemp(size_t size) override;
+    void releasePinnedTemp(void* buf) override;
+    /// Requests served from idle blocks / by a fresh allocation since construction.
+    size_t tempPoolHits() const;
+    size_t tempPoolMisses() const;
+
    private:
     struct Impl;
     std::unique_ptr<Impl> impl_;

@@ -126,6 +126,26 @@ static void testErrorsAndTokens(std::shared_ptr<B200Resources> res) {
         { B200SearchToken t = idx.searchAsync(1, v.data() + 32, 5, d2.data(), l2.data()); }  // destructor waits
         CHECK(l2[0] == 1);
     }
+    // several tokens in flight at once, then a second round: the second round's buffers come
+    // out of the resources' pools (no fresh allocation), results stay right
+    {
+        auto* sres = dynamic_cast<StandardB200Resources*>(res.get());
+        CHECK(sres != nullptr);
+        for (int round = 0; round < 2; round++) {
+            const size_t missesBefore = sres->tempPoolMisses();
+            std::vector<std::vector<float>> ds(4, std::vector<float>(3 * 5));
+            std::vector<std::vector<faiss::idx_t>> ls(4, std::vector<faiss::idx_t>(3 * 5, -7));
+            std::vector<B200SearchToken> tokens;
+            for (int i = 0; i < 4; i++)
+                tokens.push_back(idx.searchAsync(3, v.data() + (size_t)(10 * i) * 32, 5, ds[i].data(), ls[i].data()));
+            for (int i = 0; i < 4; i++) {
+                tokens[i].wait();
+                for (int q = 0; q < 3; q++) CHECK(ls[i][q * 5] == 10 * i + q);
+            }
+            if (round == 1) CHECK(sres->tempPoolMisses() == missesBefore);
+        }
+        CHECK(sres->tempPoolHits() > 0);
+    }
     idx.reset();
     CHECK(idx.ntotal == 0);
     idx.add(50, v.data());
