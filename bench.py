@@ -380,7 +380,8 @@ def run_b200(args, w, rank, world, local_rank):
         # ---- latency distribution of a stream of single searches (small-nq workloads) ------
         latency = None
         if nq <= 4 and not args.no_e2e:
-            ncalls = 1000
+            # 10,000 calls unless that would take much longer than ~25 s
+            ncalls = max(1000, min(10000, int(25000.0 / max(ms_step, 0.05))))
             qbank = torch.empty((64 * nq, d), dtype=torch.float32, device="cuda")
             fm.abi.check_op(L.b200f_fill_synthetic(ctypes.c_void_p(qbank.data_ptr()), 64 * nq, d, 0, 3, w["dist"],
                                                    w["scale"], ctypes.c_void_p(ext.cuda_stream)), "fill query bank")
