@@ -23,12 +23,14 @@ HOST_CXX = shutil.which("g++") or "g++"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CU_SOURCES = ["csrc/rows.cu", "csrc/scan.cu", "csrc/select.cu", "csrc/gemm_topk.cu", "csrc/search.cu"]
-CPP_SOURCES = ["host/Resources.cpp", "host/IndexFlat.cpp", "host/capi.cpp", "faiss_compat/compat_impl.cpp"]
+CPP_SOURCES = ["host/Resources.cpp", "host/GrowableArray.cpp", "host/IndexFlat.cpp", "host/capi.cpp",
+               "faiss_compat/compat_impl.cpp"]
 HEADERS = [
     "csrc/common.cuh",
     "../include/b200_flat.h",
     "include/faiss-b200/B200IndexFlat.h",
     "include/faiss-b200/B200Resources.h",
+    "host/GrowableArray.h",
     "include/faiss-b200/StandardB200Resources.h",
     "include/faiss-b200/B200DeviceCapabilities.h",
     "faiss_compat/faiss/Index.h",

@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <stdexcept>
@@ -18,6 +19,7 @@
 #include "../../include/b200_flat.h"
 #include "../include/faiss-b200/B200IndexFlat.h"
 #include "../include/faiss-b200/B200Resources.h"
+#include "GrowableArray.h"
 
 namespace faiss_b200 {
 
@@ -95,19 +97,89 @@ struct B200IndexFlat::Impl {
     cudaStream_t stream() const { return reinterpret_cast<cudaStream_t>(res->getDefaultStream()); }
     int storageCode() const { return (int)storage; }
 
+    // Storage that grows in place (address range reserved once, memory mapped in as rows are
+    // added; see GrowableArray.h).  When the driver calls are not available, or
+    // B200F_NO_VMM=1 is set in the environment (testing), plain allocations with the
+    // reference's allocate-copy-free growth are used instead.
+    GrowableDeviceArray vRows, vPlanes, vNorms;
+    bool inPlace = false;
+    int64_t maxRows = 0;          // rows the reserved ranges can hold
+    int64_t planeStrideFixed = 0;  // elements between split planes when inPlace
+
+    int64_t planeStride() const { return inPlace ? planeStrideFixed : capacity * planePitch; }
+
     void freeStorage() {
-        if (rows) res->deallocBuffer(rows);
-        if (planes) res->deallocBuffer(planes);
-        if (norms) res->deallocBuffer(norms);
+        if (inPlace) {
+            vRows.release();
+            vPlanes.release();
+            vNorms.release();
+            inPlace = false;
+        } else {
+            if (rows) res->deallocBuffer(rows);
+            if (planes) res->deallocBuffer(planes);
+            if (norms) res->deallocBuffer(norms);
+        }
         rows = nullptr;
         planes = nullptr;
         norms = nullptr;
         capacity = 0;
     }
 
+    // First allocation of an empty index: reserve the address ranges.  Returns false (nothing
+    // reserved) when in-place growth cannot be used.
+    bool reserveInPlace() {
+        const char* off = std::getenv("B200F_NO_VMM");
+        if (off && off[0] == '1') return false;
+        const int dev = res->getDevice();
+        if (!GrowableDeviceArray::supported(dev)) return false;
+        const size_t es = elemBytes(storage);
+        const size_t rowBytes = (size_t)pitch * es;
+        // no shard can hold more rows than fit the device memory (or the int32 row numbers)
+        size_t freeB = 0, totalB = 0;
+        if (cudaMemGetInfo(&freeB, &totalB) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        int64_t cap = (int64_t)(totalB / rowBytes);
+        cap = std::min<int64_t>(cap, B200DeviceCapabilities::kMaxVectorsPerShard);
+        cap = std::max<int64_t>(cap, 1024);
+        // planes start on 2 MiB multiples of a common stride, so that each one is backed on its own
+        const size_t planeBytes = roundUp((int64_t)((size_t)cap * planePitch * 2), 2ll << 20);
+        bool ok = vRows.reserve(dev, (size_t)cap * rowBytes);
+        if (ok && storage == StorageType::Float32) ok = vPlanes.reserve(dev, 3 * planeBytes);
+        if (ok && l2) ok = vNorms.reserve(dev, (size_t)cap * 4);
+        if (!ok) {
+            vRows.release();
+            vPlanes.release();
+            vNorms.release();
+            return false;
+        }
+        maxRows = cap;
+        planeStrideFixed = (int64_t)(planeBytes / 2);
+        rows = vRows.data();
+        planes = storage == StorageType::Float32 ? static_cast<uint16_t*>(vPlanes.data()) : nullptr;
+        norms = l2 ? static_cast<float*>(vNorms.data()) : nullptr;
+        inPlace = true;
+        return true;
+    }
+
     // Grow to hold at least `want` rows; keeps the first `keep` rows.
     void grow(int64_t want, int64_t keep) {
         if (want <= capacity) return;
+        if (capacity == 0 && !rows && !inPlace) (void)reserveInPlace();
+        if (inPlace) {
+            if (want > maxRows)
+                throw std::runtime_error("faiss-b200: the index cannot hold " + std::to_string(want) +
+                                         " rows on this device");
+            const size_t es = elemBytes(storage);
+            vRows.back(0, (size_t)want * pitch * es);
+            if (planes)
+                for (int p = 0; p < 3; p++)
+                    vPlanes.back((size_t)p * planeStrideFixed * 2, (size_t)want * planePitch * 2);
+            if (norms) vNorms.back(0, (size_t)want * 4);
+            capacity = want;
+            return;
+        }
         const size_t es = elemBytes(storage);
         void* newRows = res->allocBuffer((size_t)want * pitch * es);
         uint16_t* newPlanes = nullptr;
@@ -151,7 +223,7 @@ struct B200IndexFlat::Impl {
         a.row_pitch = pitch;
         a.planes = planes;
         a.plane_pitch = planePitch;
-        a.plane_stride = capacity * planePitch;
+        a.plane_stride = planeStride();
         a.norms = norms;
         a.nb = ntotal;
         a.metric = l2 ? B200F_METRIC_L2 : B200F_METRIC_INNER_PRODUCT;
@@ -271,7 +343,7 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
                          src, nr, d, impl_->storageCode(),
                          static_cast<uint8_t*>(impl_->rows) + (size_t)row * impl_->pitch * es, impl_->pitch,
                          impl_->planes ? impl_->planes + (size_t)row * impl_->planePitch : nullptr,
-                         impl_->planePitch, impl_->capacity * impl_->planePitch,
+                         impl_->planePitch, impl_->planeStride(),
                          impl_->norms ? impl_->norms + row : nullptr, impl_->l2 ? 1 : 0, st),
                  "add: store rows");
     }

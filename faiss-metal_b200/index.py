@@ -180,6 +180,10 @@ class B200IndexFlat:
     def set_label_base(self, base: int):
         abi.check(abi.lib().b200f_index_set_label_base(self._h, int(base)), "set_label_base")
 
+    def device_rows(self) -> int:
+        """Device address of the stored rows (0 for an empty index)."""
+        return int(abi.lib().b200f_index_device_rows(self._h) or 0)
+
     @property
     def last_device_status(self) -> int:
         return abi.lib().b200f_index_last_device_status(self._h)

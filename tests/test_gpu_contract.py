@@ -132,21 +132,66 @@ def test_search_async_is_ready(fm, res):
     idx.close()
 
 
+@pytest.fixture(params=["in_place", "copying"])
+def growth_mode(request):
+    # in_place: rows are mapped into a reserved address range as the index grows (no copies);
+    # copying: B200F_NO_VMM=1, plain allocations with the reference's allocate-copy-free growth
+    import os
+    old = os.environ.pop("B200F_NO_VMM", None)
+    if request.param == "copying":
+        os.environ["B200F_NO_VMM"] = "1"
+    yield request.param
+    os.environ.pop("B200F_NO_VMM", None)
+    if old is not None:
+        os.environ["B200F_NO_VMM"] = old
+
+
 @pytest.mark.parametrize("storage", [0, 2])
-def test_growth_over_many_adds(fm, res, storage):
-    # growth rule max(new, 2*cap, 1024) with copies (src/MetalIndexFlat.mm:196-208)
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+def test_growth_over_many_adds(fm, res, growth_mode, storage, metric):
+    # capacity rule max(new, 2*cap, 1024) (src/MetalIndexFlat.mm:196-208)
     d = 40
     xb = H.uniform_pm1(5000, d, 9)
-    idx = fm.B200IndexFlat(res, d, O.METRIC_L2, storage)
+    idx = fm.B200IndexFlat(res, d, metric, storage)
+    base0 = None
     pos = 0
     for n in (1, 7, 1000, 30, 2500, 1462):
         idx.add(xb[pos:pos + n])
         pos += n
+        if base0 is None:
+            base0 = idx.device_rows()
+        elif growth_mode == "in_place":
+            assert idx.device_rows() == base0   # the array never moves
     assert pos == 5000 and idx.ntotal == 5000
     assert np.array_equal(idx.reconstruct_n(0, 5000), O.round_storage(xb, storage))
     xq = H.uniform_pm1(9, d, 10)
     D, I = idx.search(xq, 10)
-    H.check_against_oracle(O.METRIC_L2, storage, True, xb, xq, 10, D, I)
+    H.check_against_oracle(metric, storage, True, xb, xq, 10, D, I)
+    # reset drops the storage; the index can be filled again
+    idx.reset()
+    assert idx.ntotal == 0
+    idx.add(xb[:1500])
+    D, I = idx.search(xq, 10)
+    H.check_against_oracle(metric, storage, True, xb[:1500], xq, 10, D, I)
+    idx.close()
+
+
+def test_large_growth_in_place_keeps_rows(fm, res, growth_mode):
+    # 300,000 rows of d = 256 in bf16 (158 MB) added in uneven pieces, with reserve() in the middle
+    d = 256
+    xb = H.gaussian(300_000, d, 33, scale=0.05)
+    idx = fm.B200IndexFlat(res, d, O.METRIC_L2, 2)
+    idx.add(xb[:10])
+    idx.add(xb[10:70_000])
+    idx.reserve(250_000)
+    idx.add(xb[70_000:240_000])
+    idx.add(xb[240_000:])
+    assert idx.ntotal == 300_000
+    back = idx.reconstruct_n(0, 300_000)
+    assert np.array_equal(back, O.round_storage(xb, 2))
+    xq = H.gaussian(33, d, 34, scale=0.05)
+    D, I = idx.search(xq, 10)
+    H.check_against_oracle(O.METRIC_L2, 2, True, xb, xq, 10, D, I)
     idx.close()
 
 
