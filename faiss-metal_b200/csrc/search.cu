@@ -69,11 +69,20 @@ struct SearchPlan {
     size_t total;
 };
 
-// B200F_NO_FILTER=1 in the environment switches the threshold-filter path off (same use).
+// B200F_NO_FILTER=1 in the environment switches the threshold-filter path off, B200F_FILTER=1
+// takes it whenever the shard is large enough for a pilot sample, however little work the
+// search is (same use).
 bool filter_disabled() {
     const char* e = getenv("B200F_NO_FILTER");
     return e && e[0] == '1';
 }
+bool filter_forced() {
+    const char* e = getenv("B200F_FILTER");
+    return e && e[0] == '1';
+}
+// The pilot pass costs 0.1 - 0.2 ms whatever the size (a handful of work items, each warming up
+// its lists on a single tile): below this many (query, row) pairs the fused lists are faster.
+constexpr int64_t FILTER_MIN_PAIRS = 1ll << 30;
 
 // B200F_NO_LISTS=1 in the environment sends every k > 32 search through the key matrix.  Read at
 // every call, so that a test can switch between the paths inside one process.
@@ -105,7 +114,7 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         // than k rows of the shard lie under it only if the sample caught r of the k best, which
         // is about one row in a million; about r * stride rows do lie under it.
         const int stride = k <= 128 ? 64 : 128;
-        if (nb >= (int64_t)stride * 1024) {
+        if (nb >= (int64_t)stride * 1024 && (nq * nb >= FILTER_MIN_PAIRS || filter_forced())) {
             const double e = (double)k / stride;
             int r = (int)(e + 4.5 * std::sqrt(e) + 3.0 + 0.999);
             if (r > B200F_FUSED_MAX_K) r = B200F_FUSED_MAX_K;

@@ -37,7 +37,7 @@ def res(fm):
 SELECT_MODES = {
     # which optimistic selection stages of the tensor path are allowed (environment switches of
     # the library, read at every call)
-    "auto": {},
+    "filter": {"B200F_FILTER": "1"},   # threshold filter wherever the shard allows a pilot sample
     "no_filter": {"B200F_NO_FILTER": "1"},
     "matrix_or_fused": {"B200F_NO_FILTER": "1", "B200F_NO_LISTS": "1"},
 }
@@ -47,7 +47,7 @@ SELECT_MODES = {
 def select_mode(request):
     import os
     env = SELECT_MODES[request.param]
-    old = {k: os.environ.get(k) for k in ("B200F_NO_FILTER", "B200F_NO_LISTS")}
+    old = {k: os.environ.get(k) for k in ("B200F_FILTER", "B200F_NO_FILTER", "B200F_NO_LISTS")}
     for k in old:
         os.environ.pop(k, None)
     os.environ.update(env)

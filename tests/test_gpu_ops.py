@@ -247,7 +247,7 @@ def run_search(fm, st, xq, metric, k, path):
                                                     (1, O.METRIC_L2, 1024, 300, 140_000),
                                                     (2, O.METRIC_INNER_PRODUCT, 200, 50, 140_000)])
 def test_optimistic_selection_random_rows(fm, res, select_mode, storage, metric, k, nq, nb):
-    # Tensor path, k <= 1024.  auto: threshold filter from 64k rows (k <= 128) / 128k rows up,
+    # Tensor path, k <= 1024.  filter: threshold filter from 64k rows (k <= 128) / 128k rows up,
     # else selection from the fused kernel's 32-entry lists; no_filter: lists (fused kernel for
     # k <= 32); matrix_or_fused: key matrix.  With rows in random order no stage has to give up,
     # so no row is redone (status word 1 counts them), and all modes agree with the oracle.
@@ -280,7 +280,7 @@ def test_optimistic_selection_redoes_rows(fm, res, select_mode, storage, metric,
     xq[rows] = centre + 0.3 * rng.standard_normal((near, d)).astype(np.float32)
     st = Stored(fm, xb, storage)
     D, I, redone = run_search(fm, st, xq, metric, k, 2)
-    optimistic = select_mode == "auto" or (select_mode == "no_filter" and k > 32)
+    optimistic = select_mode == "filter" or (select_mode == "no_filter" and k > 32)
     if not optimistic:
         assert redone == 0
     elif metric == O.METRIC_L2:
@@ -293,8 +293,19 @@ def test_optimistic_selection_redoes_rows(fm, res, select_mode, storage, metric,
     assert np.array_equal(I, I2) and np.array_equal(D, D2)
 
 
+@pytest.fixture
+def force_filter():
+    import os
+    old = os.environ.get("B200F_FILTER")
+    os.environ["B200F_FILTER"] = "1"
+    yield
+    os.environ.pop("B200F_FILTER", None)
+    if old is not None:
+        os.environ["B200F_FILTER"] = old
+
+
 @pytest.mark.parametrize("k", [10, 100])
-def test_threshold_filter_overflow_is_redone(fm, res, k):
+def test_threshold_filter_overflow_is_redone(fm, res, force_filter, k):
     # 30,000 copies of one row: for a query next to it every copy lies under any threshold, the
     # candidate buffer overflows, and the row must be redone (ties resolved by the lower label)
     nb, d = 80_000, 32
@@ -322,7 +333,7 @@ def test_list_selection_small_shard_uses_matrix(fm, res):
 
 @pytest.mark.parametrize("nq,nb,k,path", [(300, 70_000, 10, 2), (40, 70_000, 100, 2), (1, 200_000, 10, 1),
                                           (20, 5_000, 64, 2)])
-def test_search_is_enqueue_only_cuda_graph(fm, res, nq, nb, k, path):
+def test_search_is_enqueue_only_cuda_graph(fm, res, force_filter, nq, nb, k, path):
     # b200f_search only enqueues work (rows to redo are counted on the device, nothing is read
     # back): the whole search can be captured into a CUDA graph and replayed on new queries
     d = 64
