@@ -105,9 +105,11 @@ int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0,
 // Threshold filter over the whole shard: column c of row q with scaled key <= thr[q * thr_stride +
 // thr_pos] is appended to the row's candidate buffer cand_key/cand_idx [nq][cand_cap] in any
 // order; cand_cnt[q] counts every hit, also those beyond cand_cap, which are not stored.
+// few_hits: the threshold admits well under one column in a thousand (tunes the scan width).
 int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscale, const float* thr,
                        int thr_stride, int thr_pos, float* cand_key, int32_t* cand_idx,
-                       int32_t* cand_cnt, int cand_cap, int32_t* status, cudaStream_t stream);
+                       int32_t* cand_cnt, int cand_cap, int few_hits, int32_t* status,
+                       cudaStream_t stream);
 // Store mode: out[row*ld + (col-col0)] = sign*(-kscale*t) + rowadd[row], t = q.x (- ||x||^2/2).
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
                       float kscale, float sign, const float* rowadd, float* out,

@@ -30,7 +30,9 @@
 //   filter  a fixed per-row threshold; every column under it is appended to the row's
 //           candidate buffer in global memory
 //   store   the keys are written out as a matrix (k beyond the list paths, pairwise distances)
-// A work item is (query block, column range).
+// The mode is a template parameter (six instantiations with the two shapes): the filter and
+// store kernels carry no list registers, which lets the filter kernel read 64 accumulator
+// columns per TMEM load.  A work item is (query block, column range).
 //
 // FP32 storage: both operands are split into three bf16 planes
 // (x = x0 + x1 + x2 exactly to 24 bits) and six plane products
@@ -43,6 +45,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -132,6 +135,7 @@ struct GemmParams {
     int32_t* cand_idx;
     int32_t* cand_cnt;   // [nq]
     int cand_cap;
+    int wide;            // MODE_FILTER: 64 columns per TMEM load (few hits expected), else 32
     float* out;
     int64_t ld;
     int32_t* status;
@@ -242,6 +246,28 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
             : "r"(taddr)
             : "memory");
 }
+// 32 lanes x 64 consecutive fp32 columns -> 64 registers per thread
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+            "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+            "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+              "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+              "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]),
+              "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]),
+              "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+              "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]),
+              "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]),
+              "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+            : "r"(taddr)
+            : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -314,7 +340,8 @@ __device__ __forceinline__ void drain_to_buffer(int32_t* cnt, float* ck, int32_t
     }
 }
 
-template <bool PAIR>
+// MODE is a template parameter: the filter and store instantiations carry no list registers.
+template <bool PAIR, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
@@ -570,13 +597,13 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             float thr_eff = CUDART_INF_F;  // filter: min(thr, bound shared by all ranges of the row)
             float thr_pub = CUDART_INF_F;  // last value published to gthr
             float radd = 0.f;
-            if (p.mode == MODE_TOPK) {
+            if (MODE == MODE_TOPK) {
 #pragma unroll
                 for (int j = 0; j < KMAX; j++) {
                     lk[j] = (j >= KMAX - k) ? CUDART_INF_F : -CUDART_INF_F;
                     li[j] = -1;
                 }
-            } else if (p.mode == MODE_FILTER) {
+            } else if (MODE == MODE_FILTER) {
                 // keys <= threshold pass: the filter below is exclusive, so take the next float up
                 // (+INF, the threshold of a row whose sample was too small, stays; -INF passes nothing)
                 thr_eff = -CUDART_INF_F;
@@ -598,7 +625,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
                 tc_fence_after();
-                if (p.mode == MODE_TOPK && row_live) {
+                if (MODE == MODE_TOPK && row_live) {
                     // A full list's worst key bounds the row's 32nd best from above; the largest
                     // of gslots such keys (distinct lists) bounds the (32 * gslots)-th best, which
                     // is at or beyond the k-th.  Publish ours, adopt the bound.  A key equal to
@@ -618,25 +645,33 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // column are zero-filled by TMA (t = 0) and must be masked out.
                 const bool partial = c_tile + TILE_N > p.ncols_end;
                 const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + acc * TILE_N;
+                if constexpr (MODE != MODE_STORE) {
+                // CW columns per TMEM load.  64 saves ~3 % of the tile time when hits are rare
+                // (filter mode has the registers for it: no lists to keep); with a hit in most
+                // chunks the 64-column masks cost more than the wider load saves.
+                auto scan = [&](auto cw_tag) {
+                constexpr int CW = decltype(cw_tag)::value;
 #pragma unroll 1
-                for (int ch = eh * CH_PER_HALF; ch < (eh + 1) * CH_PER_HALF; ch++) {
-                    uint32_t r[32];
-                    tc_ld32(taddr + ch * 32, r);
+                for (int ch = 0; ch < CH_PER_HALF * 32 / CW; ch++) {
+                    uint32_t r[CW];
+                    const int col = eh * CH_PER_HALF * 32 + ch * CW;  // first column inside the tile
+                    if constexpr (CW == 64) tc_ld64(taddr + col, r);
+                    else tc_ld32(taddr + col, r);
                     tc_wait_ld();
-                    const int64_t cbase = c_tile + ch * 32;
-                    if (p.mode != MODE_STORE) {
+                    const int64_t cbase = c_tile + col;
+                    {
                         if (partial) {
 #pragma unroll
-                            for (int c = 0; c < 32; c++)
+                            for (int c = 0; c < CW; c++)
                                 if (cbase + c >= p.ncols_end) r[c] = 0xff800000u;  // -INF
                         }
-                        // one max per column (tree), one compare per 32 columns
-                        float m[16];
+                        // one max per column (tree), one compare per CW columns
+                        float m[CW / 2];
 #pragma unroll
-                        for (int c = 0; c < 16; c++)
-                            m[c] = fmaxf(__uint_as_float(r[c]), __uint_as_float(r[c + 16]));
+                        for (int c = 0; c < CW / 2; c++)
+                            m[c] = fmaxf(__uint_as_float(r[c]), __uint_as_float(r[c + CW / 2]));
 #pragma unroll
-                        for (int w2 = 8; w2 > 0; w2 >>= 1)
+                        for (int w2 = CW / 4; w2 > 0; w2 >>= 1)
 #pragma unroll
                             for (int c = 0; c < w2; c++) m[c] = fmaxf(m[c], m[c + w2]);
                         // Slow path, entered by the whole warp when any row has a candidate in
@@ -644,33 +679,52 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const bool any_hit = row_live && (-m[0] < thr_eff);
                         if (__any_sync(0xffffffffu, any_hit)) {
                             if (any_hit) {
-                                uint32_t mask = 0;
 #pragma unroll
-                                for (int c = 0; c < 32; c++)
-                                    mask |= (-__uint_as_float(r[c]) < thr_eff ? 1u : 0u) << c;
-                                while (mask != 0) {
-                                    const int cc = __ffs(mask) - 1;
-                                    mask &= mask - 1;
-                                    uint32_t bits = 0;
+                                for (int h = 0; h < CW / 32; h++) {
+                                    uint32_t mask = 0;
 #pragma unroll
-                                    for (int c = 0; c < 32; c++) bits = (c == cc) ? r[c] : bits;
-                                    if (nstaged == STAGE_N) {  // rare: list warm-up, massive ties
-                                        if (p.mode == MODE_TOPK)
-                                            drain_to_list(lk, li, stage_key, stage_idx, nstaged, thr, thr_eff);
-                                        else
-                                            drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
-                                                            p.cand_idx + grow * p.cand_cap, p.cand_cap, p.kscale,
-                                                            stage_key, stage_idx, nstaged);
-                                        nstaged = 0;
+                                    for (int c = 0; c < 32; c++)
+                                        mask |= (-__uint_as_float(r[h * 32 + c]) < thr_eff ? 1u : 0u) << c;
+                                    while (mask != 0) {
+                                        const int cc = __ffs(mask) - 1;
+                                        mask &= mask - 1;
+                                        uint32_t bits = 0;
+#pragma unroll
+                                        for (int c = 0; c < 32; c++) bits = (c == cc) ? r[h * 32 + c] : bits;
+                                        if (nstaged == STAGE_N) {  // rare: list warm-up, massive ties
+                                            if (MODE == MODE_TOPK)
+                                                drain_to_list(lk, li, stage_key, stage_idx, nstaged, thr, thr_eff);
+                                            else
+                                                drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
+                                                                p.cand_idx + grow * p.cand_cap, p.cand_cap,
+                                                                p.kscale, stage_key, stage_idx, nstaged);
+                                            nstaged = 0;
+                                        }
+                                        stage_key[nstaged * STAGE_LD] = -__uint_as_float(bits);
+                                        stage_idx[nstaged * STAGE_LD] = (int32_t)cbase + h * 32 + cc;
+                                        nstaged++;
                                     }
-                                    stage_key[nstaged * STAGE_LD] = -__uint_as_float(bits);
-                                    stage_idx[nstaged * STAGE_LD] = (int32_t)cbase + cc;
-                                    nstaged++;
                                 }
                             }
                             __syncwarp();
                         }
-                    } else {
+                    }
+                }
+                };
+                if constexpr (MODE == MODE_FILTER) {
+                    if (p.wide) scan(std::integral_constant<int, 64>{});
+                    else scan(std::integral_constant<int, 32>{});
+                } else {
+                    scan(std::integral_constant<int, 32>{});
+                }
+                } else {
+#pragma unroll 1
+                for (int ch = eh * CH_PER_HALF; ch < (eh + 1) * CH_PER_HALF; ch++) {
+                    uint32_t r[32];
+                    tc_ld32(taddr + ch * 32, r);
+                    tc_wait_ld();
+                    const int64_t cbase = c_tile + ch * 32;
+                    {
                         // Store mode: thread t holds 32 consecutive columns of ITS row; writing
                         // them directly would touch 32 different rows per instruction.  The warp
                         // transposes the 32 x 32 block through shared memory (the list area is
@@ -693,6 +747,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         __syncwarp();
                     }
                 }
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
@@ -701,7 +756,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 // the accumulator is back with the MMA issuers: now work off the staged hits
                 if (nstaged > 0) {
-                    if (p.mode == MODE_TOPK)
+                    if (MODE == MODE_TOPK)
                         drain_to_list(lk, li, stage_key, stage_idx, nstaged, thr, thr_eff);
                     else
                         drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
@@ -717,7 +772,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     acc_phase ^= 1;
                 }
             }
-            if (p.mode == MODE_TOPK && row_live && ok) {
+            if (MODE == MODE_TOPK && row_live && ok) {
                 if (thr < thr_pub) atomicMin(gslot, float_to_ordered(thr));
                 // two lists per (row, column range): one per column half
                 float* okey = p.part_key + (grow * (2 * p.P) + 2 * xr + eh) * k - (KMAX - k);
@@ -831,16 +886,23 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
               ((uint32_t)((plan.pair ? 2 * BM : BM) >> 4) << 24);
 
+    typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+    static const KernelFn kernels[2][3] = {
+            {gemm_topk_kernel<false, MODE_TOPK>, gemm_topk_kernel<false, MODE_STORE>,
+             gemm_topk_kernel<false, MODE_FILTER>},
+            {gemm_topk_kernel<true, MODE_TOPK>, gemm_topk_kernel<true, MODE_STORE>,
+             gemm_topk_kernel<true, MODE_FILTER>}};
     static bool attr_set = false;
     if (!attr_set) {
-        B200F_CUDA_TRY(cudaFuncSetAttribute(gemm_topk_kernel<false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            Cfg<false>::SMEM_BYTES));
-        B200F_CUDA_TRY(cudaFuncSetAttribute(gemm_topk_kernel<true>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            Cfg<true>::SMEM_BYTES));
+        for (int pr = 0; pr < 2; pr++)
+            for (int m = 0; m < 3; m++)
+                B200F_CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[pr][m]),
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    pr ? Cfg<true>::SMEM_BYTES : Cfg<false>::SMEM_BYTES));
         attr_set = true;
     }
+    if (p.mode < 0 || p.mode > 2) return B200F_ERR_BAD_ARG;
+    const KernelFn kernel = kernels[plan.pair ? 1 : 0][p.mode];
     main_kernel_begin(stream);
     if (plan.pair) {
         cudaLaunchConfig_t cfg = {};
@@ -855,14 +917,14 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_topk_kernel<true>, ma, mb, p);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, p);
         if (e != cudaSuccess) {
             (void)cudaGetLastError();
             main_kernel_end(stream);
             return B200F_ERR_CUDA;
         }
     } else {
-        gemm_topk_kernel<false><<<plan.grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, stream>>>(ma, mb, p);
+        kernel<<<plan.grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, stream>>>(ma, mb, p);
     }
     main_kernel_end(stream);
     count_launch();
@@ -899,9 +961,9 @@ static int max_active_pairs(int sm_count) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaFuncSetAttribute(gemm_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_topk_kernel<true, MODE_TOPK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<true>::SMEM_BYTES) == cudaSuccess &&
-            cudaOccupancyMaxActiveClusters(&n, gemm_topk_kernel<true>, &cfg) == cudaSuccess && n > 0) {
+            cudaOccupancyMaxActiveClusters(&n, gemm_topk_kernel<true, MODE_TOPK>, &cfg) == cudaSuccess && n > 0) {
             if (n < cached) cached = n;
         } else {
             (void)cudaGetLastError();
@@ -974,7 +1036,8 @@ int launch_gemm_topk(const GemmOperands& op, const GemmPlan& plan, int64_t col0,
 
 int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscale, const float* thr,
                        int thr_stride, int thr_pos, float* cand_key, int32_t* cand_idx,
-                       int32_t* cand_cnt, int cand_cap, int32_t* status, cudaStream_t stream) {
+                       int32_t* cand_cnt, int cand_cap, int few_hits, int32_t* status,
+                       cudaStream_t stream) {
     if (!thr || !cand_key || !cand_idx || !cand_cnt || cand_cap < 1) return B200F_ERR_BAD_ARG;
     B200F_CUDA_TRY(cudaMemsetAsync(cand_cnt, 0, (size_t)op.nq * sizeof(int32_t), stream));
     GemmParams p{};
@@ -988,6 +1051,7 @@ int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscal
     p.cand_idx = cand_idx;
     p.cand_cnt = cand_cnt;
     p.cand_cap = cand_cap;
+    p.wide = few_hits ? 1 : 0;
     p.status = status;
     return launch_common(op, plan, p, 0, op.nb, stream);
 }

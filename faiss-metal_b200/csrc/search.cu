@@ -483,8 +483,9 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
         if (rc != B200F_OK) return rc;
         rc = launch_merge_keys(pkey, pidx, 2 * pl.pilot.P, a->nq, pl.frank, thr, st);
         if (rc != B200F_OK) return rc;
+        // candidates per row ~ frank * fstride: a few hundred for k <= 128, thousands beyond
         rc = launch_gemm_filter(op, pl.gemm, kscale, thr, pl.frank, pl.frank - 1, ckey, cidx, ccnt,
-                                pl.fcap, a->status, st);
+                                pl.fcap, pl.fstride == 64 ? 1 : 0, a->status, st);
         if (rc != B200F_OK) return rc;
         rc = launch_select_candidates(ckey, cidx, ccnt, pl.fcap, a->nb, a->nq, a->k, a->metric, qnorm,
                                       a->label_base, a->out_dist, a->out_labels, dirty, st);
