@@ -406,6 +406,20 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
         const int t = lane & 3;
         int stage = 0;
         uint32_t phase = 0;
+        // Bounds of the two queries whose scores land in this lane (2t and 2t+1), so that ONE vote
+        // per tile tells whether any of its 16 x nq scores is a candidate; a query beyond nq
+        // gets -INF and never is.
+        float mta, mtb;
+        int mia, mib;
+        auto refresh_bounds = [&]() {
+            mta = t == 0 ? thr[0] : t == 1 ? thr[2] : t == 2 ? thr[4] : thr[6];
+            mtb = t == 0 ? thr[1] : t == 1 ? thr[3] : t == 2 ? thr[5] : thr[7];
+            mia = t == 0 ? thr_id[0] : t == 1 ? thr_id[2] : t == 2 ? thr_id[4] : thr_id[6];
+            mib = t == 0 ? thr_id[1] : t == 1 ? thr_id[3] : t == 2 ? thr_id[5] : thr_id[7];
+            if (2 * t >= p.nq) mta = -CUDART_INF_F;
+            if (2 * t + 1 >= p.nq) mtb = -CUDART_INF_F;
+        };
+        refresh_bounds();
         for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
             const bool w = mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status,
                                              kDevErrBarrierWait);
@@ -434,6 +448,13 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
                     mma16816<BF16>(acc, x0.z, x1.z, x0.w, x1.w, q.z, q.w);
                 }
                 // acc[0]: (row r0, query 2t)  acc[1]: (r0, 2t+1)  acc[2]: (r1, 2t)  acc[3]: (r1, 2t+1)
+                {
+                    const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
+                    const bool any_hit =
+                            (v0 && (before(kmul * acc[0], row_a, mta, mia) || before(kmul * acc[1], row_a, mtb, mib))) ||
+                            (v1 && (before(kmul * acc[2], row_b, mta, mia) || before(kmul * acc[3], row_b, mtb, mib)));
+                    if (!__any_sync(FULL, any_hit)) continue;  // the usual case: nothing for any query
+                }
 #pragma unroll
                 for (int qi = 0; qi < SM_NQ; qi++) {
                     if (qi >= p.nq) break;
@@ -457,6 +478,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
                         }
                     }
                 }
+                refresh_bounds();
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + stage * 8);
