@@ -218,7 +218,7 @@ def run_reference(args, w, rank, world):
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------
@@ -498,11 +498,30 @@ def run_b200(args, w, rank, world, local_rank):
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches.value),
         "latency": latency, "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     teardown()
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict):
+    """The one JSON line of the run, on the process's original stdout."""
+    text = json.dumps(line) + "\n"
+    if _RESULT_FD is not None:
+        os.write(_RESULT_FD, text.encode())
+    else:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+
+
 def main():
+    # Libraries may print to stdout on their own (NCCL writes its version line there when the
+    # first communicator is created): everything but the result line goes to stderr.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     args = parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.nb:

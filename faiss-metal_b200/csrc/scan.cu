@@ -208,7 +208,9 @@ scan_kernel(const ScanParams p) {
                 for (int qi = 0; qi < NQ; qi++)
                     acc[u][qi] += __shfl_xor_sync(FULL, acc[u][qi], o);
         }
-        // lane cl == 0 of each row group owns the row's candidates
+        // lane cl == 0 of each row group owns the row's candidates: turn the dot products into
+        // keys there, and let ONE vote decide whether any row of the block has a candidate
+        bool any_hit = false;
 #pragma unroll
         for (int u = 0; u < SCAN_U; u++) {
             const int64_t row = row_base + u * rps + sub;
@@ -217,7 +219,18 @@ scan_kernel(const ScanParams p) {
             if (owner && l2) nrm = __ldg(p.norms + row);
 #pragma unroll
             for (int qi = 0; qi < NQ; qi++) {
-                const float key = l2 ? fmaf(-2.f, acc[u][qi], nrm) : -acc[u][qi];
+                acc[u][qi] = l2 ? fmaf(-2.f, acc[u][qi], nrm) : -acc[u][qi];
+                if (!STORE) any_hit |= owner && before(acc[u][qi], (int)row, thr[qi], thr_id[qi]);
+            }
+        }
+        if (!STORE && !__any_sync(FULL, any_hit)) continue;
+#pragma unroll
+        for (int u = 0; u < SCAN_U; u++) {
+            const int64_t row = row_base + u * rps + sub;
+            const bool owner = (cl == 0) && row < p.col1;
+#pragma unroll
+            for (int qi = 0; qi < NQ; qi++) {
+                const float key = acc[u][qi];
                 if (STORE) {
                     if (owner && qi < p.nq) p.out[(int64_t)qi * p.ld + (row - p.col0)] = key;
                 } else {
@@ -543,8 +556,11 @@ void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch, int nor
     } else {
         p.nscale[0] = 1.f; p.nscale[1] = 1.f; p.nscale[2] = 1.f; p.nscale[3] = 0.f;
     }
+    // lanes per row: at most 8, so that a warp step covers at least 4 rows and the shuffle
+    // reduction has 3 levels (with 32 lanes on one row the reduction and the candidate votes
+    // cost more instructions than the dot product itself)
     int lpr = 1;
-    while (lpr < p.C && lpr < 32) lpr <<= 1;
+    while (lpr < p.C && lpr < 8) lpr <<= 1;
     p.lpr = lpr;
     p.iters = (p.C + lpr - 1) / lpr;
     p.qstride = p.C * E;
