@@ -64,6 +64,7 @@ int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint1
 struct ScanPlan {
     int grid;        // CTAs == number of partial lists per query
     int threads;
+    int lpr_cap;     // plain kernel: upper limit of the lanes that share one row
 };
 ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count);
 // *out_P receives the number of partial lists per query actually written (<= plan.grid).

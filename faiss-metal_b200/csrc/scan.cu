@@ -545,7 +545,7 @@ size_t scan_smem_bytes(int nq_t, int qstride) {
     return a > b ? a : b;
 }
 
-void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch, int norm_cols) {
+void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch, int norm_cols, int lpr_cap) {
     const int E = storage == B200F_STORAGE_F32 ? 4 : 8;
     const int es = storage == B200F_STORAGE_F32 ? 4 : 2;
     p.pitch_bytes = row_pitch * es;
@@ -556,11 +556,12 @@ void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch, int nor
     } else {
         p.nscale[0] = 1.f; p.nscale[1] = 1.f; p.nscale[2] = 1.f; p.nscale[3] = 0.f;
     }
-    // lanes per row: at most 8, so that a warp step covers at least 4 rows and the shuffle
-    // reduction has 3 levels (with 32 lanes on one row the reduction and the candidate votes
-    // cost more instructions than the dot product itself)
+    // lanes per row: at most lpr_cap.  With several queries 8 is best (a warp step covers at
+    // least 4 rows and the shuffle reduction has 3 levels: with 32 lanes on one row the reduction
+    // and the candidate votes cost more instructions than the dot products); a single query
+    // is limited by loads in flight, not instructions, and runs faster with whole rows per step.
     int lpr = 1;
-    while (lpr < p.C && lpr < 8) lpr <<= 1;
+    while (lpr < p.C && lpr < lpr_cap) lpr <<= 1;
     p.lpr = lpr;
     p.iters = (p.C + lpr - 1) / lpr;
     p.qstride = p.C * E;
@@ -622,9 +623,11 @@ bool plan_stream(ScanParams& p, int storage, int d, int norm_cols) {
     return ns >= 3;
 }
 
-int scan_grid(int64_t nrows, int d, int storage, int sm_count) {
+int lanes_per_row_cap(int64_t nq) { return nq == 1 ? 32 : 8; }
+
+int scan_grid(int64_t nrows, int d, int storage, int sm_count, int lpr_cap) {
     ScanParams t{};
-    fill_geometry(t, storage, d, d, 0);
+    fill_geometry(t, storage, d, d, 0, lpr_cap);
     const int rows_per_block = (32 / t.lpr) * SCAN_U;
     const int64_t nblocks = ceil_div64(nrows, rows_per_block);
     int64_t g = ceil_div64(nblocks, SCAN_WARPS);
@@ -637,9 +640,9 @@ int scan_grid(int64_t nrows, int d, int storage, int sm_count) {
 }  // namespace
 
 ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count) {
-    (void)nq;
     ScanPlan s;
-    s.grid = scan_grid(nb, d, storage, sm_count);
+    s.lpr_cap = lanes_per_row_cap(nq);  // of the whole search: every query group uses the same geometry
+    s.grid = scan_grid(nb, d, storage, sm_count, s.lpr_cap);
     s.threads = SCAN_THREADS;
     return s;
 }
@@ -648,7 +651,8 @@ int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part
                      int32_t* part_idx, int* out_P, cudaStream_t stream) {
     if (a.nq < 1 || a.nq > 8 || a.k < 1 || a.k > 32) return B200F_ERR_UNSUPPORTED;
     ScanParams p{};
-    fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0);
+    fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0,
+                  plan.lpr_cap);
     p.queries = a.queries;
     p.rows = a.rows;
     p.norms = a.norms;
@@ -701,7 +705,8 @@ int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, flo
     if (a.nq < 1 || a.nq > 4) return B200F_ERR_UNSUPPORTED;
     if (ncols <= 0) return B200F_OK;
     ScanParams p{};
-    fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0);
+    fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0,
+                  lanes_per_row_cap(a.nq));
     p.queries = a.queries;
     p.rows = a.rows;
     p.norms = a.norms;
@@ -714,7 +719,8 @@ int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, flo
     p.metric = a.metric;
     p.out = out;
     p.ld = ld;
-    return launch_storage<true>(p, a.storage, scan_grid(ncols, a.d, a.storage, sm_count), stream);
+    return launch_storage<true>(p, a.storage, scan_grid(ncols, a.d, a.storage, sm_count, lanes_per_row_cap(a.nq)),
+                                stream);
 }
 
 }  // namespace b200f
