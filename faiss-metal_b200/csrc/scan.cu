@@ -208,29 +208,36 @@ scan_kernel(const ScanParams p) {
                 for (int qi = 0; qi < NQ; qi++)
                     acc[u][qi] += __shfl_xor_sync(FULL, acc[u][qi], o);
         }
-        // lane cl == 0 of each row group owns the row's candidates: turn the dot products into
-        // keys there, and let ONE vote decide whether any row of the block has a candidate
-        bool any_hit = false;
+        // lane cl == 0 of each row group owns the row's candidates.  With several queries the
+        // dot products are first turned into keys and ONE vote decides whether any row of the block
+        // has a candidate for any query (a single query is bound by loads in flight, and measured
+        // slower with the extra pass).
+        constexpr bool PREVOTE = (NQ > 1) && !STORE;
+        if (PREVOTE) {
+            bool any_hit = false;
+#pragma unroll
+            for (int u = 0; u < SCAN_U; u++) {
+                const int64_t row = row_base + u * rps + sub;
+                const bool owner = (cl == 0) && row < p.col1;
+                float nrm = 0.f;
+                if (owner && l2) nrm = __ldg(p.norms + row);
+#pragma unroll
+                for (int qi = 0; qi < NQ; qi++) {
+                    acc[u][qi] = l2 ? fmaf(-2.f, acc[u][qi], nrm) : -acc[u][qi];
+                    any_hit |= owner && before(acc[u][qi], (int)row, thr[qi], thr_id[qi]);
+                }
+            }
+            if (!__any_sync(FULL, any_hit)) continue;
+        }
 #pragma unroll
         for (int u = 0; u < SCAN_U; u++) {
             const int64_t row = row_base + u * rps + sub;
             const bool owner = (cl == 0) && row < p.col1;
             float nrm = 0.f;
-            if (owner && l2) nrm = __ldg(p.norms + row);
+            if (!PREVOTE && owner && l2) nrm = __ldg(p.norms + row);
 #pragma unroll
             for (int qi = 0; qi < NQ; qi++) {
-                acc[u][qi] = l2 ? fmaf(-2.f, acc[u][qi], nrm) : -acc[u][qi];
-                if (!STORE) any_hit |= owner && before(acc[u][qi], (int)row, thr[qi], thr_id[qi]);
-            }
-        }
-        if (!STORE && !__any_sync(FULL, any_hit)) continue;
-#pragma unroll
-        for (int u = 0; u < SCAN_U; u++) {
-            const int64_t row = row_base + u * rps + sub;
-            const bool owner = (cl == 0) && row < p.col1;
-#pragma unroll
-            for (int qi = 0; qi < NQ; qi++) {
-                const float key = acc[u][qi];
+                const float key = PREVOTE ? acc[u][qi] : (l2 ? fmaf(-2.f, acc[u][qi], nrm) : -acc[u][qi]);
                 if (STORE) {
                     if (owner && qi < p.nq) p.out[(int64_t)qi * p.ld + (row - p.col0)] = key;
                 } else {
