@@ -112,9 +112,10 @@ __device__ __forceinline__ void warp_insert(float& lk, int& li, float s, int id,
 }
 
 template <int STORAGE, int NQ, bool STORE>
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(SCAN_THREADS, NQ == 4 ? 2 : 3)  // three CTAs per SM; four queries would spill at 80 registers
 scan_kernel(const ScanParams p) {
     constexpr int E = Piece<STORAGE>::E;
+    constexpr int U = SCAN_U;  // rows per lane and block
     extern __shared__ __align__(16) float sq[];  // [NQ][qstride] queries, then merge area
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -137,7 +138,7 @@ scan_kernel(const ScanParams p) {
     const int rps = 32 / lpr;            // rows per warp step
     const int cl = lane & (lpr - 1);     // piece lane inside the row
     const int sub = lane / lpr;          // which of the rps rows
-    const int rows_per_block = rps * SCAN_U;
+    const int rows_per_block = rps * U;
     const int64_t nrows = p.col1 - p.col0;
     const int64_t nblocks = ceil_div64(nrows, rows_per_block);
     const int64_t gw = (int64_t)blockIdx.x * SCAN_WARPS + warp;
@@ -159,18 +160,18 @@ scan_kernel(const ScanParams p) {
 
     for (int64_t blk = gw; blk < nblocks; blk += total_warps) {
         const int64_t row_base = p.col0 + blk * rows_per_block;
-        float acc[SCAN_U][NQ];
+        float acc[U][NQ];
 #pragma unroll
-        for (int u = 0; u < SCAN_U; u++)
+        for (int u = 0; u < U; u++)
 #pragma unroll
             for (int qi = 0; qi < NQ; qi++) acc[u][qi] = 0.f;
 
         for (int it = 0; it < p.iters; it++) {
             const int piece = it * lpr + cl;
             const bool pv = piece < p.C;
-            uint4 v[SCAN_U];
+            uint4 v[U];
 #pragma unroll
-            for (int u = 0; u < SCAN_U; u++) {
+            for (int u = 0; u < U; u++) {
                 const int64_t row = row_base + u * rps + sub;
                 if (pv && row < p.col1)
                     v[u] = ldg_stream(base + row * p.pitch_bytes + (int64_t)piece * 16);
@@ -191,7 +192,7 @@ scan_kernel(const ScanParams p) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < SCAN_U; u++) {
+            for (int u = 0; u < U; u++) {
                 float x[E];
                 unpack<STORAGE>(v[u], x);
 #pragma unroll
@@ -203,20 +204,19 @@ scan_kernel(const ScanParams p) {
         // reduce the partial dot products over the lpr lanes of each row
         for (int o = lpr >> 1; o > 0; o >>= 1) {
 #pragma unroll
-            for (int u = 0; u < SCAN_U; u++)
+            for (int u = 0; u < U; u++)
 #pragma unroll
                 for (int qi = 0; qi < NQ; qi++)
                     acc[u][qi] += __shfl_xor_sync(FULL, acc[u][qi], o);
         }
         // lane cl == 0 of each row group owns the row's candidates.  With several queries the
         // dot products are first turned into keys and ONE vote decides whether any row of the block
-        // has a candidate for any query (a single query is bound by loads in flight, and measured
-        // slower with the extra pass).
+        // has a candidate for any query (a single query measured slower with the extra pass).
         constexpr bool PREVOTE = (NQ > 1) && !STORE;
         if (PREVOTE) {
             bool any_hit = false;
 #pragma unroll
-            for (int u = 0; u < SCAN_U; u++) {
+            for (int u = 0; u < U; u++) {
                 const int64_t row = row_base + u * rps + sub;
                 const bool owner = (cl == 0) && row < p.col1;
                 float nrm = 0.f;
@@ -230,7 +230,7 @@ scan_kernel(const ScanParams p) {
             if (!__any_sync(FULL, any_hit)) continue;
         }
 #pragma unroll
-        for (int u = 0; u < SCAN_U; u++) {
+        for (int u = 0; u < U; u++) {
             const int64_t row = row_base + u * rps + sub;
             const bool owner = (cl == 0) && row < p.col1;
             float nrm = 0.f;
@@ -563,10 +563,9 @@ void fill_geometry(ScanParams& p, int storage, int d, int64_t row_pitch, int nor
     } else {
         p.nscale[0] = 1.f; p.nscale[1] = 1.f; p.nscale[2] = 1.f; p.nscale[3] = 0.f;
     }
-    // lanes per row: at most lpr_cap.  With several queries 8 is best (a warp step covers at
-    // least 4 rows and the shuffle reduction has 3 levels: with 32 lanes on one row the reduction
-    // and the candidate votes cost more instructions than the dot products); a single query
-    // is limited by loads in flight, not instructions, and runs faster with whole rows per step.
+    // lanes per row: at most lpr_cap (8: a warp step covers at least 4 rows and the shuffle
+    // reduction has 3 levels; with 32 lanes on one row the reduction and the candidate votes
+    // cost more instructions than the dot products).
     int lpr = 1;
     while (lpr < p.C && lpr < lpr_cap) lpr <<= 1;
     p.lpr = lpr;
@@ -630,7 +629,7 @@ bool plan_stream(ScanParams& p, int storage, int d, int norm_cols) {
     return ns >= 3;
 }
 
-int lanes_per_row_cap(int64_t nq) { return nq == 1 ? 32 : 8; }
+int lanes_per_row_cap(int64_t nq) { (void)nq; return 8; }
 
 int scan_grid(int64_t nrows, int d, int storage, int sm_count, int lpr_cap) {
     ScanParams t{};
