@@ -3,8 +3,8 @@
 // Replaces the encode sequence of MetalIndexFlat::search (src/MetalIndexFlat.mm:358-378)
 // and the path selection of MetalDistance / MetalSelect (src/MetalDistance.mm:107-128,
 // 327-363; src/MetalSelect.mm:34-89).  Paths here depend on (nq, k) only:
-//   nq <= 4            streaming scan (scan.cu)
-//   nq  > 4            tensor-core GEMM (gemm_topk.cu)
+//   nq <= 4 (8 on 16-bit rows)   streaming scan (scan.cu)
+//   more queries                 tensor-core GEMM (gemm_topk.cu)
 //   k  <= 32           top-k fused into the distance kernel, partial lists merged after
 //   k  <= 1024         (tensor path, shard of >= 64k / 128k rows) threshold filter: a pilot pass
 //                      over every 64th / 128th column tile gives each query a key threshold
@@ -98,7 +98,11 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     const int sm = cached_sm_count();
     pl = SearchPlan{};
     pl.path = path;
-    if (path == B200F_PATH_AUTO) pl.path = (nq <= SCAN_GROUP) ? B200F_PATH_SCAN : B200F_PATH_TENSOR;
+    // 16-bit rows: the streaming scan takes up to 8 queries per pass at HBM speed, which beats a
+    // 128-row tensor tile that is mostly padding; fp32 rows: 4 per pass (the reference's limit,
+    // src/MetalDistance.mm:346-354)
+    const int64_t scan_limit = (storage == B200F_STORAGE_F32) ? SCAN_GROUP : 2 * SCAN_GROUP;
+    if (path == B200F_PATH_AUTO) pl.path = (nq <= scan_limit) ? B200F_PATH_SCAN : B200F_PATH_TENSOR;
     pl.fused = (k <= B200F_FUSED_MAX_K) && !pairwise;
     pl.npl = (storage == B200F_STORAGE_F32) ? 3 : 1;
     pl.a_pitch = round_up64(d, 8) + 8;
@@ -504,18 +508,25 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
                                   a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
-            // every group of <= 4 queries writes the same number of lists (same shard, same
-            // geometry); the first launch reports it
+            // every group of queries writes the same number of lists (same shard, same
+            // geometry); the first launch reports it.  Groups of 8 where the streaming kernel
+            // applies (16-bit rows, shard large enough), else of 4.
             P = pl.scan.grid;
-            for (int64_t g = 0; g < pl.ngroups; g++) {
+            int64_t group = (a->storage != B200F_STORAGE_F32 && a->nq > SCAN_GROUP) ? 2 * SCAN_GROUP : SCAN_GROUP;
+            for (int64_t q0 = 0; q0 < a->nq;) {
                 B200FSearchArgs sub = *a;
-                sub.queries = a->queries + g * SCAN_GROUP * (int64_t)a->d;
-                sub.nq = (a->nq - g * SCAN_GROUP) < SCAN_GROUP ? (a->nq - g * SCAN_GROUP) : SCAN_GROUP;
+                sub.queries = a->queries + q0 * (int64_t)a->d;
+                sub.nq = (a->nq - q0) < group ? (a->nq - q0) : group;
                 int Pg = P;
-                rc = launch_scan_topk(sub, pl.scan, part_key + g * SCAN_GROUP * (int64_t)P * a->k,
-                                      part_idx + g * SCAN_GROUP * (int64_t)P * a->k, &Pg, st);
+                rc = launch_scan_topk(sub, pl.scan, part_key + q0 * (int64_t)P * a->k,
+                                      part_idx + q0 * (int64_t)P * a->k, &Pg, st);
+                if (rc == B200F_ERR_UNSUPPORTED && q0 == 0 && group > SCAN_GROUP) {
+                    group = SCAN_GROUP;  // no streaming kernel for this shape: nothing was launched
+                    continue;
+                }
                 if (rc != B200F_OK) return rc;
-                if (g == 0) P = Pg;
+                if (q0 == 0) P = Pg;
+                q0 += sub.nq;
             }
         }
         return launch_merge_partials(part_key, part_idx, P, a->nq, a->k, a->metric, qnorm,

@@ -53,8 +53,25 @@ def test_flat_more_shapes(fm, res, path, nv, nq, d, k, storage, metric):
     xq = H.uniform_pm1(nq, d, 8)
     idx = make_index(fm, res, xb, metric, storage, path)
     D, I = idx.search(xq, k)
-    tensor = (path == PATH_TENSOR) or (path == 0 and nq > 4)
+    # automatic choice: scan up to 4 queries on fp32 rows and up to 8 on 16-bit rows (these shards
+    # are too small for the streaming kernel, so the scan multiplies unrounded fp32 queries)
+    tensor = (path == PATH_TENSOR) or (path == 0 and nq > (4 if storage == 0 else 8))
     H.check_against_oracle(metric, storage, tensor, xb, xq, k, D, I)
+    idx.close()
+
+
+@pytest.mark.parametrize("storage", [1, 2])
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+@pytest.mark.parametrize("nv,nq,d,k", [(60_000, 5, 64, 10), (60_000, 8, 128, 32), (60_000, 7, 200, 3), (2_000, 8, 64, 10)])
+def test_automatic_path_five_to_eight_queries(fm, res, storage, metric, nv, nq, d, k):
+    # 16-bit rows, 5 - 8 queries: one pass of the streaming scan on large shards (queries rounded
+    # to the storage format, like the tensor path), two passes of the plain scan on small ones
+    xb = H.uniform_pm1(nv, d, 71)
+    xq = H.uniform_pm1(nq, d, 72)
+    idx = make_index(fm, res, xb, metric, storage)
+    D, I = idx.search(xq, k)
+    H.check_against_oracle(metric, storage, nv >= 20_000, xb, xq, k, D, I)
+    # same labels as the tensor path up to ties inside the tolerance: compare with the oracle only
     idx.close()
 
 
