@@ -1,4 +1,8 @@
-// Streaming search for small query batches (nq <= 4): HBM-bound, CUDA cores only.
+// Streaming search for small query batches: HBM-bound.  Two kernels:
+//   scan_mma_kernel  16-bit rows, up to 8 queries per pass: rows staged through a
+//                    cp.async.bulk ring, scores by mma.sync (described further down)
+//   scan_kernel      the plain version (fp32 rows, shards too small for the ring, and the
+//                    store mode that writes keys for k > 32): up to 4 queries per pass
 //
 // Replaces fused_l2_topk_min / fused_ip_topk_max and their f16storage variants
 // (shaders/fused_l2_topk.metal:19-444, gate in src/MetalDistance.mm:341-354) and the
@@ -9,8 +13,8 @@
 // a sorted warp list (one slot per lane) updated by ballot + shuffle insertion so no
 // candidate is dropped.
 //
-// Work layout: a row of C 16-byte pieces is covered by LPR = min(32, pow2(C)) lanes
-// (ITERS = ceil(C / LPR) pieces per lane); a warp therefore covers 32 / LPR rows per
+// Work layout of scan_kernel: a row of C 16-byte pieces is covered by LPR = min(8, pow2(C))
+// lanes (ITERS = ceil(C / LPR) pieces per lane); a warp therefore covers 32 / LPR rows per
 // step and U steps per block, keeping U independent 16-byte loads in flight per lane.
 #include "common.cuh"
 #include "ptx.cuh"

@@ -4,7 +4,7 @@
 // (shaders/block_select.metal:111-274), their dispatch (src/MetalSelect.mm:34-108) and the
 // final list merge inside the fused kernels (shaders/fused_l2_topk.metal:88-131).
 //
-// Two building blocks:
+// Building blocks:
 //  * merge_small: k <= 32.  One CTA per query; each warp folds a subset of sorted input
 //    lists into a sorted warp list (lane j = rank j) by ballot + shuffle insertion with
 //    early exit, then warp 0 folds the warp lists.
@@ -12,6 +12,11 @@
 //    the current k-th best in a shared-memory buffer of 8192 packed (key, payload) words
 //    and compacts with a bitonic sort whenever the buffer could overflow.  Results are
 //    exact for every k (the reference's block_select keeps only 8 real results per row).
+//    Sources: a key matrix chunk, sorted lists of other ranks, the fused kernel's 32-entry
+//    lists, or a threshold-filtered candidate buffer; the last two also report rows whose
+//    result is not proven exact.
+//  * select_small: k <= 32 from a candidate buffer, one warp per query.
+//  * compact_rows / gather_rows: the rows to redo, counted and gathered on the device.
 //
 // Keys are "smaller is better" everywhere: L2 key = distance, inner product key = -dot.
 // Ties go to the lower id.
