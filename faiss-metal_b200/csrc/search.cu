@@ -81,8 +81,10 @@ bool filter_forced() {
     return e && e[0] == '1';
 }
 // The pilot pass costs 0.1 - 0.2 ms whatever the size (a handful of work items, each warming up
-// its lists on a single tile): below this many (query, row) pairs the fused lists are faster.
-constexpr int64_t FILTER_MIN_PAIRS = 1ll << 30;
+// its lists on a single tile).  Measured: at 2.6e8 (query, row) pairs the filter path is 19 - 47 %
+// faster than the lists (d = 768 / 1536, 16-bit rows), at 1e8 - 4e8 pairs of fp32 rows with
+// d = 128 the two are level; below this many pairs the lists are used.
+constexpr int64_t FILTER_MIN_PAIRS = 1ll << 27;
 
 // B200F_NO_LISTS=1 in the environment sends every k > 32 search through the key matrix.  Read at
 // every call, so that a test can switch between the paths inside one process.
