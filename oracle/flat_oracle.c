@@ -19,12 +19,18 @@
  * Accumulation is in double so that the order of summation does not matter
  * at the tolerances the tests use.  Ties are broken towards the lower label.
  *
- * PARITY PINNING: the reference holds no golden vectors for this path (its
- * tests compare against an external CPU FAISS build that is not available
- * here).  The oracle is pinned on the reference's known-answer cases only
- * (empty index, k > ntotal padding, fp32 reconstruct bit-exactness, fp16
- * reconstruct tolerance, norm / distance loops); distances and ranks >= 2 are
- * "parity unpinned" beyond those.
+ * PARITY PINNING: pinned to the reference's own CPU code.  The reference's unit tests hold
+ * plain C++ loops for squared norms, squared L2, inner product and the inner-product top-1
+ * with seeded std::mt19937 inputs; oracle/Makefile (`make ref`) compiles those lines out of
+ * the reference tree inside ref_loops.cpp, tests/golden/make_ref_golden.py stores what they
+ * compute in tests/golden/ref_loops.npz, and tests/test_ref_pin.py holds this file to those
+ * values (1e-5 relative: fp32 accumulation there, double here) and to the rank-1 labels they
+ * imply, on the shapes of tests/test_metal_flat.mm:477-490.  Also pinned: the reference's
+ * known-answer cases (empty index, k > ntotal padding, fp32 reconstruct bit-exactness, fp16
+ * reconstruct tolerance).  Not pinned by anything the reference holds: ranks >= 2 (its tests
+ * never compare them; they are held to the order its distance values imply), k > 10, BF16
+ * storage -- the contract there is the stated tolerance against this file.  The reference's
+ * external comparison, CPU FAISS, is not installed here.
  */
 #include <math.h>
 #include <stdint.h>

@@ -13,10 +13,13 @@ with (faiss::IndexFlatL2 / IndexFlatIP, tests/test_metal_flat.mm:73-78,108-113):
   C file on small cases, and ``blas_search`` (sgemm + partial select, the way
   CPU FAISS evaluates large batches) used as the timed CPU baseline.
 
-PARITY PINNING: the reference has no golden vectors for this path; the oracle
-is pinned on the reference's known-answer cases only (empty index,
-k > ntotal padding, reconstruct round trips, norm / distance loops).  Ranks
->= 2 and distances are "parity unpinned" by the reference itself.
+PARITY PINNING: pinned to the reference's own CPU code -- the inline loops and seeded
+generators of its unit tests, compiled out of the reference tree by ``make -C oracle ref``
+(ref_loops.cpp) into tests/golden/ref_loops.npz and checked by tests/test_ref_pin.py: norms,
+squared-L2 and inner-product values to 1e-5 relative, rank-1 labels exactly, on the shapes of
+tests/test_metal_flat.mm:477-490; plus the reference's known-answer cases (empty index,
+k > ntotal padding, reconstruct round trips).  Ranks >= 2, k > 10 and BF16 storage are not
+pinned by anything the reference holds; CPU FAISS, its external comparison, is not installed.
 """
 from __future__ import annotations
 
@@ -44,6 +47,19 @@ def build(force: bool = False) -> str:
         env.pop("CC", None)
         subprocess.check_call(["make", "-C", _HERE, "-s"], env=env)
     return _LIB_PATH
+
+
+def build_ref(ref_root: str | None = None) -> str | None:
+    """Compile the reference's own CPU loops (``make ref``: ref_loops.cpp around lines cut out of
+    the reference's test files) into _ref/ref_loops.  Returns None when the reference checkout
+    is not present, which is the normal case away from the machine the fixtures are made on."""
+    root = ref_root or os.environ.get("B200F_REFERENCE_ROOT", "/root/reference")
+    if not os.path.isfile(os.path.join(root, "tests", "test_metal_distance.mm")):
+        return None
+    env = dict(os.environ)
+    env.pop("CXX", None)
+    subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "REF=" + root], env=env)
+    return os.path.join(_HERE, "_ref", "ref_loops")
 
 
 def lib() -> ctypes.CDLL:

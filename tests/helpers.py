@@ -15,6 +15,30 @@ def uniform_pm1(n, d, seed):
     return rng.uniform(-1.0, 1.0, size=(n, d)).astype(np.float32)
 
 
+def mt19937_uniform_pm1(seed, count):
+    """`count` draws of std::uniform_real_distribution<float>(-1, 1) from std::mt19937(seed), in
+    order: the reference's test-data generator (tests/test_metal_distance.mm:26-31,
+    tests/test_metal_flat.mm:64-70) restated for numpy.  std::mt19937(seed) is the standard
+    init_genrand seeding, which numpy's legacy RandomState(seed) uses too; the distribution
+    takes one 32-bit output per value: float(raw) / 2^32 (a value that rounds up to 1 becomes
+    the float below 1), then 2 * u - 1, all in fp32.  Bit-exact against the fixture made from
+    the reference's code (tests/golden/ref_loops.npz)."""
+    raw = np.random.RandomState(seed)._bit_generator.random_raw(count).astype(np.uint32)
+    u = raw.astype(np.float32) / np.float32(4294967296.0)
+    u = np.where(u >= np.float32(1.0), np.nextafter(np.float32(1.0), np.float32(0.0)), u).astype(np.float32)
+    return (np.float32(2.0) * u + np.float32(-1.0)).astype(np.float32)
+
+
+def fnv1a64_half(*arrays):
+    """Checksum the fixture keeps of inputs too large to commit (FNV-1a 64 over the bytes of the
+    arrays in order, shifted right once to fit int64): oracle/ref_loops.cpp, flat_case."""
+    h = 1469598103934665603
+    for a in arrays:
+        for b in np.ascontiguousarray(a).view(np.uint8).ravel().tolist():
+            h = ((h ^ b) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h >> 1
+
+
 def uniform01(n, d, seed):
     rng = np.random.default_rng(seed)
     return rng.random(size=(n, d), dtype=np.float32)
