@@ -9,6 +9,10 @@ STORAGE_F32, STORAGE_F16, STORAGE_BF16 = 0, 1, 2
 PATH_AUTO, PATH_SCAN, PATH_TENSOR = 0, 1, 2
 MAX_K = 4096
 FUSED_MAX_K = 32
+SELECT_AUTO, SELECT_FILTER, SELECT_NO_FILTER, SELECT_MATRIX = 0, 1, 2, 3
+GEMM_SHAPE_AUTO, GEMM_SHAPE_SINGLE, GEMM_SHAPE_PAIR = -1, 0, 1
+ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_SCRATCH, ERR_CUDA, ERR_DEVICE_WAIT = 1, 2, 3, 4, 5
+ERR_NO_DEVICE, ERR_OOM, ERR_RANGE, ERR_STATE, ERR_DEVICE_CHECK = 6, 7, 8, 9, 10
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
@@ -52,6 +56,12 @@ class SearchArgs(ctypes.Structure):
 # name -> (restype, argtypes); the symbol test checks this table against the header
 SIGNATURES = {
     "b200f_status_string": (ctypes.c_char_p, [c_int]),
+    "b200f_set_selection_mode": (c_int, [c_int]),
+    "b200f_get_selection_mode": (c_int, []),
+    "b200f_set_gemm_shape": (c_int, [c_int]),
+    "b200f_set_debug_canaries": (c_int, [c_int]),
+    "b200f_debug_wait_expiry": (c_int, [c_vp, c_i64, c_vp]),
+    "b200f_debug_canary_selftest": (c_int, [c_vp, c_sz, c_int, c_vp, c_vp]),
     "b200f_device_count": (c_int, [ctypes.POINTER(c_int)]),
     "b200f_device_caps": (c_int, [c_int, ctypes.POINTER(Caps)]),
     "b200f_row_norms": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_vp]),
@@ -70,10 +80,12 @@ SIGNATURES = {
     "b200f_profile_enable": (c_int, [c_int]),
     "b200f_profile_read": (c_int, [ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(ctypes.c_double), c_int]),
     "b200f_last_error": (ctypes.c_char_p, []),
+    "b200f_debug_raise": (c_int, [c_int]),
     "b200f_resources_create": (c_int, [c_int, ctypes.POINTER(c_vp)]),
     "b200f_resources_destroy": (None, [c_vp]),
     "b200f_resources_device": (c_int, [c_vp]),
     "b200f_resources_stream": (c_vp, [c_vp]),
+    "b200f_resources_wait_stream": (c_int, [c_vp, c_vp]),
     "b200f_resources_scratch_bytes": (c_sz, [c_vp]),
     "b200f_index_create": (c_int, [c_vp, c_int, c_int, c_int, ctypes.POINTER(c_vp)]),
     "b200f_index_destroy": (None, [c_vp]),
@@ -95,8 +107,11 @@ SIGNATURES = {
     "b200f_index_set_path": (c_int, [c_vp, c_int]),
     "b200f_index_reserve": (c_int, [c_vp, c_i64]),
     "b200f_index_set_label_base": (c_int, [c_vp, c_i64]),
+    "b200f_index_set_growth_mode": (c_int, [c_vp, c_int]),
+    "b200f_index_set_use_graphs": (c_int, [c_vp, c_int]),
     "b200f_index_device_rows": (c_vp, [c_vp]),
     "b200f_index_last_device_status": (c_int, [c_vp]),
+    "b200f_index_debug_wait_expiry": (c_int, [c_vp, c_i64]),
 }
 
 

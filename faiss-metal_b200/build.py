@@ -25,18 +25,15 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CU_SOURCES = ["csrc/rows.cu", "csrc/scan.cu", "csrc/select.cu", "csrc/gemm_topk.cu", "csrc/search.cu"]
 CPP_SOURCES = ["host/Resources.cpp", "host/GrowableArray.cpp", "host/IndexFlat.cpp", "host/capi.cpp",
                "faiss_compat/compat_impl.cpp"]
-HEADERS = [
-    "csrc/common.cuh",
-    "../include/b200_flat.h",
-    "include/faiss-b200/B200IndexFlat.h",
-    "include/faiss-b200/B200Resources.h",
-    "host/GrowableArray.h",
-    "include/faiss-b200/StandardB200Resources.h",
-    "include/faiss-b200/B200DeviceCapabilities.h",
-    "faiss_compat/faiss/Index.h",
-    "faiss_compat/faiss/IndexFlat.h",
-    "faiss_compat/faiss/impl/FaissAssert.h",
-]
+def _headers():
+    """Every header an object may depend on (globbed, so that a new one cannot be forgotten)."""
+    import glob
+    pats = ["csrc/*.cuh", "csrc/*.h", "host/*.h", "include/faiss-b200/*.h", "faiss_compat/faiss/*.h",
+            "faiss_compat/faiss/impl/*.h", "../include/*.h"]
+    out = []
+    for pat in pats:
+        out += sorted(glob.glob(os.path.join(HERE, pat)))
+    return out
 
 
 def _newer(target: str, deps) -> bool:
@@ -64,7 +61,7 @@ def include_dirs():
 def build_library(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(BUILD_DIR, exist_ok=True)
     os.makedirs(LIB_DIR, exist_ok=True)
-    hdrs = [os.path.join(HERE, h) for h in HEADERS] + [os.path.abspath(__file__)]
+    hdrs = _headers() + [os.path.abspath(__file__)]
     incs = []
     for d in include_dirs():
         incs += ["-I", d]

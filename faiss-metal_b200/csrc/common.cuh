@@ -18,6 +18,7 @@ constexpr float kHostInf = __builtin_huge_valf();
 constexpr int kDevErrBarrierWait = 1;   // a bounded mbarrier wait ran out
 constexpr int kDevErrSmemAlign = 2;     // dynamic shared memory base not 1024-byte aligned
 constexpr int kDevErrOverflow = 4;      // a candidate buffer overflowed (never expected)
+constexpr int kDevErrCanary = 8;        // debug canaries: a kernel wrote past its scratch slice
 
 #define B200F_CUDA_TRY(expr)                         \
     do {                                             \
@@ -161,6 +162,11 @@ int launch_gather_rows(const uint16_t* a, int npl, int64_t plane_stride, int64_t
                        const int32_t* rows, const int32_t* count, int64_t nq_max, uint16_t* out,
                        cudaStream_t stream);
 
+// Per-device state: function attributes (the opt-in to more than 48 KiB of dynamic shared
+// memory), SM counts and occupancy figures belong to a device, and one process may hold
+// resources on several.  device_slot() is the current device's index into such tables.
+constexpr int kMaxDevices = 64;
+int device_slot();
 int cached_sm_count();
 
 // Profiling (off by default): counts kernel launches of this library and, when enabled,

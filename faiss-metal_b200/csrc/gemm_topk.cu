@@ -44,6 +44,7 @@
 // all roles drain out, TMEM is released and the kernel returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <type_traits>
 
@@ -892,14 +893,15 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
              gemm_topk_kernel<false, MODE_FILTER>},
             {gemm_topk_kernel<true, MODE_TOPK>, gemm_topk_kernel<true, MODE_STORE>,
              gemm_topk_kernel<true, MODE_FILTER>}};
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[kMaxDevices] = {false};   // the shared-memory opt-in is per device
+    const int slot = device_slot();
+    if (!attr_set[slot]) {
         for (int pr = 0; pr < 2; pr++)
             for (int m = 0; m < 3; m++)
                 B200F_CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void*>(kernels[pr][m]),
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                     pr ? Cfg<true>::SMEM_BYTES : Cfg<false>::SMEM_BYTES));
-        attr_set = true;
+        attr_set[slot] = true;
     }
     if (p.mode < 0 || p.mode > 2) return B200F_ERR_BAD_ARG;
     const KernelFn kernel = kernels[plan.pair ? 1 : 0][p.mode];
@@ -934,20 +936,26 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
 
 }  // namespace
 
-// B200F_GEMM_PAIR=0 / 1 in the environment forces the single-CTA / CTA-pair shape (testing).
+// Shape override (testing): b200f_set_gemm_shape, default from the environment variable
+// B200F_GEMM_PAIR=0 / 1 read ONCE at the first plan.  -1 = choose by the number of queries.
+static std::atomic<int> g_pair_override{-2};
+
 static int pair_override() {
-    static int v = -2;
+    int v = g_pair_override.load(std::memory_order_relaxed);
     if (v == -2) {
         const char* e = getenv("B200F_GEMM_PAIR");
         v = (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+        int expected = -2;
+        if (!g_pair_override.compare_exchange_strong(expected, v)) v = expected;
     }
     return v;
 }
 
 // CTA pairs that can be resident at once (GPC boundaries may leave a few SMs unpaired).
 static int max_active_pairs(int sm_count) {
-    static int cached = -1;
-    if (cached < 0) {
+    static int per_device[kMaxDevices] = {0};   // 0 = not asked yet on that device
+    int& cached = per_device[device_slot()];
+    if (cached <= 0) {
         cached = sm_count / 2;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2), 1, 1);
@@ -1074,3 +1082,9 @@ int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0
 }
 
 }  // namespace b200f
+
+extern "C" int b200f_set_gemm_shape(int shape) {
+    if (shape < B200F_GEMM_SHAPE_AUTO || shape > B200F_GEMM_SHAPE_PAIR) return B200F_ERR_BAD_ARG;
+    b200f::g_pair_override.store(shape, std::memory_order_relaxed);
+    return B200F_OK;
+}

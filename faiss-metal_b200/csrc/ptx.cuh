@@ -48,7 +48,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // leave its loop.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag, int32_t* status,
-                                                  int err_bit) {
+                                                  int err_bit, long long limit_cycles = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     int spins = 0;
@@ -56,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 if (status) atomicOr(status, err_bit);
                 return false;

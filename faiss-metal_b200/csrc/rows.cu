@@ -326,18 +326,29 @@ int grid_for_rows(int64_t n) {
 
 }  // namespace
 
+int device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return (dev >= 0 && dev < kMaxDevices) ? dev : kMaxDevices - 1;
+}
+
+// SM count of the CURRENT device (a process may drive several GPUs: one value per device).
 int cached_sm_count() {
-    static int sm = 0;
-    if (sm == 0) {
-        int dev = 0;
+    static int sm[kMaxDevices] = {0};
+    const int slot = device_slot();
+    if (sm[slot] == 0) {
+        int dev = 0, n = 0;
         if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm <= 0) {
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
             (void)cudaGetLastError();
-            sm = 0;
             return kNumSMsDefault;
         }
+        sm[slot] = n;
     }
-    return sm;
+    return sm[slot];
 }
 
 int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,

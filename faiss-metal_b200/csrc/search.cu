@@ -17,6 +17,7 @@
 //                      through the key matrix only when a full list could have dropped one of
 //                      its k results (rows counted and compacted on the device, no host sync)
 //   k   > 32 otherwise distance keys written per column chunk, running sort-select
+#include <atomic>
 #include <cstdio>
 #include <cmath>
 #include <cstdlib>
@@ -26,6 +27,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200f {
 
@@ -47,6 +49,9 @@ struct ProfileState {
 ProfileState g_prof;
 std::mutex g_prof_mu;
 
+constexpr int kMaxGuards = 32;
+constexpr uint32_t kCanaryWord = 0xC0DEFACEu;
+
 struct SearchPlan {
     int path;         // B200F_PATH_SCAN or B200F_PATH_TENSOR
     bool fused;       // k <= 32
@@ -67,31 +72,40 @@ struct SearchPlan {
     size_t off_dirty, off_rows, off_count, off_a2;
     size_t off_pilot_key, off_pilot_idx, off_thr, off_cand_key, off_cand_idx, off_cand_cnt;
     size_t total;
+    // debug canaries: a 256-byte guard behind every slice of the scratch region
+    int nguards;
+    uint32_t guard_off[kMaxGuards];   // in units of 256 bytes
 };
 
-// B200F_NO_FILTER=1 in the environment switches the threshold-filter path off, B200F_FILTER=1
-// takes it whenever the shard is large enough for a pilot sample, however little work the
-// search is (same use).
-bool filter_disabled() {
-    const char* e = getenv("B200F_NO_FILTER");
-    return e && e[0] == '1';
+// Which optimistic selection stages of the tensor path may run (B200F_SELECT_*): set by
+// b200f_set_selection_mode; until then the default comes from the environment variable
+// B200F_SELECT_MODE (auto | filter | no_filter | matrix), read ONCE at the first search.
+std::atomic<int> g_select_mode{-1};
+std::atomic<int> g_canaries{0};   // b200f_set_debug_canaries
+
+int select_mode() {
+    int m = g_select_mode.load(std::memory_order_relaxed);
+    if (m < 0) {
+        m = B200F_SELECT_AUTO;
+        if (const char* e = getenv("B200F_SELECT_MODE")) {
+            if (!strcmp(e, "filter")) m = B200F_SELECT_FILTER;
+            else if (!strcmp(e, "no_filter")) m = B200F_SELECT_NO_FILTER;
+            else if (!strcmp(e, "matrix")) m = B200F_SELECT_MATRIX;
+        }
+        int expected = -1;
+        if (!g_select_mode.compare_exchange_strong(expected, m)) m = expected;
+    }
+    return m;
 }
-bool filter_forced() {
-    const char* e = getenv("B200F_FILTER");
-    return e && e[0] == '1';
-}
+bool filter_disabled() { const int m = select_mode(); return m == B200F_SELECT_NO_FILTER || m == B200F_SELECT_MATRIX; }
+bool filter_forced() { return select_mode() == B200F_SELECT_FILTER; }
+bool lists_disabled() { return select_mode() == B200F_SELECT_MATRIX; }
+
 // The pilot pass costs 0.1 - 0.2 ms whatever the size (a handful of work items, each warming up
 // its lists on a single tile).  Measured: at 2.6e8 (query, row) pairs the filter path is 19 - 47 %
 // faster than the lists (d = 768 / 1536, 16-bit rows), at 1e8 - 4e8 pairs of fp32 rows with
 // d = 128 the two are level; below this many pairs the lists are used.
 constexpr int64_t FILTER_MIN_PAIRS = 1ll << 27;
-
-// B200F_NO_LISTS=1 in the environment sends every k > 32 search through the key matrix.  Read at
-// every call, so that a test can switch between the paths inside one process.
-bool lists_disabled() {
-    const char* e = getenv("B200F_NO_LISTS");
-    return e && e[0] == '1';
-}
 
 bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool pairwise,
                SearchPlan& pl) {
@@ -111,8 +125,17 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     pl.a_plane_stride = round_up64((nq > 0 ? nq : 1) * pl.a_pitch, 128);
     pl.ngroups = ceil_div64(nq, SCAN_GROUP);
     size_t off = 0;
+    const bool canaries = g_canaries.load(std::memory_order_relaxed) != 0;
+    // every slice ends on a 256-byte boundary; with canaries on, a guard follows it
+    auto adv = [&](size_t bytes) {
+        off += align256(bytes);
+        if (canaries && pl.nguards < kMaxGuards) {
+            pl.guard_off[pl.nguards++] = (uint32_t)(off / 256);
+            off += 256;
+        }
+    };
     pl.off_qnorm = off;
-    off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+    adv((size_t)(nq > 0 ? nq : 1) * 4);
     pl.gslots = 1;
     if (!pairwise && pl.path == B200F_PATH_TENSOR && k <= B200F_LIST_MAX_K && !filter_disabled()) {
         // The pilot sample holds nb / stride rows and, on average, e = k / stride of a query's k
@@ -142,10 +165,10 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         }
     }
     pl.off_gthr = off;
-    off += align256((size_t)(nq > 0 ? nq : 1) * pl.gslots * 4);
+    adv((size_t)(nq > 0 ? nq : 1) * pl.gslots * 4);
     if (pl.path == B200F_PATH_TENSOR) {
         pl.off_a = off;
-        off += align256((size_t)pl.npl * pl.a_plane_stride * 2);
+        adv((size_t)pl.npl * pl.a_plane_stride * 2);
     }
     if (pairwise) {
         pl.gemm = plan_gemm(nq, nb, sm);
@@ -165,36 +188,36 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         }
         if (P < 1) P = 1;
         pl.off_part_key = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
         pl.off_part_idx = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * P * kl * 4);
     }
     if (pl.filter) {
         const int64_t n1 = nq > 0 ? nq : 1;
         if (!pl.fused) pl.gemm = plan_gemm(nq, nb, sm);
         pl.pilot = plan_gemm(nq, ceil_div64(pl.gemm.ntiles, pl.fstride) * pl.gemm.tile_n, sm);
         pl.off_pilot_key = off;
-        off += align256((size_t)n1 * 2 * (pl.pilot.P > 0 ? pl.pilot.P : 1) * pl.frank * 4);
+        adv((size_t)n1 * 2 * (pl.pilot.P > 0 ? pl.pilot.P : 1) * pl.frank * 4);
         pl.off_pilot_idx = off;
-        off += align256((size_t)n1 * 2 * (pl.pilot.P > 0 ? pl.pilot.P : 1) * pl.frank * 4);
+        adv((size_t)n1 * 2 * (pl.pilot.P > 0 ? pl.pilot.P : 1) * pl.frank * 4);
         pl.off_thr = off;
-        off += align256((size_t)n1 * pl.frank * 4);
+        adv((size_t)n1 * pl.frank * 4);
         pl.off_cand_key = off;
-        off += align256((size_t)n1 * pl.fcap * 4);
+        adv((size_t)n1 * pl.fcap * 4);
         pl.off_cand_idx = off;
-        off += align256((size_t)n1 * pl.fcap * 4);
+        adv((size_t)n1 * pl.fcap * 4);
         pl.off_cand_cnt = off;
-        off += align256((size_t)n1 * 4);
+        adv((size_t)n1 * 4);
     }
     if (pl.lists || pl.filter) {
         pl.off_dirty = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * 4);
         pl.off_rows = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * 4);
         pl.off_count = off;
-        off += 256;
+        adv(256);
         pl.off_a2 = off;
-        off += align256((size_t)pl.npl * pl.a_plane_stride * 2);
+        adv((size_t)pl.npl * pl.a_plane_stride * 2);
     }
     if (!pl.fused) {
         int64_t cols = MATRIX_BUDGET_BYTES / (4 * (nq > 0 ? nq : 1));
@@ -205,11 +228,11 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         pl.chunk_cols = cols;
         if (!pl.lists && !pl.filter) pl.gemm = plan_gemm(nq, cols, sm);
         pl.off_matrix = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * cols * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * cols * 4);
         pl.off_run_key = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * k * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * k * 4);
         pl.off_run_idx = off;
-        off += align256((size_t)(nq > 0 ? nq : 1) * k * 4);
+        adv((size_t)(nq > 0 ? nq : 1) * k * 4);
     }
     pl.total = off;
     return true;
@@ -298,6 +321,12 @@ void count_launch(int n) {
 void main_kernel_begin(cudaStream_t stream) {
     std::lock_guard<std::mutex> g(g_prof_mu);
     if (!g_prof.enabled) return;
+    // a launch that is being captured into a graph is not timed (its events would belong to the graph)
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        (void)cudaGetLastError();
+        return;
+    }
     std::pair<cudaEvent_t, cudaEvent_t> ev;
     if (!g_prof.pool.empty()) {
         ev = g_prof.pool.back();
@@ -315,6 +344,11 @@ void main_kernel_begin(cudaStream_t stream) {
 void main_kernel_end(cudaStream_t stream) {
     std::lock_guard<std::mutex> g(g_prof_mu);
     if (!g_prof.enabled || g_prof.pending.empty()) return;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        (void)cudaGetLastError();
+        return;
+    }
     cudaEventRecord(g_prof.pending.back().second, stream);
 }
 
@@ -354,6 +388,45 @@ extern "C" int b200f_profile_read(int64_t* launches, int64_t* main_launches, dou
     return B200F_OK;
 }
 
+extern "C" int b200f_set_selection_mode(int mode) {
+    if (mode < B200F_SELECT_AUTO || mode > B200F_SELECT_MATRIX) return B200F_ERR_BAD_ARG;
+    g_select_mode.store(mode, std::memory_order_relaxed);
+    return B200F_OK;
+}
+
+extern "C" int b200f_get_selection_mode(void) { return select_mode(); }
+
+// One CTA waits, with the library's bounded-wait helper, on an mbarrier that nothing arrives
+// at.  The wait runs out after limit_cycles, the status word gets kDevErrBarrierWait and the
+// kernel returns normally: the expiry path without any fault.
+__global__ void wait_expiry_kernel(int32_t* status, long long limit_cycles) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    // every thread of the warp waits: the first one to give up raises the abort flag, the
+    // others leave through it, as the roles of the search kernels do
+    (void)mbar_wait_bounded(smem_u32(&bar), 0, &abort_flag, status, kDevErrBarrierWait, limit_cycles);
+    __syncthreads();
+}
+
+extern "C" int b200f_debug_wait_expiry(int32_t* status, int64_t limit_cycles, void* stream) {
+    if (!status || limit_cycles < 1 || limit_cycles > kWaitLimitCycles) return B200F_ERR_BAD_ARG;
+    wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, (long long)limit_cycles);
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+extern "C" int b200f_set_debug_canaries(int on) {
+    g_canaries.store(on ? 1 : 0, std::memory_order_relaxed);
+    return B200F_OK;
+}
+
 extern "C" const char* b200f_status_string(int status) {
     switch (status) {
         case B200F_OK: return "ok";
@@ -366,6 +439,7 @@ extern "C" const char* b200f_status_string(int status) {
         case B200F_ERR_OOM: return "out of device or pinned host memory";
         case B200F_ERR_RANGE: return "key out of range";
         case B200F_ERR_STATE: return "token already consumed";
+        case B200F_ERR_DEVICE_CHECK: return "a device-side self-check failed";
     }
     return "unknown status";
 }
@@ -419,6 +493,41 @@ extern "C" size_t b200f_search_scratch_bytes(int64_t nq, int64_t nb, int d, int 
     return pl.total + 256;
 }
 
+// Debug canaries: the guards behind the scratch slices are filled before the search and
+// compared after it; a changed word means some kernel wrote past its slice.  status == nullptr
+// fills, otherwise checks (status[0] |= kDevErrCanary, status[2] = 1 + number of the first bad guard).
+struct GuardList {
+    int n;
+    uint32_t off[kMaxGuards];
+};
+__global__ void canary_kernel(uint8_t* scratch, GuardList g, int32_t* status) {
+    const int gi = blockIdx.x;
+    if (gi >= g.n) return;
+    uint32_t* w = reinterpret_cast<uint32_t*>(scratch + (size_t)g.off[gi] * 256);
+    const int t = threadIdx.x;   // 64 threads: one word each
+    if (!status) {
+        w[t] = kCanaryWord ^ (uint32_t)(gi * 64 + t);
+    } else if (w[t] != (kCanaryWord ^ (uint32_t)(gi * 64 + t))) {
+        atomicOr(status, kDevErrCanary);
+        atomicMax(status + 2, gi + 1);
+    }
+}
+static int launch_canaries(const SearchPlan& pl, uint8_t* scratch, int32_t* status, cudaStream_t st) {
+    GuardList g;
+    g.n = pl.nguards;
+    for (int i = 0; i < kMaxGuards; i++) g.off[i] = i < pl.nguards ? pl.guard_off[i] : 0;
+    if (status == nullptr) {
+        canary_kernel<<<g.n, 64, 0, st>>>(scratch, g, nullptr);
+    } else {
+        canary_kernel<<<g.n, 64, 0, st>>>(scratch, g, status);
+    }
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+static int run_search(const B200FSearchArgs* a, const SearchPlan& pl);
+
 extern "C" int b200f_search(const B200FSearchArgs* a) {
     int rc = validate(a, false);
     if (rc != B200F_OK) return rc;
@@ -437,6 +546,21 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
     SearchPlan pl;
     if (!make_plan(a->nq, a->nb, a->d, a->k, a->storage, a->path, false, pl)) return B200F_ERR_BAD_ARG;
     if (!a->scratch || a->scratch_bytes < pl.total) return B200F_ERR_SCRATCH;
+    if (pl.nguards > 0) {
+        rc = launch_canaries(pl, static_cast<uint8_t*>(a->scratch), nullptr, st);
+        if (rc != B200F_OK) return rc;
+    }
+    rc = run_search(a, pl);
+    if (rc == B200F_OK && pl.nguards > 0 && a->status)
+        rc = launch_canaries(pl, static_cast<uint8_t*>(a->scratch), a->status, st);
+    return rc;
+}
+
+// The kernel sequence of one planned search (everything is enqueued on a->stream).
+static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
+    int rc = B200F_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+    const bool l2 = a->metric == B200F_METRIC_L2;
     uint8_t* scratch = static_cast<uint8_t*>(a->scratch);
     float* qnorm = reinterpret_cast<float*>(scratch + pl.off_qnorm);
     const int sm = cached_sm_count();
@@ -582,6 +706,27 @@ extern "C" int b200f_search(const B200FSearchArgs* a) {
                                  a->out_dist, a->out_labels, nq_dev, row_map, st);
 }
 
+__global__ void poke_kernel(uint32_t* word) { *word = 0; }
+
+extern "C" int b200f_debug_canary_selftest(void* scratch, size_t scratch_bytes, int corrupt, int32_t* status,
+                                           void* stream) {
+    if (!scratch || scratch_bytes < 4 * 1024 || !status || (reinterpret_cast<uintptr_t>(scratch) & 255) != 0)
+        return B200F_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    SearchPlan pl{};
+    pl.nguards = 3;
+    pl.guard_off[0] = 1;   // guards at bytes 256, 1536 and 3584 of the region
+    pl.guard_off[1] = 6;
+    pl.guard_off[2] = 14;
+    int rc = launch_canaries(pl, static_cast<uint8_t*>(scratch), nullptr, st);
+    if (rc != B200F_OK) return rc;
+    if (corrupt) {   // what a kernel running past its slice would do: one word of guard 1
+        poke_kernel<<<1, 1, 0, st>>>(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + 6 * 256 + 40));
+        B200F_LAUNCH_CHECK();
+    }
+    return launch_canaries(pl, static_cast<uint8_t*>(scratch), status, st);
+}
+
 extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64_t ld_out) {
     int rc = validate(a, true);
     if (rc != B200F_OK) return rc;
@@ -638,7 +783,6 @@ namespace {
 constexpr size_t kNoAllocScratchBytes = 1u << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
-constexpr int kMaxDevices = 64;
 void* g_noalloc_ptr[kMaxDevices] = {nullptr};
 std::mutex g_noalloc_mu;
 
@@ -669,7 +813,8 @@ extern "C" size_t b200f_noalloc_scratch_capacity(void) { return kNoAllocScratchB
 
 extern "C" int b200f_search_small_noalloc(const B200FSearchArgs* a) {
     if (!a) return B200F_ERR_BAD_ARG;
-    if (a->nq < 0 || a->nq > 4 || a->k < 1 || a->k > B200F_FUSED_MAX_K) return B200F_ERR_UNSUPPORTED;
+    if (a->nq < 0 || a->k < 1) return B200F_ERR_BAD_ARG;   // same codes as b200f_search
+    if (a->nq > 4 || a->k > B200F_FUSED_MAX_K) return B200F_ERR_UNSUPPORTED;
     B200FSearchArgs c = *a;
     c.path = B200F_PATH_SCAN;
     const size_t need = b200f_search_scratch_bytes(c.nq, c.nb, c.d, c.k, c.storage, c.path);

@@ -599,11 +599,12 @@ int launch_sort_select(const SortSelectParams& p, cudaStream_t stream) {
     if (p.nq <= 0) return B200F_OK;
     if (p.k < 1 || p.k > B200F_MAX_K) return B200F_ERR_UNSUPPORTED;
     const int smem = SS_CAP * 8;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[kMaxDevices] = {false};   // the opt-in is per device
+    const int slot = device_slot();
+    if (!attr_set[slot]) {
         B200F_CUDA_TRY(cudaFuncSetAttribute(sort_select_kernel<SRC>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
+        attr_set[slot] = true;
     }
     int64_t g = p.nq;
     const int64_t cap = (int64_t)cached_sm_count() * 2 * 8;

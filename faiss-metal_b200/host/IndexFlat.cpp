@@ -11,12 +11,15 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <future>
 #include <limits>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/b200_flat.h"
+#include "../include/faiss-b200/B200Exception.h"
 #include "../include/faiss-b200/B200IndexFlat.h"
 #include "../include/faiss-b200/B200Resources.h"
 #include "GrowableArray.h"
@@ -25,7 +28,9 @@ namespace faiss_b200 {
 
 namespace {
 
-constexpr size_t kStageBytes = 64ull << 20;   // fp32 staging chunk for add / reconstruct_n
+constexpr size_t kStageBytes = 32ull << 20;   // fp32 staging chunk of add / reconstruct_n (two in flight)
+constexpr int64_t kGraphMaxQueries = 8;        // searches this small are replayed from a CUDA graph
+constexpr size_t kMaxGraphs = 8;               // graphs kept per index (least recently used goes)
 constexpr int64_t kFusedBatch = 16384;        // queries per launch, k <= 1024 (fused kernel, lists)
 constexpr int64_t kSelectBatch = 1024;        // queries per launch beyond: few rows, wide column chunks
 
@@ -33,15 +38,27 @@ void cudaCheck(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
         std::string msg = std::string("faiss-b200: ") + what + ": " + cudaGetErrorString(e);
         (void)cudaGetLastError();
-        throw std::runtime_error(msg);
+        throw B200RuntimeError(e == cudaErrorMemoryAllocation ? B200F_ERR_OOM : B200F_ERR_CUDA, msg);
     }
 }
 
+// A status code of the op-level C-ABI becomes the exception class the reference would have
+// thrown (argument errors: faiss::FaissException; everything else: std::runtime_error), with
+// the code kept inside.
 void abiCheck(int rc, const char* what) {
     if (rc == B200F_OK) return;
     std::string msg = std::string("faiss-b200: ") + what + ": " + b200f_status_string(rc);
-    if (rc == B200F_ERR_BAD_ARG || rc == B200F_ERR_UNSUPPORTED) throw faiss::FaissException(msg);
-    throw std::runtime_error(msg);
+    if (rc == B200F_ERR_BAD_ARG || rc == B200F_ERR_UNSUPPORTED || rc == B200F_ERR_RANGE || rc == B200F_ERR_STATE)
+        throw B200ArgumentError(rc, msg);
+    throw B200RuntimeError(rc, msg);
+}
+
+// Device status word of a search (B200FSearchArgs::status[0]): bit 1 = a bounded wait ran out,
+// any other bit = a self-check of a kernel failed.
+[[noreturn]] void throwDeviceStatus(int word, const char* what) {
+    const int code = (word & 1) ? B200F_ERR_DEVICE_WAIT : B200F_ERR_DEVICE_CHECK;
+    throw B200RuntimeError(code, std::string("faiss-b200: ") + what + " reported device status " +
+                                         std::to_string(word) + " (" + b200f_status_string(code) + ")");
 }
 
 struct DeviceGuard {
@@ -56,14 +73,52 @@ struct DeviceGuard {
     }
 };
 
-bool isDevicePointer(const void* p) {
-    if (!p) return false;
+enum class PtrKind { Pageable, Pinned, Device };
+
+PtrKind pointerKind(const void* p) {
+    if (!p) return PtrKind::Pageable;
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
         (void)cudaGetLastError();
-        return false;
+        return PtrKind::Pageable;
     }
-    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return PtrKind::Device;
+    return attr.type == cudaMemoryTypeHost ? PtrKind::Pinned : PtrKind::Pageable;
+}
+
+bool isDevicePointer(const void* p) { return pointerKind(p) == PtrKind::Device; }
+
+// Host copy into / out of pinned staging.  One thread moves ~10 GB/s, well under what the
+// copy engine takes from pinned memory, so large blocks are split over a few threads.
+void hostCopy(void* dst, const void* src, size_t bytes) {
+    constexpr size_t kPerThread = 4ull << 20;
+    const unsigned hw = std::thread::hardware_concurrency();
+    size_t nthreads = std::min<size_t>({bytes / kPerThread, (size_t)4, (size_t)(hw > 1 ? hw - 1 : 1)});
+    if (nthreads <= 1) {
+        std::memcpy(dst, src, bytes);
+        return;
+    }
+    const size_t per = ((bytes / nthreads) + 63) & ~(size_t)63;
+    std::vector<std::future<void>> parts;
+    for (size_t t = 1; t < nthreads; t++) {
+        const size_t off = t * per;
+        if (off >= bytes) break;
+        const size_t len = std::min(per, bytes - off);
+        parts.push_back(std::async(std::launch::async, [=] {
+            std::memcpy(static_cast<uint8_t*>(dst) + off, static_cast<const uint8_t*>(src) + off, len);
+        }));
+    }
+    std::memcpy(dst, src, std::min(per, bytes));
+    for (auto& f : parts) f.get();
+}
+
+// B200F_NO_VMM=1 in the environment makes allocate-copy-free growth the default (read once).
+bool growthByCopyDefault() {
+    static const bool v = [] {
+        const char* off = std::getenv("B200F_NO_VMM");
+        return off && off[0] == '1';
+    }();
+    return v;
 }
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -107,6 +162,43 @@ struct B200IndexFlat::Impl {
     int64_t planeStrideFixed = 0;  // elements between split planes when inPlace
 
     int64_t planeStride() const { return inPlace ? planeStrideFixed : capacity * planePitch; }
+    int growthMode = -1;           // -1: process default, 0: in place, 1: allocate-copy-free
+
+    // Small searches (n <= kGraphMaxQueries, host buffers) replayed from CUDA graphs.  A graph
+    // holds the whole call: host-to-device copy of the queries out of its pinned slot, the
+    // search, and the copies of distances, labels and status word back into the slot.  It is
+    // tied to the addresses and sizes it was captured with: `generation` changes whenever the
+    // stored rows, the label base or the forced path change, and stale graphs are dropped.
+    struct SearchGraph {
+        int64_t n = 0, k = 0;
+        int selectMode = 0;
+        void* region = nullptr;      // device: queries, outputs, scratch (owned by the graph)
+        uint8_t* host = nullptr;     // pinned: queries | distances | labels | status
+        size_t hostDistOff = 0, hostLabOff = 0, hostStatusOff = 0;
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        uint64_t lastUse = 0;
+    };
+    mutable std::vector<SearchGraph> graphs;
+    mutable std::vector<std::pair<int64_t, int64_t>> seenShapes;  // (n, k) searched once without a graph
+    mutable uint64_t useCounter = 0;
+    bool useGraphs = true;
+
+    void destroyGraph(SearchGraph& g) const {
+        if (g.exec) (void)cudaGraphExecDestroy(g.exec);
+        if (g.graph) (void)cudaGraphDestroy(g.graph);
+        if (g.region) res->releaseDeviceTemp(g.region);
+        if (g.host) res->releasePinnedTemp(g.host);
+        g = SearchGraph{};
+    }
+    // The stored rows / label base / path changed: nothing captured so far is valid.
+    void invalidateGraphs() const {
+        if (graphs.empty() && seenShapes.empty()) return;
+        (void)cudaStreamSynchronize(stream());
+        for (auto& g : graphs) destroyGraph(g);
+        graphs.clear();
+        seenShapes.clear();
+    }
 
     void freeStorage() {
         if (inPlace) {
@@ -128,8 +220,7 @@ struct B200IndexFlat::Impl {
     // First allocation of an empty index: reserve the address ranges.  Returns false (nothing
     // reserved) when in-place growth cannot be used.
     bool reserveInPlace() {
-        const char* off = std::getenv("B200F_NO_VMM");
-        if (off && off[0] == '1') return false;
+        if (growthMode == 1 || (growthMode < 0 && growthByCopyDefault())) return false;
         const int dev = res->getDevice();
         if (!GrowableDeviceArray::supported(dev)) return false;
         const size_t es = elemBytes(storage);
@@ -169,8 +260,8 @@ struct B200IndexFlat::Impl {
         if (capacity == 0 && !rows && !inPlace) (void)reserveInPlace();
         if (inPlace) {
             if (want > maxRows)
-                throw std::runtime_error("faiss-b200: the index cannot hold " + std::to_string(want) +
-                                         " rows on this device");
+                throw B200RuntimeError(B200F_ERR_OOM, "faiss-b200: the index cannot hold " + std::to_string(want) +
+                                                              " rows on this device");
             const size_t es = elemBytes(storage);
             vRows.back(0, (size_t)want * pitch * es);
             if (planes)
@@ -285,7 +376,7 @@ B200IndexFlat::B200IndexFlat(std::shared_ptr<B200Resources> resources, int d_,
     impl_->status = static_cast<int32_t*>(impl_->res->allocBuffer(256));
     impl_->oneRow = static_cast<float*>(impl_->res->allocBuffer((size_t)d_ * 4));
     impl_->hostStatus = static_cast<int32_t*>(alloc_pinned(16));
-    if (!impl_->hostStatus) throw std::runtime_error("faiss-b200: pinned allocation failed");
+    if (!impl_->hostStatus) throw B200RuntimeError(B200F_ERR_OOM, "faiss-b200: pinned allocation failed");
     cudaCheck(cudaMemsetAsync(impl_->status, 0, 256, impl_->stream()), "memset status");
     is_trained = true;
     ntotal = 0;
@@ -296,6 +387,7 @@ B200IndexFlat::~B200IndexFlat() {
     try {
         DeviceGuard g(impl_->res->getDevice());
         (void)cudaStreamSynchronize(impl_->stream());
+        impl_->invalidateGraphs();
         impl_->freeStorage();
         impl_->res->deallocBuffer(impl_->status);
         impl_->res->deallocBuffer(impl_->oneRow);
@@ -306,16 +398,35 @@ B200IndexFlat::~B200IndexFlat() {
 
 void B200IndexFlat::reserve(faiss::idx_t n) {
     DeviceGuard g(impl_->res->getDevice());
-    if (n > impl_->capacity) impl_->grow(n, ntotal);
+    if (n > impl_->capacity) {
+        impl_->invalidateGraphs();
+        impl_->grow(n, ntotal);
+    }
+}
+
+void B200IndexFlat::setGrowthMode(int mode) {
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, mode == 0 || mode == 1, "growth mode must be 0 (in place) or 1 (copy)");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_STATE, impl_->capacity == 0 && !impl_->rows,
+                          "the growth mode can only be chosen on an index that holds no storage yet");
+    impl_->growthMode = mode;
+}
+
+void B200IndexFlat::setUseGraphs(bool on) {
+    if (!on) {
+        DeviceGuard g(impl_->res->getDevice());
+        impl_->invalidateGraphs();
+    }
+    impl_->useGraphs = on;
 }
 
 void B200IndexFlat::add(faiss::idx_t n, const float* x) {
     if (n == 0) return;  // src/MetalIndexFlat.mm:186
-    FAISS_THROW_IF_NOT_MSG(n > 0 && x != nullptr, "add: invalid arguments");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, n > 0 && x != nullptr, "add: invalid arguments");
     const int64_t newTotal = ntotal + n;
-    FAISS_THROW_IF_NOT_MSG(newTotal <= B200DeviceCapabilities::kMaxVectorsPerShard,
-                           "B200IndexFlat holds at most 2^31-1 vectors per shard (int32 row numbers)");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_UNSUPPORTED, newTotal <= B200DeviceCapabilities::kMaxVectorsPerShard,
+                          "B200IndexFlat holds at most 2^31-1 vectors per shard (int32 row numbers)");
     DeviceGuard g(impl_->res->getDevice());
+    impl_->invalidateGraphs();
     if (newTotal > impl_->capacity) {
         // growth rule of the reference: max(newTotal, 2 * capacity, 1024)
         // (src/MetalIndexFlat.mm:196-197,272-273)
@@ -325,19 +436,7 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
     }
     cudaStream_t st = impl_->stream();
     const size_t es = elemBytes(impl_->storage);
-    const bool onDevice = isDevicePointer(x);
-    const int64_t rowsPerChunk = std::max<int64_t>(1, (int64_t)(kStageBytes / ((size_t)d * 4)));
-    float* stage = nullptr;
-    if (!onDevice)
-        stage = static_cast<float*>(impl_->res->getScratch((size_t)std::min<int64_t>(rowsPerChunk, n) * d * 4));
-    for (int64_t r0 = 0; r0 < n; r0 += rowsPerChunk) {
-        const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
-        const float* src = x + (size_t)r0 * d;
-        if (!onDevice) {
-            cudaCheck(cudaMemcpyAsync(stage, src, (size_t)nr * d * 4, cudaMemcpyHostToDevice, st),
-                      "add: host to device copy");
-            src = stage;
-        }
+    auto store = [&](const float* src, int64_t r0, int64_t nr) {
         const int64_t row = ntotal + r0;
         abiCheck(b200f_store_rows(
                          src, nr, d, impl_->storageCode(),
@@ -346,6 +445,72 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
                          impl_->planePitch, impl_->planeStride(),
                          impl_->norms ? impl_->norms + row : nullptr, impl_->l2 ? 1 : 0, st),
                  "add: store rows");
+    };
+    const PtrKind kind = pointerKind(x);
+    if (kind == PtrKind::Device) {
+        store(x, 0, n);
+    } else {
+        // Ingest pipeline.  The input is cut into chunks of kStageBytes; chunk i is copied host to
+        // device on the upload stream into one of two device staging buffers while the
+        // conversion kernel of chunk i - 1 runs on the search stream.  Pageable input goes through
+        // two pinned staging buffers first (filled by host threads while the previous chunk is
+        // on the bus); pinned input is copied straight from where it lies.  One host
+        // synchronisation, at the end.
+        const int64_t rowsPerChunk = std::max<int64_t>(1, (int64_t)(kStageBytes / ((size_t)d * 4)));
+        const size_t chunkBytes = align256((size_t)std::min<int64_t>(rowsPerChunk, n) * d * 4);
+        const int nbuf = n > rowsPerChunk ? 2 : 1;
+        uint8_t* dev = static_cast<uint8_t*>(impl_->res->getScratch(nbuf * chunkBytes));
+        uint8_t* pin = kind == PtrKind::Pageable
+                               ? static_cast<uint8_t*>(impl_->res->getPinnedStaging(nbuf * chunkBytes))
+                               : nullptr;
+        cudaStream_t up = reinterpret_cast<cudaStream_t>(impl_->res->getAuxStream(B200Resources::kUploadStream));
+        cudaEvent_t copied[2] = {nullptr, nullptr}, consumed[2] = {nullptr, nullptr};
+        cudaEvent_t start = reinterpret_cast<cudaEvent_t>(impl_->res->acquireEvent());
+        for (int i = 0; i < nbuf; i++) {
+            copied[i] = reinterpret_cast<cudaEvent_t>(impl_->res->acquireEvent());
+            consumed[i] = reinterpret_cast<cudaEvent_t>(impl_->res->acquireEvent());
+        }
+        auto releaseEvents = [&] {
+            impl_->res->releaseEvent(start);
+            for (int i = 0; i < nbuf; i++) {
+                impl_->res->releaseEvent(copied[i]);
+                impl_->res->releaseEvent(consumed[i]);
+            }
+        };
+        try {
+            // the staging region may still be in use by work queued earlier on the search stream
+            cudaCheck(cudaEventRecord(start, st), "add: event record");
+            cudaCheck(cudaStreamWaitEvent(up, start, 0), "add: stream wait");
+            int64_t chunk = 0;
+            for (int64_t r0 = 0; r0 < n; r0 += rowsPerChunk, chunk++) {
+                const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
+                const size_t bytes = (size_t)nr * d * 4;
+                const int b = (int)(chunk % nbuf);
+                const float* src = x + (size_t)r0 * d;
+                if (chunk >= nbuf) {
+                    // device buffer b: the conversion of chunk - 2 has to be done with it
+                    cudaCheck(cudaStreamWaitEvent(up, consumed[b], 0), "add: stream wait");
+                    // pinned buffer b: its copy to the device has to be complete
+                    if (pin) cudaCheck(cudaEventSynchronize(copied[b]), "add: event synchronize");
+                }
+                if (pin) {
+                    hostCopy(pin + (size_t)b * chunkBytes, src, bytes);
+                    src = reinterpret_cast<const float*>(pin + (size_t)b * chunkBytes);
+                }
+                cudaCheck(cudaMemcpyAsync(dev + (size_t)b * chunkBytes, src, bytes, cudaMemcpyHostToDevice, up),
+                          "add: host to device copy");
+                cudaCheck(cudaEventRecord(copied[b], up), "add: event record");
+                cudaCheck(cudaStreamWaitEvent(st, copied[b], 0), "add: stream wait");
+                store(reinterpret_cast<const float*>(dev + (size_t)b * chunkBytes), r0, nr);
+                cudaCheck(cudaEventRecord(consumed[b], st), "add: event record");
+            }
+        } catch (...) {
+            (void)cudaStreamSynchronize(up);
+            (void)cudaStreamSynchronize(st);
+            releaseEvents();
+            throw;
+        }
+        releaseEvents();
     }
     // the caller may free x as soon as add returns
     cudaCheck(cudaStreamSynchronize(st), "add: synchronize");
@@ -356,6 +521,7 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
 void B200IndexFlat::reset() {
     DeviceGuard g(impl_->res->getDevice());
     cudaCheck(cudaStreamSynchronize(impl_->stream()), "reset: synchronize");
+    impl_->invalidateGraphs();
     impl_->freeStorage();
     impl_->mirror.clear();
     impl_->mirror.shrink_to_fit();
@@ -364,40 +530,90 @@ void B200IndexFlat::reset() {
 }
 
 void B200IndexFlat::reconstruct_n(faiss::idx_t first, faiss::idx_t n, float* out) const {
-    FAISS_THROW_IF_NOT_FMT(first >= 0 && n >= 0 && first + n <= ntotal,
-                           "reconstruct_n: range [%lld, %lld) outside [0, %lld)", (long long)first,
-                           (long long)(first + n), (long long)ntotal);
+    if (!(first >= 0 && n >= 0 && first + n <= ntotal))
+        throw B200ArgumentError(B200F_ERR_RANGE, "faiss-b200: reconstruct_n: range [" + std::to_string(first) + ", " +
+                                                         std::to_string(first + n) + ") outside [0, " +
+                                                         std::to_string(ntotal) + ")");
     if (n == 0) return;
-    FAISS_THROW_IF_NOT_MSG(out != nullptr, "reconstruct_n: null output");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, out != nullptr, "reconstruct_n: null output");
     DeviceGuard g(impl_->res->getDevice());
     cudaStream_t st = impl_->stream();
     const size_t es = elemBytes(impl_->storage);
-    const bool outOnDevice = isDevicePointer(out);
-    const int64_t rowsPerChunk = std::max<int64_t>(1, (int64_t)(kStageBytes / ((size_t)d * 4)));
-    float* stage = nullptr;
-    if (!outOnDevice)
-        stage = static_cast<float*>(impl_->res->getScratch((size_t)std::min<int64_t>(rowsPerChunk, n) * d * 4));
-    for (int64_t r0 = 0; r0 < n; r0 += rowsPerChunk) {
-        const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
-        float* dst = outOnDevice ? out + (size_t)r0 * d : stage;
+    auto load = [&](int64_t r0, int64_t nr, float* dst) {
         abiCheck(b200f_load_rows(static_cast<const uint8_t*>(impl_->rows) + (size_t)(first + r0) * impl_->pitch * es,
                                  impl_->storageCode(), nr, d, impl_->pitch, dst, st),
                  "reconstruct_n: load rows");
-        if (!outOnDevice) {
-            cudaCheck(cudaMemcpyAsync(out + (size_t)r0 * d, stage, (size_t)nr * d * 4,
-                                      cudaMemcpyDeviceToHost, st),
-                      "reconstruct_n: device to host copy");
-            cudaCheck(cudaStreamSynchronize(st), "reconstruct_n: synchronize");
-        }
+    };
+    const PtrKind kind = pointerKind(out);
+    if (kind == PtrKind::Device) {
+        load(0, n, out);
+        cudaCheck(cudaStreamSynchronize(st), "reconstruct_n: synchronize");
+        return;
     }
-    cudaCheck(cudaStreamSynchronize(st), "reconstruct_n: synchronize");
+    // The ingest pipeline backwards: chunk i is dequantised on the search stream into one of two
+    // device buffers while chunk i - 1 crosses the bus on the download stream (into pinned
+    // staging for pageable output, else straight into `out`) and the host threads copy chunk
+    // i - 2 out of the staging.
+    const int64_t rowsPerChunk = std::max<int64_t>(1, (int64_t)(kStageBytes / ((size_t)d * 4)));
+    const size_t chunkBytes = align256((size_t)std::min<int64_t>(rowsPerChunk, n) * d * 4);
+    const int nbuf = n > rowsPerChunk ? 2 : 1;
+    uint8_t* dev = static_cast<uint8_t*>(impl_->res->getScratch(nbuf * chunkBytes));
+    uint8_t* pin = kind == PtrKind::Pageable ? static_cast<uint8_t*>(impl_->res->getPinnedStaging(nbuf * chunkBytes))
+                                             : nullptr;
+    cudaStream_t down = reinterpret_cast<cudaStream_t>(impl_->res->getAuxStream(B200Resources::kDownloadStream));
+    cudaEvent_t loaded[2] = {nullptr, nullptr}, landed[2] = {nullptr, nullptr};
+    for (int i = 0; i < nbuf; i++) {
+        loaded[i] = reinterpret_cast<cudaEvent_t>(impl_->res->acquireEvent());
+        landed[i] = reinterpret_cast<cudaEvent_t>(impl_->res->acquireEvent());
+    }
+    auto releaseEvents = [&] {
+        for (int i = 0; i < nbuf; i++) {
+            impl_->res->releaseEvent(loaded[i]);
+            impl_->res->releaseEvent(landed[i]);
+        }
+    };
+    // host side of chunk c (pageable output only): wait for its copy, move it out of the staging
+    auto finish = [&](int64_t c) {
+        if (!pin) return;
+        const int64_t r0 = c * rowsPerChunk;
+        const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
+        cudaCheck(cudaEventSynchronize(landed[c % nbuf]), "reconstruct_n: event synchronize");
+        hostCopy(out + (size_t)r0 * d, pin + (size_t)(c % nbuf) * chunkBytes, (size_t)nr * d * 4);
+    };
+    try {
+        int64_t chunk = 0;
+        for (int64_t r0 = 0; r0 < n; r0 += rowsPerChunk, chunk++) {
+            const int64_t nr = std::min<int64_t>(rowsPerChunk, n - r0);
+            const int b = (int)(chunk % nbuf);
+            // device buffer b is free once the copy of chunk - 2 has left it
+            if (chunk >= nbuf) cudaCheck(cudaStreamWaitEvent(st, landed[b], 0), "reconstruct_n: stream wait");
+            load(r0, nr, reinterpret_cast<float*>(dev + (size_t)b * chunkBytes));
+            cudaCheck(cudaEventRecord(loaded[b], st), "reconstruct_n: event record");
+            cudaCheck(cudaStreamWaitEvent(down, loaded[b], 0), "reconstruct_n: stream wait");
+            // pinned buffer b was emptied by finish(chunk - 2) in the previous round
+            void* dst = pin ? static_cast<void*>(pin + (size_t)b * chunkBytes) : static_cast<void*>(out + (size_t)r0 * d);
+            cudaCheck(cudaMemcpyAsync(dst, dev + (size_t)b * chunkBytes, (size_t)nr * d * 4, cudaMemcpyDeviceToHost, down),
+                      "reconstruct_n: device to host copy");
+            cudaCheck(cudaEventRecord(landed[b], down), "reconstruct_n: event record");
+            if (chunk >= 1) finish(chunk - 1);
+        }
+        finish(chunk - 1);
+        cudaCheck(cudaStreamSynchronize(down), "reconstruct_n: synchronize");
+        cudaCheck(cudaStreamSynchronize(st), "reconstruct_n: synchronize");
+    } catch (...) {
+        (void)cudaStreamSynchronize(down);
+        (void)cudaStreamSynchronize(st);
+        releaseEvents();
+        throw;
+    }
+    releaseEvents();
 }
 
 void B200IndexFlat::reconstruct(faiss::idx_t key, float* recons) const {
     // range check of the reference: src/MetalIndexFlat.mm:509-511
-    FAISS_THROW_IF_NOT_FMT(key >= 0 && key < ntotal, "reconstruct: key %lld out of range [0, %lld)",
-                           (long long)key, (long long)ntotal);
-    FAISS_THROW_IF_NOT_MSG(recons != nullptr, "reconstruct: null output");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_RANGE, key >= 0 && key < ntotal,
+                          "reconstruct: key " + std::to_string(key) + " out of range [0, " + std::to_string(ntotal) + ")");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, recons != nullptr, "reconstruct: null output");
     DeviceGuard g(impl_->res->getDevice());
     cudaStream_t st = impl_->stream();
     const size_t es = elemBytes(impl_->storage);
@@ -425,12 +641,26 @@ bool B200IndexFlat::isFloat16Storage() const { return impl_->storage == StorageT
 bool B200IndexFlat::isBFloat16Storage() const { return impl_->storage == StorageType::BFloat16; }
 StorageType B200IndexFlat::getStorageType() const { return impl_->storage; }
 void B200IndexFlat::setForcePath(int path) {
-    FAISS_THROW_IF_NOT_MSG(path >= B200F_PATH_AUTO && path <= B200F_PATH_TENSOR, "invalid path");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, path >= B200F_PATH_AUTO && path <= B200F_PATH_TENSOR, "invalid path");
+    if (path != impl_->forcePath) {
+        DeviceGuard g(impl_->res->getDevice());
+        impl_->invalidateGraphs();
+    }
     impl_->forcePath = path;
 }
-void B200IndexFlat::setLabelBase(faiss::idx_t base) { impl_->labelBase = base; }
+void B200IndexFlat::setLabelBase(faiss::idx_t base) {
+    if (base != impl_->labelBase) {
+        DeviceGuard g(impl_->res->getDevice());
+        impl_->invalidateGraphs();
+    }
+    impl_->labelBase = base;
+}
 const void* B200IndexFlat::getDeviceRows() const { return impl_->rows; }
 int B200IndexFlat::lastDeviceStatus() const { return impl_->lastStatus; }
+void B200IndexFlat::debugWaitExpiry(int64_t limitCycles) {
+    DeviceGuard g(impl_->res->getDevice());
+    abiCheck(b200f_debug_wait_expiry(impl_->status, limitCycles, impl_->stream()), "debugWaitExpiry");
+}
 
 // ---------------------------------------------------------------------------------------
 // search
@@ -439,13 +669,14 @@ namespace {
 
 void checkSearchArgs(faiss::idx_t n, const float* x, faiss::idx_t k, const float* distances,
                      const faiss::idx_t* labels, faiss::idx_t ntotal) {
-    FAISS_THROW_IF_NOT_MSG(k > 0, "k must be > 0");  // src/MetalIndexFlat.mm:321
-    FAISS_THROW_IF_NOT_FMT(k <= B200F_MAX_K, "k = %lld exceeds the maximum of %d", (long long)k,
-                           B200F_MAX_K);             // src/MetalSelect.mm:65-70
-    FAISS_THROW_IF_NOT_MSG(ntotal <= B200DeviceCapabilities::kMaxVectorsPerShard,
-                           "B200IndexFlat supports at most 2^31-1 vectors per shard (int32 row numbers)");
-    FAISS_THROW_IF_NOT_MSG(n >= 0, "n must be >= 0");
-    if (n > 0) FAISS_THROW_IF_NOT_MSG(x && distances && labels, "search: null pointer");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, k > 0, "k must be > 0");  // src/MetalIndexFlat.mm:321
+    B200_THROW_ARG_IF_NOT(B200F_ERR_UNSUPPORTED, k <= B200F_MAX_K,
+                          "k = " + std::to_string(k) + " exceeds the maximum of " +
+                                  std::to_string(B200F_MAX_K));  // src/MetalSelect.mm:65-70
+    B200_THROW_ARG_IF_NOT(B200F_ERR_UNSUPPORTED, ntotal <= B200DeviceCapabilities::kMaxVectorsPerShard,
+                          "B200IndexFlat supports at most 2^31-1 vectors per shard (int32 row numbers)");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, n >= 0, "n must be >= 0");
+    if (n > 0) B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, x && distances && labels, "search: null pointer");
 }
 
 }  // namespace
@@ -459,10 +690,13 @@ void B200IndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k, float
     const bool qOnDevice = isDevicePointer(x);
     const bool dOnDevice = isDevicePointer(distances);
     const bool lOnDevice = isDevicePointer(labels);
+    if (n <= kGraphMaxQueries && impl_->useGraphs && !qOnDevice && !dOnDevice && !lOnDevice &&
+        searchFromGraph(n, x, k, distances, labels))
+        return;
     const int64_t batch = std::min<int64_t>(n, k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch);
     const size_t scratchBytes =
             b200f_search_scratch_bytes(batch, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
-    FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "search: cannot plan this shape");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, scratchBytes > 0, "search: cannot plan this shape");
     CallLayout L = makeLayout(batch, batch, d, k, !qOnDevice, batch, true, scratchBytes);
     uint8_t* region = static_cast<uint8_t*>(impl_->res->getScratch(L.total));
     impl_->lastStatus = 0;
@@ -502,11 +736,103 @@ void B200IndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k, float
         cudaCheck(cudaStreamSynchronize(st), "search: synchronize");
         if (impl_->hostStatus[0] != 0) {
             impl_->lastStatus = impl_->hostStatus[0];
-            throw std::runtime_error("faiss-b200: search kernel reported device status " +
-                                     std::to_string(impl_->hostStatus[0]) + " (" +
-                                     b200f_status_string(B200F_ERR_DEVICE_WAIT) + ")");
+            throwDeviceStatus(impl_->hostStatus[0], "search");
         }
     }
+}
+
+// Small search with host buffers through a captured graph.  The first call with a shape runs
+// the ordinary path (which also performs every lazy one-time set-up of the library, none of
+// which may happen inside a capture); the second call captures; later calls replay: one memcpy
+// into the pinned slot, one graph launch, one stream synchronisation, one memcpy out.
+// Returns false when the ordinary path should serve the call.
+bool B200IndexFlat::searchFromGraph(faiss::idx_t n, const float* x, faiss::idx_t k, float* distances,
+                                    faiss::idx_t* labels) const {
+    Impl& im = *impl_;
+    cudaStream_t st = im.stream();
+    const int selectMode = b200f_get_selection_mode();
+    Impl::SearchGraph* g = nullptr;
+    for (auto& e : im.graphs)
+        if (e.n == n && e.k == k && e.selectMode == selectMode) g = &e;
+    if (!g) {
+        const std::pair<int64_t, int64_t> shape(n, k);
+        if (std::find(im.seenShapes.begin(), im.seenShapes.end(), shape) == im.seenShapes.end()) {
+            if (im.seenShapes.size() >= 64) im.seenShapes.clear();
+            im.seenShapes.push_back(shape);
+            return false;
+        }
+        const size_t scratchBytes = b200f_search_scratch_bytes(n, ntotal, d, (int)k, im.storageCode(), im.forcePath);
+        if (scratchBytes == 0) return false;
+        if (im.graphs.size() >= kMaxGraphs) {
+            size_t oldest = 0;
+            for (size_t i = 1; i < im.graphs.size(); i++)
+                if (im.graphs[i].lastUse < im.graphs[oldest].lastUse) oldest = i;
+            cudaCheck(cudaStreamSynchronize(st), "search: synchronize");
+            im.destroyGraph(im.graphs[oldest]);
+            im.graphs.erase(im.graphs.begin() + (long)oldest);
+        }
+        Impl::SearchGraph e;
+        e.n = n;
+        e.k = k;
+        e.selectMode = selectMode;
+        CallLayout L = makeLayout(n, n, d, k, true, n, true, scratchBytes);
+        size_t hoff = align256((size_t)n * d * 4);
+        e.hostDistOff = hoff;
+        hoff += align256((size_t)n * k * 4);
+        e.hostLabOff = hoff;
+        hoff += align256((size_t)n * k * 8);
+        e.hostStatusOff = hoff;
+        hoff += 256;
+        try {
+            e.region = im.res->acquireDeviceTemp(L.total);
+            e.host = static_cast<uint8_t*>(im.res->acquirePinnedTemp(hoff));
+            if (!e.host) throw B200RuntimeError(B200F_ERR_OOM, "faiss-b200: pinned allocation failed");
+            uint8_t* region = static_cast<uint8_t*>(e.region);
+            B200FSearchArgs a;
+            im.fillArgs(a, ntotal);
+            a.queries = reinterpret_cast<const float*>(region + L.offQueries);
+            a.nq = n;
+            a.k = (int)k;
+            a.out_dist = reinterpret_cast<float*>(region + L.offDist);
+            a.out_labels = reinterpret_cast<int64_t*>(region + L.offLabels);
+            a.scratch = region + L.offScratch;
+            a.scratch_bytes = L.scratchBytes;
+            cudaCheck(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "search: begin capture");
+            cudaError_t ce = cudaMemcpyAsync(region + L.offQueries, e.host, (size_t)n * d * 4, cudaMemcpyHostToDevice, st);
+            int rc = ce == cudaSuccess ? b200f_search(&a) : B200F_ERR_CUDA;
+            if (rc == B200F_OK) {
+                ce = cudaMemcpyAsync(e.host + e.hostDistOff, a.out_dist, (size_t)n * k * 4, cudaMemcpyDeviceToHost, st);
+                if (ce == cudaSuccess)
+                    ce = cudaMemcpyAsync(e.host + e.hostLabOff, a.out_labels, (size_t)n * k * 8, cudaMemcpyDeviceToHost, st);
+                if (ce == cudaSuccess)
+                    ce = cudaMemcpyAsync(e.host + e.hostStatusOff, im.status, 16, cudaMemcpyDeviceToHost, st);
+                if (ce != cudaSuccess) rc = B200F_ERR_CUDA;
+            }
+            cudaError_t ee = cudaStreamEndCapture(st, &e.graph);   // always ends the capture
+            if (rc != B200F_OK || ee != cudaSuccess || !e.graph ||
+                cudaGraphInstantiate(&e.exec, e.graph, 0) != cudaSuccess) {
+                (void)cudaGetLastError();
+                im.destroyGraph(e);
+                im.useGraphs = false;   // this build / driver cannot capture the search: stop trying
+                return false;
+            }
+        } catch (...) {
+            im.destroyGraph(e);
+            throw;
+        }
+        im.graphs.push_back(e);
+        g = &im.graphs.back();
+    }
+    g->lastUse = ++im.useCounter;
+    std::memcpy(g->host, x, (size_t)n * d * 4);
+    cudaCheck(cudaGraphLaunch(g->exec, st), "search: graph launch");
+    cudaCheck(cudaStreamSynchronize(st), "search: synchronize");
+    std::memcpy(distances, g->host + g->hostDistOff, (size_t)n * k * 4);
+    std::memcpy(labels, g->host + g->hostLabOff, (size_t)n * k * 8);
+    const int32_t word = *reinterpret_cast<const int32_t*>(g->host + g->hostStatusOff);
+    im.lastStatus = word;
+    if (word != 0) throwDeviceStatus(word, "search");
+    return true;
 }
 
 void B200IndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::idx_t k,
@@ -514,11 +840,11 @@ void B200IndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::i
     checkSearchArgs(n, x, k, distances, labels, ntotal);
     if (n == 0) return;
     const int64_t batch = k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch;
-    FAISS_THROW_IF_NOT_MSG(n <= batch, "searchDeviceEnqueue: too many queries for one launch");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_UNSUPPORTED, n <= batch, "searchDeviceEnqueue: too many queries for one launch");
     DeviceGuard g(impl_->res->getDevice());
     const size_t scratchBytes =
             b200f_search_scratch_bytes(n, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
-    FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "searchDeviceEnqueue: cannot plan this shape");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, scratchBytes > 0, "searchDeviceEnqueue: cannot plan this shape");
     uint8_t* region = static_cast<uint8_t*>(impl_->res->getScratch(align256(scratchBytes)));
     B200FSearchArgs a;
     impl_->fillArgs(a, ntotal);
@@ -540,8 +866,7 @@ void B200IndexFlat::synchronize() const {
     cudaCheck(cudaStreamSynchronize(st), "synchronize");
     if (impl_->hostStatus[0] != 0) {
         impl_->lastStatus = impl_->hostStatus[0];
-        throw std::runtime_error("faiss-b200: search kernel reported device status " +
-                                 std::to_string(impl_->hostStatus[0]));
+        throwDeviceStatus(impl_->hostStatus[0], "search");
     }
 }
 
@@ -570,9 +895,16 @@ struct B200SearchToken::Impl {
             int prev = -1;
             (void)cudaGetDevice(&prev);
             (void)cudaSetDevice(res->getDevice());
-            if (!finished && (region || status || host))
-                (void)cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(res->getDefaultStream()));
-            if (done) (void)cudaEventDestroy(done);
+            if (!finished && (region || status || host)) {
+                // dropped before its work was waited for: everything of this token is in front of `done`
+                if (!done || cudaEventSynchronize(done) != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    (void)cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(res->getDefaultStream()));
+                    (void)cudaStreamSynchronize(
+                            reinterpret_cast<cudaStream_t>(res->getAuxStream(B200Resources::kDownloadStream)));
+                }
+            }
+            if (done) res->releaseEvent(reinterpret_cast<EventHandle>(done));
             if (region) res->releaseDeviceTemp(region);
             if (status) res->releaseDeviceTemp(status);
             if (host) res->releasePinnedTemp(host);
@@ -608,7 +940,7 @@ B200SearchToken::~B200SearchToken() {
 }
 
 void B200SearchToken::wait() {
-    FAISS_THROW_IF_NOT_MSG(impl_ != nullptr, "wait() on a moved-from search token");  // :50
+    B200_THROW_ARG_IF_NOT(B200F_ERR_STATE, impl_ != nullptr, "wait() on a moved-from search token");  // :50
     if (impl_->waited) return;
     impl_->waited = true;
     if (impl_->done) {
@@ -624,12 +956,12 @@ void B200SearchToken::wait() {
         for (int b = 0; b < impl_->nbatches; b++) bad |= hs[4 * b];
         impl_->release();
         if (bad)
-            throw std::runtime_error("faiss-b200: async search reported device status " + std::to_string(bad));
+            throwDeviceStatus(bad, "async search");
     }
 }
 
 bool B200SearchToken::isReady() const {
-    FAISS_THROW_IF_NOT_MSG(impl_ != nullptr, "isReady() on a moved-from search token");  // :75
+    B200_THROW_ARG_IF_NOT(B200F_ERR_STATE, impl_ != nullptr, "isReady() on a moved-from search token");  // :75
     if (impl_->waited || !impl_->done) return true;
     cudaError_t e = cudaEventQuery(impl_->done);
     if (e == cudaSuccess) return true;
@@ -664,7 +996,7 @@ B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss
     t->nbatches = (int)((n + batch - 1) / batch);
     const size_t scratchBytes =
             b200f_search_scratch_bytes(batch, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
-    FAISS_THROW_IF_NOT_MSG(scratchBytes > 0, "searchAsync: cannot plan this shape");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, scratchBytes > 0, "searchAsync: cannot plan this shape");
     // per-call buffers: the token owns them (src/MetalIndexFlat.mm:441-476)
     CallLayout L = makeLayout(n, batch, d, k, !qOnDevice, n, true, scratchBytes);
     t->region = impl_->res->acquireDeviceTemp(L.total);
@@ -679,16 +1011,28 @@ B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss
     t->hostStatusOff = hoff;
     hoff += align256((size_t)t->nbatches * 16);
     t->host = static_cast<uint8_t*>(impl_->res->acquirePinnedTemp(hoff));
-    if (!t->host) throw std::runtime_error("faiss-b200: pinned allocation failed");
+    if (!t->host) throw B200RuntimeError(B200F_ERR_OOM, "faiss-b200: pinned allocation failed");
     uint8_t* region = static_cast<uint8_t*>(t->region);
 
+    // Three streams: the queries go up on the upload stream, the kernels run on the search
+    // stream, the results come down on the download stream.  The tokens' kernels still run one
+    // after the other, but the copies of a token overlap the kernels of its neighbours:
+    // H2D(q[i+1]) | search(q[i]) | D2H(r[i-1]).  Each token has its own buffers, so only the
+    // three hand-overs of one token need ordering (events).
+    cudaStream_t up = reinterpret_cast<cudaStream_t>(impl_->res->getAuxStream(B200Resources::kUploadStream));
+    cudaStream_t down = reinterpret_cast<cudaStream_t>(impl_->res->getAuxStream(B200Resources::kDownloadStream));
+    t->done = reinterpret_cast<cudaEvent_t>(impl_->res->acquireEvent());
     const float* dqAll = x;
     if (!qOnDevice) {
         // the caller's array is only read during this call
         std::memcpy(t->host + hostQOff, x, (size_t)n * d * 4);
         cudaCheck(cudaMemcpyAsync(region + L.offQueries, t->host + hostQOff, (size_t)n * d * 4,
-                                  cudaMemcpyHostToDevice, st),
+                                  cudaMemcpyHostToDevice, up),
                   "searchAsync: host to device copy of queries");
+        if (up != st) {
+            cudaCheck(cudaEventRecord(t->done, up), "searchAsync: event record");
+            cudaCheck(cudaStreamWaitEvent(st, t->done, 0), "searchAsync: stream wait");
+        }
         dqAll = reinterpret_cast<const float*>(region + L.offQueries);
     }
     float* dDistAll = t->distOnDevice ? distances : reinterpret_cast<float*>(region + L.offDist);
@@ -709,19 +1053,22 @@ B200SearchToken B200IndexFlat::searchAsync(faiss::idx_t n, const float* x, faiss
         a.status = t->status + 4 * b;
         abiCheck(b200f_search(&a), "searchAsync");
     }
+    if (down != st) {
+        cudaCheck(cudaEventRecord(t->done, st), "searchAsync: event record");
+        cudaCheck(cudaStreamWaitEvent(down, t->done, 0), "searchAsync: stream wait");
+    }
     if (!t->distOnDevice)
         cudaCheck(cudaMemcpyAsync(t->host + t->hostDistOff, dDistAll, (size_t)n * k * 4,
-                                  cudaMemcpyDeviceToHost, st),
+                                  cudaMemcpyDeviceToHost, down),
                   "searchAsync: distances copy");
     if (!t->labelsOnDevice)
         cudaCheck(cudaMemcpyAsync(t->host + t->hostLabOff, dLabAll, (size_t)n * k * 8,
-                                  cudaMemcpyDeviceToHost, st),
+                                  cudaMemcpyDeviceToHost, down),
                   "searchAsync: labels copy");
     cudaCheck(cudaMemcpyAsync(t->host + t->hostStatusOff, t->status, (size_t)t->nbatches * 16,
-                              cudaMemcpyDeviceToHost, st),
+                              cudaMemcpyDeviceToHost, down),
               "searchAsync: status copy");
-    cudaCheck(cudaEventCreateWithFlags(&t->done, cudaEventDisableTiming), "event create");
-    cudaCheck(cudaEventRecord(t->done, st), "event record");
+    cudaCheck(cudaEventRecord(t->done, down), "event record");
     return B200SearchToken(std::move(t));
 }
 

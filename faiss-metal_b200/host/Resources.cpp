@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "../../include/b200_flat.h"
+#include "../include/faiss-b200/B200Exception.h"
 #include "../include/faiss-b200/StandardB200Resources.h"
 
 namespace faiss_b200 {
@@ -21,7 +22,7 @@ void check(cudaError_t e, const char* what) {
     if (e != cudaSuccess) {
         std::string msg = std::string("faiss-b200: ") + what + ": " + cudaGetErrorString(e);
         (void)cudaGetLastError();
-        throw std::runtime_error(msg);
+        throw B200RuntimeError(e == cudaErrorMemoryAllocation ? B200F_ERR_OOM : B200F_ERR_CUDA, msg);
     }
 }
 
@@ -52,12 +53,21 @@ void free_pinned(void* ptr) {
     if (ptr) (void)cudaFreeHost(ptr);
 }
 
+EventHandle B200Resources::acquireEvent() {
+    cudaEvent_t ev = nullptr;
+    check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+    return ev;
+}
+
+void B200Resources::releaseEvent(EventHandle ev) {
+    if (ev) (void)cudaEventDestroy(ev);
+}
+
 B200DeviceCapabilities queryDeviceCapabilities(int device) {
     B200FCaps c;
     int rc = b200f_device_caps(device, &c);
     if (rc != B200F_OK)
-        throw std::runtime_error(std::string("faiss-b200: cannot query device: ") +
-                                 b200f_status_string(rc));
+        throw B200RuntimeError(rc, std::string("faiss-b200: cannot query device: ") + b200f_status_string(rc));
     B200DeviceCapabilities caps;
     caps.device = c.device;
     caps.ccMajor = c.cc_major;
@@ -168,6 +178,9 @@ class BlockPool {
 struct StandardB200Resources::Impl {
     int device = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t aux[2] = {nullptr, nullptr};
+    std::mutex evMu;
+    std::vector<cudaEvent_t> idleEvents;
     B200DeviceCapabilities caps;
     void* scratch = nullptr;
     size_t scratchBytes = 0;
@@ -180,18 +193,21 @@ StandardB200Resources::StandardB200Resources(int device) : impl_(new Impl) {
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
         (void)cudaGetLastError();
-        throw std::runtime_error(
-                "faiss-b200: no CUDA device available (this backend has no CPU fallback)");
+        throw B200RuntimeError(B200F_ERR_NO_DEVICE,
+                               "faiss-b200: no CUDA device available (this backend has no CPU fallback)");
     }
     if (device < 0) check(cudaGetDevice(&device), "cudaGetDevice");
-    if (device >= count) throw std::runtime_error("faiss-b200: device ordinal out of range");
+    if (device >= count)
+        throw B200RuntimeError(B200F_ERR_NO_DEVICE, "faiss-b200: device ordinal out of range");
     impl_->device = device;
     impl_->caps = queryDeviceCapabilities(device);
     if (!impl_->caps.supported)
-        throw std::runtime_error("faiss-b200: device is not sm_100 (" + impl_->caps.name +
-                                 "); kernels are built for sm_100a only");
+        throw B200RuntimeError(B200F_ERR_NO_DEVICE, "faiss-b200: device is not sm_100 (" + impl_->caps.name +
+                                                            "); kernels are built for sm_100a only");
     DeviceGuard g(device);
     check(cudaStreamCreateWithFlags(&impl_->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    for (int i = 0; i < 2; i++)
+        check(cudaStreamCreateWithFlags(&impl_->aux[i], cudaStreamNonBlocking), "cudaStreamCreate");
 }
 
 StandardB200Resources::~StandardB200Resources() {
@@ -199,10 +215,16 @@ StandardB200Resources::~StandardB200Resources() {
     int prev = -1;
     (void)cudaGetDevice(&prev);
     (void)cudaSetDevice(impl_->device);
+    for (int i = 0; i < 2; i++)
+        if (impl_->aux[i]) {
+            (void)cudaStreamSynchronize(impl_->aux[i]);
+            (void)cudaStreamDestroy(impl_->aux[i]);
+        }
     if (impl_->stream) {
         (void)cudaStreamSynchronize(impl_->stream);
         (void)cudaStreamDestroy(impl_->stream);
     }
+    for (cudaEvent_t ev : impl_->idleEvents) (void)cudaEventDestroy(ev);
     if (impl_->scratch) (void)cudaFree(impl_->scratch);
     if (impl_->pinned) (void)cudaFreeHost(impl_->pinned);
     impl_->devicePool.clear([](void* p) { (void)cudaFree(p); });
@@ -214,6 +236,43 @@ StandardB200Resources::~StandardB200Resources() {
 const B200DeviceCapabilities& StandardB200Resources::getCapabilities() const { return impl_->caps; }
 int StandardB200Resources::getDevice() const { return impl_->device; }
 StreamHandle StandardB200Resources::getDefaultStream() const { return impl_->stream; }
+StreamHandle StandardB200Resources::getAuxStream(int which) const {
+    return (which == kUploadStream || which == kDownloadStream) ? impl_->aux[which] : impl_->stream;
+}
+
+EventHandle StandardB200Resources::acquireEvent() {
+    {
+        std::lock_guard<std::mutex> g(impl_->evMu);
+        if (!impl_->idleEvents.empty()) {
+            cudaEvent_t ev = impl_->idleEvents.back();
+            impl_->idleEvents.pop_back();
+            return ev;
+        }
+    }
+    DeviceGuard g(impl_->device);
+    cudaEvent_t ev = nullptr;
+    check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+    return ev;
+}
+
+void StandardB200Resources::releaseEvent(EventHandle ev) {
+    if (!ev) return;
+    std::lock_guard<std::mutex> g(impl_->evMu);
+    if (impl_->idleEvents.size() < 64) {
+        impl_->idleEvents.push_back(ev);
+        return;
+    }
+    (void)cudaEventDestroy(ev);
+}
+
+void StandardB200Resources::waitStream(StreamHandle producer) {
+    DeviceGuard g(impl_->device);
+    cudaEvent_t ev = acquireEvent();
+    cudaError_t e = cudaEventRecord(ev, producer);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(impl_->stream, ev, 0);
+    releaseEvent(ev);   // the wait has captured the record; the event may be recorded again
+    check(e, "waitStream");
+}
 
 void* StandardB200Resources::allocBuffer(size_t size) {
     DeviceGuard g(impl_->device);
@@ -221,8 +280,9 @@ void* StandardB200Resources::allocBuffer(size_t size) {
     cudaError_t e = cudaMalloc(&p, size ? size : 256);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
-        throw std::runtime_error("faiss-b200: failed to allocate device buffer of " +
-                                 std::to_string(size) + " bytes: " + cudaGetErrorString(e));
+        throw B200RuntimeError(e == cudaErrorMemoryAllocation ? B200F_ERR_OOM : B200F_ERR_CUDA,
+                               "faiss-b200: failed to allocate device buffer of " + std::to_string(size) +
+                                       " bytes: " + cudaGetErrorString(e));
     }
     return p;
 }
@@ -244,8 +304,8 @@ void* StandardB200Resources::acquireDeviceTemp(size_t size) {
         return q;
     });
     if (!p)
-        throw std::runtime_error("faiss-b200: failed to allocate device buffer of " + std::to_string(size) +
-                                 " bytes");
+        throw B200RuntimeError(B200F_ERR_OOM,
+                               "faiss-b200: failed to allocate device buffer of " + std::to_string(size) + " bytes");
     return p;
 }
 

@@ -33,35 +33,23 @@ int fail(int code, const std::string& msg) {
     return code;
 }
 
-int classify(const std::string& msg) {
-    if (msg.find("out of range") != std::string::npos || msg.find("outside [0") != std::string::npos)
-        return B200F_ERR_RANGE;
-    if (msg.find("exceeds the maximum") != std::string::npos || msg.find("2^31-1") != std::string::npos)
-        return B200F_ERR_UNSUPPORTED;
-    if (msg.find("moved-from") != std::string::npos) return B200F_ERR_STATE;
-    return B200F_ERR_BAD_ARG;
-}
-
+// Every exception the host layer throws carries its status code (B200Exception.h); the
+// bare base classes can only come from outside it (a user-supplied resources object, the
+// FAISS headers) and map to the generic code of their kind.
 #define B200F_GUARD_BEGIN try {
 #define B200F_GUARD_END                                                        \
     }                                                                          \
+    catch (const B200ArgumentError& e) {                                       \
+        return fail(e.status(), e.what());                                     \
+    }                                                                          \
+    catch (const B200RuntimeError& e) {                                        \
+        return fail(e.status(), e.what());                                     \
+    }                                                                          \
     catch (const faiss::FaissException& e) {                                   \
-        return fail(classify(e.what()), e.what());                             \
+        return fail(B200F_ERR_BAD_ARG, e.what());                              \
     }                                                                          \
     catch (const std::bad_alloc& e) {                                          \
         return fail(B200F_ERR_OOM, e.what());                                  \
-    }                                                                          \
-    catch (const std::runtime_error& e) {                                      \
-        std::string m = e.what();                                              \
-        int code = B200F_ERR_CUDA;                                             \
-        if (m.find("no CUDA device") != std::string::npos ||                   \
-            m.find("not sm_100") != std::string::npos)                         \
-            code = B200F_ERR_NO_DEVICE;                                        \
-        else if (m.find("allocat") != std::string::npos)                       \
-            code = B200F_ERR_OOM;                                              \
-        else if (m.find("device status") != std::string::npos)                 \
-            code = B200F_ERR_DEVICE_WAIT;                                      \
-        return fail(code, m);                                                  \
     }                                                                          \
     catch (const std::exception& e) {                                          \
         return fail(B200F_ERR_CUDA, e.what());                                 \
@@ -75,6 +63,24 @@ int classify(const std::string& msg) {
 extern "C" {
 
 const char* b200f_last_error(void) { return g_last_error.c_str(); }
+
+int b200f_debug_raise(int status) {
+    B200F_GUARD_BEGIN
+    switch (status) {
+        case B200F_OK: return B200F_OK;
+        case B200F_ERR_BAD_ARG:
+        case B200F_ERR_UNSUPPORTED:
+        case B200F_ERR_RANGE:
+        case B200F_ERR_STATE:
+            throw B200ArgumentError(status, std::string("raised for the test: ") + b200f_status_string(status));
+        case -1: throw faiss::FaissException("a bare FaissException");
+        case -2: throw std::runtime_error("a bare runtime_error");
+        case -3: throw std::bad_alloc();
+        default:
+            throw B200RuntimeError(status, std::string("raised for the test: ") + b200f_status_string(status));
+    }
+    B200F_GUARD_END
+}
 
 int b200f_resources_create(int device, B200FResources** out) {
     if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");
@@ -93,6 +99,14 @@ int b200f_resources_device(const B200FResources* res) { return res ? res->res->g
 
 void* b200f_resources_stream(const B200FResources* res) {
     return res ? static_cast<void*>(res->res->getDefaultStream()) : nullptr;
+}
+
+int b200f_resources_wait_stream(B200FResources* res, void* producer_stream) {
+    if (!res) return fail(B200F_ERR_BAD_ARG, "null resources");
+    B200F_GUARD_BEGIN
+    res->res->waitStream(static_cast<StreamHandle>(producer_stream));
+    return B200F_OK;
+    B200F_GUARD_END
 }
 
 size_t b200f_resources_scratch_bytes(const B200FResources* res) {
@@ -237,8 +251,26 @@ int b200f_index_set_path(B200FIndex* index, int path) {
 
 int b200f_index_set_label_base(B200FIndex* index, int64_t base) {
     if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
     index->index->setLabelBase(base);
     return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_set_growth_mode(B200FIndex* index, int mode) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->setGrowthMode(mode);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_set_use_graphs(B200FIndex* index, int on) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->setUseGraphs(on != 0);
+    return B200F_OK;
+    B200F_GUARD_END
 }
 
 const void* b200f_index_device_rows(const B200FIndex* index) {
@@ -247,6 +279,14 @@ const void* b200f_index_device_rows(const B200FIndex* index) {
 
 int b200f_index_last_device_status(const B200FIndex* index) {
     return index ? index->index->lastDeviceStatus() : -1;
+}
+
+int b200f_index_debug_wait_expiry(B200FIndex* index, int64_t limit_cycles) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->debugWaitExpiry(limit_cycles);
+    return B200F_OK;
+    B200F_GUARD_END
 }
 
 }  // extern "C"

@@ -83,6 +83,13 @@ class B200IndexFlat : public faiss::Index {
     // --- additions needed by a discrete, multi-GPU device ---
     /// Make room for n vectors in total without the x2 growth copies.
     void reserve(faiss::idx_t n);
+    /// 0: grow in place (address range reserved once, memory mapped behind the rows; default
+    /// where the driver supports it), 1: the reference's allocate-copy-free growth
+    /// (src/MetalIndexFlat.mm:196-222).  Only before the first add / reserve.
+    void setGrowthMode(int mode);
+    /// Searches of at most 8 queries with host buffers are replayed from a CUDA graph captured
+    /// on their second occurrence (default on).  Off: every search is enqueued call by call.
+    void setUseGraphs(bool on);
     /// Rows [first, first + n) as fp32 into out (host or device pointer).
     void reconstruct_n(faiss::idx_t first, faiss::idx_t n, float* out) const;
     /// Labels returned by search are local row number + this base (row shards).
@@ -99,10 +106,17 @@ class B200IndexFlat : public faiss::Index {
     void synchronize() const;
     /// Device status word of the most recent synchronous search (0 = fine).
     int lastDeviceStatus() const;
+    /// Test aid: queues a one-CTA kernel that waits, with the library's bounded-wait helper and a
+    /// limit of `limitCycles` SM clocks, on a barrier nothing signals; it gives up, marks this
+    /// index's status word and returns.  The next synchronize() then throws the device-wait
+    /// error; the search after that clears the word and runs normally.
+    void debugWaitExpiry(int64_t limitCycles);
 
    private:
     struct Impl;
     std::unique_ptr<Impl> impl_;
+    bool searchFromGraph(faiss::idx_t n, const float* x, faiss::idx_t k, float* distances,
+                         faiss::idx_t* labels) const;
 };
 
 /// CPU IndexFlat -> GPU index (index_cpu_to_metal, MetalIndexFlat.h:114).  The

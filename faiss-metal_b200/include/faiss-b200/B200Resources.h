@@ -9,10 +9,12 @@
 #include "B200DeviceCapabilities.h"
 
 struct CUstream_st;
+struct CUevent_st;
 
 namespace faiss_b200 {
 
 typedef CUstream_st* StreamHandle;  // == cudaStream_t
+typedef CUevent_st* EventHandle;    // == cudaEvent_t
 
 /// Pinned host memory suitable for asynchronous copies; the analogue of the
 /// reference's alloc_aligned / free_aligned (MetalResources.h:20-34).
@@ -27,6 +29,19 @@ class B200Resources {
     virtual const B200DeviceCapabilities& getCapabilities() const = 0;
     virtual int getDevice() const = 0;
     virtual StreamHandle getDefaultStream() const = 0;
+
+    /// Side streams for copies that should overlap the kernels on the default stream:
+    /// 0 = host-to-device (queries of the next search, the next chunk of an add),
+    /// 1 = device-to-host (results of the previous search, reconstructed rows).  Work on them
+    /// is ordered against the default stream with events only.  An implementation without side
+    /// streams returns the default stream: everything then serialises, results are the same.
+    enum { kUploadStream = 0, kDownloadStream = 1 };
+    virtual StreamHandle getAuxStream(int /*which*/) const { return getDefaultStream(); }
+
+    /// Timing-disabled events for the ordering above and for search tokens.  Recycled by the
+    /// standard implementation, so that an asynchronous search creates nothing per call.
+    virtual EventHandle acquireEvent();
+    virtual void releaseEvent(EventHandle ev);
 
     /// Device buffer (throws std::runtime_error on failure,
     /// src/StandardMetalResources.mm:68-76).

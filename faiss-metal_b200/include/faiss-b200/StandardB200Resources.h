@@ -21,6 +21,12 @@ class StandardB200Resources : public B200Resources {
     void* getScratch(size_t bytes) override;
     size_t getScratchSize() const override;
     void* getPinnedStaging(size_t bytes) override;
+    StreamHandle getAuxStream(int which) const override;
+    EventHandle acquireEvent() override;
+    void releaseEvent(EventHandle ev) override;
+    /// Makes the default stream wait for everything queued so far on `producer` (a stream of
+    /// the same device; nullptr = the legacy default stream).  No host synchronisation.
+    void waitStream(StreamHandle producer);
 
     /// Recycling pools (at most 8 idle blocks each; a request takes the smallest idle block of
     /// at least its size and at most twice its size, else allocates).

@@ -36,6 +36,25 @@ def _ptr(a):
     raise TypeError("expected numpy array or torch tensor")
 
 
+def _dtype_name(a) -> str:
+    return str(a.dtype).replace("torch.", "")
+
+
+def _check(a, what: str, dtype: str, shape) -> None:
+    """The C side reads / writes rows * cols * itemsize bytes behind the pointer: a wrong dtype
+    or shape would be an out-of-bounds access there, so it is refused here."""
+    if not (isinstance(a, np.ndarray) or hasattr(a, "data_ptr")):
+        raise TypeError("%s: expected numpy array or torch tensor" % what)
+    if _dtype_name(a) != dtype:
+        raise ValueError("%s: expected dtype %s, got %s" % (what, dtype, _dtype_name(a)))
+    if tuple(int(v) for v in a.shape) != tuple(shape):
+        raise ValueError("%s: expected shape %s, got %s" % (what, tuple(shape), tuple(a.shape)))
+
+
+def _is_cuda(a) -> bool:
+    return hasattr(a, "is_cuda") and bool(a.is_cuda)
+
+
 class StandardB200Resources:
     """StandardMetalResources (include/faiss-metal/StandardMetalResources.h:9-32)."""
 
@@ -55,6 +74,21 @@ class StandardB200Resources:
     @property
     def scratch_bytes(self) -> int:
         return abi.lib().b200f_resources_scratch_bytes(self._h)
+
+    def wait_stream(self, producer_stream: int = 0):
+        """Orders the resources' stream after everything queued so far on `producer_stream`
+        (a cudaStream_t as an integer; 0 = the legacy default stream)."""
+        abi.check(abi.lib().b200f_resources_wait_stream(self._h, ctypes.c_void_p(producer_stream)), "wait_stream")
+
+    def _order_after_torch(self, *arrays):
+        """The library's stream does not synchronise with torch's streams: a CUDA tensor that
+        torch has just produced (or will overwrite) must be ordered explicitly.  Makes the
+        resources' stream wait for torch's current stream when any argument is a CUDA tensor."""
+        if any(_is_cuda(a) for a in arrays if a is not None):
+            import torch
+            cur = torch.cuda.current_stream().cuda_stream
+            if cur != self.stream:
+                self.wait_stream(cur)
 
     def close(self):
         if getattr(self, "_h", None):
@@ -118,9 +152,11 @@ class B200IndexFlat:
         return abi.lib().b200f_index_ntotal(self._h)
 
     def add(self, x):
+        if len(x.shape) != 2:
+            raise ValueError("add: expected a 2-d array [n, %d]" % self.d)
         n = int(x.shape[0])
-        if n and int(x.shape[1]) != self.d:
-            raise ValueError("add: expected [n, %d]" % self.d)
+        _check(x, "add: x", "float32", (n, self.d))
+        self.resources._order_after_torch(x)
         abi.check(abi.lib().b200f_index_add(self._h, n, _ptr(x) if n else None), "add")
 
     def reserve(self, n: int):
@@ -129,7 +165,7 @@ class B200IndexFlat:
     def search(self, x, k: int, distances=None, labels=None):
         """Returns (distances float32 [n,k], labels int64 [n,k]) in the memory space of x
         unless output arrays are given."""
-        n = int(x.shape[0])
+        n = self._check_queries(x, "search")
         if distances is None or labels is None:
             if isinstance(x, np.ndarray):
                 distances = np.empty((n, k), dtype=np.float32)
@@ -138,13 +174,31 @@ class B200IndexFlat:
                 import torch
                 distances = torch.empty((n, k), dtype=torch.float32, device=x.device)
                 labels = torch.empty((n, k), dtype=torch.int64, device=x.device)
+        self._check_outputs(n, k, distances, labels, "search")
+        self.resources._order_after_torch(x, distances, labels)
         abi.check(abi.lib().b200f_index_search(self._h, n, _ptr(x) if n else None, int(k),
                                                 _ptr(distances), _ptr(labels)), "search")
         return distances, labels
 
-    def search_enqueue(self, x, k: int, distances, labels):
-        """Device tensors only; queues the search on the resources' stream without waiting."""
+    def _check_queries(self, x, what: str) -> int:
+        if len(x.shape) != 2:
+            raise ValueError("%s: expected a 2-d array [n, %d]" % (what, self.d))
         n = int(x.shape[0])
+        _check(x, what + ": x", "float32", (n, self.d))
+        return n
+
+    def _check_outputs(self, n: int, k: int, distances, labels, what: str) -> None:
+        if int(k) >= 1:   # k < 1 is reported by the library with its own status code
+            _check(distances, what + ": distances", "float32", (n, int(k)))
+            _check(labels, what + ": labels", "int64", (n, int(k)))
+
+    def search_enqueue(self, x, k: int, distances, labels):
+        """Device tensors only; queues the search on the resources' stream without waiting.
+        The inputs are ordered after torch's current stream; the OUTPUTS are complete only on
+        the resources' stream (call synchronize(), or make your stream wait on that one)."""
+        n = self._check_queries(x, "search_enqueue")
+        self._check_outputs(n, k, distances, labels, "search_enqueue")
+        self.resources._order_after_torch(x, distances, labels)
         abi.check(abi.lib().b200f_index_search_enqueue(self._h, n, _ptr(x) if n else None, int(k),
                                                         _ptr(distances), _ptr(labels)), "search_enqueue")
 
@@ -152,7 +206,9 @@ class B200IndexFlat:
         abi.check(abi.lib().b200f_index_synchronize(self._h), "synchronize")
 
     def search_async(self, x, k: int, distances, labels) -> SearchToken:
-        n = int(x.shape[0])
+        n = self._check_queries(x, "search_async")
+        self._check_outputs(n, k, distances, labels, "search_async")
+        self.resources._order_after_torch(x, distances, labels)
         t = ctypes.c_void_p()
         abi.check(abi.lib().b200f_index_search_async(self._h, n, _ptr(x) if n else None, int(k),
                                                       _ptr(distances), _ptr(labels), ctypes.byref(t)),
@@ -170,12 +226,21 @@ class B200IndexFlat:
     def reconstruct_n(self, first: int, n: int, out=None):
         if out is None:
             out = np.empty((n, self.d), dtype=np.float32)
+        _check(out, "reconstruct_n: out", "float32", (int(n), self.d))
+        self.resources._order_after_torch(out)
         abi.check(abi.lib().b200f_index_reconstruct_n(self._h, int(first), int(n), _ptr(out)), "reconstruct_n")
         return out
 
     # -- extras ---------------------------------------------------------------------------
     def set_path(self, path: int):
         abi.check(abi.lib().b200f_index_set_path(self._h, int(path)), "set_path")
+
+    def set_growth_mode(self, mode: int):
+        """0: grow in place (default where supported), 1: allocate-copy-free; empty index only."""
+        abi.check(abi.lib().b200f_index_set_growth_mode(self._h, int(mode)), "set_growth_mode")
+
+    def set_use_graphs(self, on: bool):
+        abi.check(abi.lib().b200f_index_set_use_graphs(self._h, 1 if on else 0), "set_use_graphs")
 
     def set_label_base(self, base: int):
         abi.check(abi.lib().b200f_index_set_label_base(self._h, int(base)), "set_label_base")

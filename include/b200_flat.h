@@ -49,6 +49,8 @@ extern "C" {
 #define B200F_ERR_OOM 7          /* device or pinned-host allocation failed             */
 #define B200F_ERR_RANGE 8        /* reconstruct key out of range                        */
 #define B200F_ERR_STATE 9        /* token already consumed / moved-from                 */
+#define B200F_ERR_DEVICE_CHECK 10 /* a device-side self-check failed: shared-memory base misaligned,
+                                     candidate buffer overflow, debug canary overwritten   */
 
 /* Largest k any path accepts (README.md:218-219 / src/MetalSelect.mm:65-70: 4096 on M3+). */
 #define B200F_MAX_K 4096
@@ -67,6 +69,44 @@ extern "C" {
 #define B200F_PATH_TENSOR 2  /* tcgen05 GEMM with fused top-k / select      */
 
 const char* b200f_status_string(int status);
+
+/* ---- library-wide switches (testing aids) ------------------------------- */
+/* The counterpart of MetalIndexFlat::setForceMPS (include/faiss-metal/MetalIndexFlat.h:106)
+ * one level down: which selection scheme the tensor path uses.  Results are identical in
+ * every mode; only the kernel sequence differs.  Process-wide, read by every later search.
+ * Until the setter is called the default comes from the environment variable
+ * B200F_SELECT_MODE (auto | filter | no_filter | matrix), which is read once, at the first
+ * search; nothing else in the search path reads the environment. */
+#define B200F_SELECT_AUTO 0       /* threshold filter from 2^27 (query, row) pairs, 32-entry lists below */
+#define B200F_SELECT_FILTER 1     /* threshold filter wherever the shard allows a pilot sample */
+#define B200F_SELECT_NO_FILTER 2  /* never the threshold filter                                */
+#define B200F_SELECT_MATRIX 3     /* neither filter nor lists: fused lists (k <= 32), key matrix beyond */
+int b200f_set_selection_mode(int mode);
+int b200f_get_selection_mode(void);
+/* Shape of the tensor kernel: one CTA per 128 x 256 tile, or a CTA pair per 256 x 512 tile.
+ * Default: by the number of queries (environment default B200F_GEMM_PAIR=0|1, read once). */
+#define B200F_GEMM_SHAPE_AUTO (-1)
+#define B200F_GEMM_SHAPE_SINGLE 0
+#define B200F_GEMM_SHAPE_PAIR 1
+int b200f_set_gemm_shape(int shape);
+/* Debug canaries, the stand-in for a memory checker on the scratch arena: with on != 0 every
+ * slice of a search's scratch region is followed by a 256-byte guard that is filled before the
+ * search and compared after it; a kernel that wrote past its slice sets bit 8 of status[0]
+ * (B200F_ERR_DEVICE_CHECK at the index level).  Changes b200f_search_scratch_bytes(): set it
+ * before sizing scratch, not between sizing and searching.  No counterpart in the reference. */
+int b200f_set_debug_canaries(int on);
+/* Self-test of the canary checker on a caller-provided device region (>= 4 KiB, 256-byte
+ * aligned): three guards are filled, with corrupt != 0 one word of the second guard is
+ * overwritten the way a kernel running past its slice would, and the guards are compared:
+ * status[0] gets bit 8 and status[2] = 2 exactly when corrupt != 0.  status is not cleared. */
+int b200f_debug_canary_selftest(void* scratch, size_t scratch_bytes, int corrupt, int32_t* status, void* stream);
+/* Runs the bounded-wait helper every kernel of this library waits with, on a barrier that
+ * nothing will ever signal, with a limit of limit_cycles SM clocks (about a millisecond is
+ * plenty): one CTA, the wait gives up, records bit 1 in status[0] and the kernel returns
+ * normally.  It exists so that the expiry path (status word, B200F_ERR_DEVICE_WAIT) can be
+ * exercised without a fault, trap or hang.  status: device int32[4], not cleared by the call.
+ * No counterpart in the reference. */
+int b200f_debug_wait_expiry(int32_t* status, int64_t limit_cycles, void* stream);
 
 /* ---- device capabilities ----------------------------------------------- */
 /* Replaces MetalDeviceCapabilities / queryDeviceCapabilities
@@ -244,12 +284,30 @@ typedef struct B200FToken B200FToken;         /* MetalSearchToken (include/faiss
 
 /* Message of the last failed index-level call on this thread. */
 const char* b200f_last_error(void);
+/* Throws, inside the same exception barrier every index-level call runs behind, the exception
+ * the host layer uses for `status` (-1 / -2 / -3: a bare faiss::FaissException /
+ * std::runtime_error / std::bad_alloc, as foreign code could throw) and returns what the
+ * barrier made of it.  Lets a test without a GPU see every error code come out of the typed
+ * exceptions.  The reference throws across its C++ boundary (src/MetalIndexFlat.mm:321-326). */
+int b200f_debug_raise(int status);
 
-/* StandardMetalResources() (src/StandardMetalResources.mm:17-44): device < 0 = current device. */
+/* StandardMetalResources() (src/StandardMetalResources.mm:17-44): device < 0 = current device.
+ *
+ * Stream semantics of every index-level call: the work runs on the resources' own stream
+ * (b200f_resources_stream), which does NOT synchronise with the legacy default stream or
+ * any other stream.  Host pointers need no care (the calls block until the data has been
+ * read / written, searchAsync until token wait).  DEVICE pointers handed to add / search /
+ * search_enqueue / reconstruct_n must be complete before the call: produce them on the
+ * resources' stream, or make that stream wait on an event recorded after their producer
+ * (b200f_resources_wait_stream does exactly that). */
 int b200f_resources_create(int device, B200FResources** out);
 void b200f_resources_destroy(B200FResources* res);
 int b200f_resources_device(const B200FResources* res);
 void* b200f_resources_stream(const B200FResources* res);
+/* Orders the resources' stream after everything queued so far on `producer_stream` (a
+ * cudaStream_t of the same device; NULL = the legacy default stream): an event is recorded
+ * there and the resources' stream waits for it.  No host synchronisation. */
+int b200f_resources_wait_stream(B200FResources* res, void* producer_stream);
 /* bytes currently held by the grow-only scratch arena (src/MetalIndexFlat.mm:102-142) */
 size_t b200f_resources_scratch_bytes(const B200FResources* res);
 
@@ -296,6 +354,17 @@ int b200f_index_set_path(B200FIndex* index, int path);
 /* Pre-size the storage for n rows in total (avoids the x2 growth copies of
  * src/MetalIndexFlat.mm:196-208 when the final size is known). */
 int b200f_index_reserve(B200FIndex* index, int64_t n);
+/* How the storage grows: 0 = in place (address range reserved once, memory mapped behind the
+ * rows as they are added; the default where the driver supports it), 1 = the reference's
+ * allocate-copy-free (src/MetalIndexFlat.mm:196-222).  Only on an empty index.  The default
+ * comes from the environment variable B200F_NO_VMM=1 (read once per process). */
+int b200f_index_set_growth_mode(B200FIndex* index, int mode);
+/* Searches of at most 8 queries whose three arrays are host memory are replayed from a CUDA
+ * graph (query upload, every kernel of the search, result download in one launch), captured
+ * the second time a (n, k) shape is seen and dropped whenever the index changes.  on = 0
+ * switches that off.  Replaces the per-call encode of searchAsync for the single-query
+ * stream (src/MetalIndexFlat.mm:403-490). */
+int b200f_index_set_use_graphs(B200FIndex* index, int on);
 /* Row shards: labels returned by search = local row number + base. */
 int b200f_index_set_label_base(B200FIndex* index, int64_t base);
 /* Device pointers to the stored rows / norms of the shard (used by the
@@ -304,6 +373,10 @@ int b200f_index_set_label_base(B200FIndex* index, int64_t base);
 const void* b200f_index_device_rows(const B200FIndex* index);
 /* Device-side status of the most recent search (0 = fine). */
 int b200f_index_last_device_status(const B200FIndex* index);
+/* b200f_debug_wait_expiry on the index's stream with the index's own status word: the next
+ * b200f_index_synchronize then reports B200F_ERR_DEVICE_WAIT, and the search after it runs
+ * normally (every search clears the word first).  For tests of the error path. */
+int b200f_index_debug_wait_expiry(B200FIndex* index, int64_t limit_cycles);
 
 #ifdef __cplusplus
 }

@@ -35,24 +35,17 @@ def res(fm):
 
 
 SELECT_MODES = {
-    # which optimistic selection stages of the tensor path are allowed (environment switches of
-    # the library, read at every call)
-    "filter": {"B200F_FILTER": "1"},   # threshold filter wherever the shard allows a pilot sample
-    "no_filter": {"B200F_NO_FILTER": "1"},
-    "matrix_or_fused": {"B200F_NO_FILTER": "1", "B200F_NO_LISTS": "1"},
+    # which optimistic selection stages of the tensor path are allowed (b200f_set_selection_mode)
+    "filter": 1,            # threshold filter wherever the shard allows a pilot sample
+    "no_filter": 2,
+    "matrix_or_fused": 3,
 }
 
 
 @pytest.fixture(params=list(SELECT_MODES))
-def select_mode(request):
-    import os
-    env = SELECT_MODES[request.param]
-    old = {k: os.environ.get(k) for k in ("B200F_FILTER", "B200F_NO_FILTER", "B200F_NO_LISTS")}
-    for k in old:
-        os.environ.pop(k, None)
-    os.environ.update(env)
+def select_mode(request, fm):
+    L = fm.lib()
+    old = L.b200f_get_selection_mode()
+    assert L.b200f_set_selection_mode(SELECT_MODES[request.param]) == 0
     yield request.param
-    for k, v in old.items():
-        os.environ.pop(k, None)
-        if v is not None:
-            os.environ[k] = v
+    assert L.b200f_set_selection_mode(old) == 0

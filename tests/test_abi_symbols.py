@@ -40,7 +40,7 @@ def test_search_args_layout(fm):
 
 
 def test_status_strings(fm):
-    for code in range(0, 10):
+    for code in range(0, 11):
         s = fm.status_string(code)
         assert isinstance(s, str) and s and s != "unknown status"
     assert fm.status_string(99) == "unknown status"
@@ -66,3 +66,47 @@ def test_bad_arguments_rejected_without_gpu(fm):
     assert L.b200f_merge_lists(None, None, 0, 1, 1, 1, None, None, None) == 1
     assert L.b200f_select_rows(None, 1, 10, 5, 1, 3, None, None, None, 0, None) == 1  # ld < ncols
     assert L.b200f_index_ntotal(None) == -1
+
+
+def test_every_status_code_comes_out_of_a_typed_exception(fm):
+    # the host layer throws exceptions that carry their status code; the C mirror returns the
+    # code without looking at the message
+    L = fm.lib()
+    assert L.b200f_debug_raise(0) == 0
+    for code in range(1, 11):
+        assert L.b200f_debug_raise(code) == code
+        assert fm.status_string(code) in L.b200f_last_error().decode()
+    assert L.b200f_debug_raise(-1) == fm.abi.ERR_BAD_ARG     # foreign FaissException
+    assert L.b200f_debug_raise(-2) == fm.abi.ERR_CUDA        # foreign runtime_error
+    assert L.b200f_debug_raise(-3) == fm.abi.ERR_OOM         # bad_alloc
+
+
+def test_library_switches_without_gpu(fm):
+    L = fm.lib()
+    old = L.b200f_get_selection_mode()
+    assert old in (0, 1, 2, 3)
+    for mode in (1, 2, 3, 0):
+        assert L.b200f_set_selection_mode(mode) == 0 and L.b200f_get_selection_mode() == mode
+    assert L.b200f_set_selection_mode(4) == 1 and L.b200f_set_selection_mode(-1) == 1
+    L.b200f_set_selection_mode(old)
+    assert L.b200f_set_gemm_shape(2) == 1 and L.b200f_set_gemm_shape(-1) == 0
+    # debug canaries add a guard behind every slice of the scratch region
+    plain = L.b200f_search_scratch_bytes(64, 100000, 128, 10, 2, 2)
+    assert L.b200f_set_debug_canaries(1) == 0
+    guarded = L.b200f_search_scratch_bytes(64, 100000, 128, 10, 2, 2)
+    assert L.b200f_set_debug_canaries(0) == 0
+    assert guarded > plain and (guarded - plain) % 256 == 0
+    assert L.b200f_search_scratch_bytes(64, 100000, 128, 10, 2, 2) == plain
+
+
+def test_python_mirror_validates_arrays(fm):
+    # dtype / shape errors are caught before a pointer reaches the C side
+    import numpy as np
+    from faiss_metal_b200 import index as I
+    with pytest.raises(ValueError):
+        I._check(np.zeros((3, 4), np.float64), "x", "float32", (3, 4))
+    with pytest.raises(ValueError):
+        I._check(np.zeros((3, 5), np.float32), "x", "float32", (3, 4))
+    with pytest.raises(TypeError):
+        I._check([1.0, 2.0], "x", "float32", (2,))
+    I._check(np.zeros((3, 4), np.float32), "x", "float32", (3, 4))

@@ -135,15 +135,8 @@ def test_search_async_is_ready(fm, res):
 @pytest.fixture(params=["in_place", "copying"])
 def growth_mode(request):
     # in_place: rows are mapped into a reserved address range as the index grows (no copies);
-    # copying: B200F_NO_VMM=1, plain allocations with the reference's allocate-copy-free growth
-    import os
-    old = os.environ.pop("B200F_NO_VMM", None)
-    if request.param == "copying":
-        os.environ["B200F_NO_VMM"] = "1"
-    yield request.param
-    os.environ.pop("B200F_NO_VMM", None)
-    if old is not None:
-        os.environ["B200F_NO_VMM"] = old
+    # copying: plain allocations with the reference's allocate-copy-free growth
+    return request.param
 
 
 @pytest.mark.parametrize("storage", [0, 2])
@@ -153,6 +146,7 @@ def test_growth_over_many_adds(fm, res, growth_mode, storage, metric):
     d = 40
     xb = H.uniform_pm1(5000, d, 9)
     idx = fm.B200IndexFlat(res, d, metric, storage)
+    idx.set_growth_mode(1 if growth_mode == "copying" else 0)
     base0 = None
     pos = 0
     for n in (1, 7, 1000, 30, 2500, 1462):
@@ -181,6 +175,7 @@ def test_large_growth_in_place_keeps_rows(fm, res, growth_mode):
     d = 256
     xb = H.gaussian(300_000, d, 33, scale=0.05)
     idx = fm.B200IndexFlat(res, d, O.METRIC_L2, 2)
+    idx.set_growth_mode(1 if growth_mode == "copying" else 0)
     idx.add(xb[:10])
     idx.add(xb[10:70_000])
     idx.reserve(250_000)

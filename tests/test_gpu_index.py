@@ -36,7 +36,12 @@ def test_flat_reference_cases(fm, res, path, storage, metric, nv, nq, d, k):
     D, I = idx.search(xq, k)
     H.check_against_oracle(metric, storage, path == PATH_TENSOR, xb, xq, k, D, I)
     # the reference's own assertion: top-1 labels equal CPU results (tests/test_metal_flat.mm:52-58)
-    _, ref_i, _ = O.search(metric, *H.effective_operands(storage, path == PATH_TENSOR, xb, xq), 1)
+    _, ref_i, ref_d = O.search(metric, *H.effective_operands(storage, path == PATH_TENSOR, xb, xq), min(2, nv))
+    if ref_i.shape[1] == 2:   # except where rank 1 and rank 2 are closer than fp32 accumulation noise
+        clear = np.abs(ref_d[:, 1] - ref_d[:, 0]) > 1e-4 * np.maximum(np.abs(ref_d[:, 0]), 1e-3)
+    else:
+        clear = np.ones(nq, dtype=bool)
+    assert np.array_equal(np.asarray(I)[clear, 0], ref_i[clear, 0])
     idx.close()
 
 

@@ -3,8 +3,6 @@ matrix).  All of them see the same keys (the same GEMM kernel produces them), so
 must agree bit for bit on any input; one of them (the key matrix) is also checked against the
 oracle on the smaller shapes.  Seeded random shapes: odd dimensions, partial tiles, k from 1 to
 1024, several query blocks, all storage types and both metrics."""
-import os
-
 import numpy as np
 import pytest
 
@@ -13,26 +11,17 @@ from oracle import flat_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-MODES = {
-    "filter": {"B200F_FILTER": "1"},
-    "no_filter": {"B200F_NO_FILTER": "1"},
-    "matrix_or_fused": {"B200F_NO_FILTER": "1", "B200F_NO_LISTS": "1"},
-}
-KEYS = ("B200F_FILTER", "B200F_NO_FILTER", "B200F_NO_LISTS")
+MODES = {"filter": 1, "no_filter": 2, "matrix_or_fused": 3}   # B200F_SELECT_*
 
 
-def search_in_mode(idx, xq, k, mode):
-    old = {key: os.environ.get(key) for key in KEYS}
-    for key in KEYS:
-        os.environ.pop(key, None)
-    os.environ.update(MODES[mode])
+def search_in_mode(fm, idx, xq, k, mode):
+    L = fm.lib()
+    old = L.b200f_get_selection_mode()
+    assert L.b200f_set_selection_mode(MODES[mode]) == 0
     try:
         return idx.search(xq, k)
     finally:
-        for key in KEYS:
-            os.environ.pop(key, None)
-            if old[key] is not None:
-                os.environ[key] = old[key]
+        L.b200f_set_selection_mode(old)
 
 
 def random_shapes(seed, count):
@@ -68,7 +57,7 @@ def test_selection_modes_agree(fm, res, nb, nq, d, k, storage, metric, dup):
     idx = fm.B200IndexFlat(res, d, metric, storage)
     idx.add(xb)
     idx.set_path(2)
-    results = {mode: search_in_mode(idx, xq, k, mode) for mode in MODES}
+    results = {mode: search_in_mode(fm, idx, xq, k, mode) for mode in MODES}
     D0, I0 = results["matrix_or_fused"]
     for mode in ("filter", "no_filter"):
         Dm, Im = results[mode]

@@ -294,14 +294,12 @@ def test_optimistic_selection_redoes_rows(fm, res, select_mode, storage, metric,
 
 
 @pytest.fixture
-def force_filter():
-    import os
-    old = os.environ.get("B200F_FILTER")
-    os.environ["B200F_FILTER"] = "1"
+def force_filter(fm):
+    L = fm.lib()
+    old = L.b200f_get_selection_mode()
+    assert L.b200f_set_selection_mode(fm.abi.SELECT_FILTER) == 0
     yield
-    os.environ.pop("B200F_FILTER", None)
-    if old is not None:
-        os.environ["B200F_FILTER"] = old
+    L.b200f_set_selection_mode(old)
 
 
 @pytest.mark.parametrize("k", [10, 100])

@@ -47,6 +47,7 @@ def test_noalloc_matches_regular_entry_point_twice(fm, res, storage, metric, nb,
     # two calls in a row with different shapes: the second one finds the first one's lists
     for call, (nq, k, seed) in enumerate([(4, 32, 11), (1, 10, 12), (3, 7, 13)]):
         xq = H.uniform_pm1(nq, d, seed)
+        assert fm.lib().b200f_search_scratch_bytes(nq, nb, d, k, storage, 1) <= fm.lib().b200f_noalloc_scratch_capacity()
         want_d, want_l = _search(fm, st, xq, metric, k, noalloc=False)
         got_d, got_l = _search(fm, st, xq, metric, k, noalloc=True)
         assert np.array_equal(got_l, want_l), call
@@ -68,3 +69,34 @@ def test_noalloc_rejects_shapes_beyond_its_scratch(fm, res):
     a.k = 33
     assert fm.lib().b200f_search_small_noalloc(ctypes.byref(a)) == 2      # k > 32: unsupported
     assert fm.lib().b200f_search_small_noalloc(None) == 1
+    a = st.args(fm, xq1, O.METRIC_L2, 10, 1, out_d, out_l)
+    a.k = 0
+    assert fm.lib().b200f_search_small_noalloc(ctypes.byref(a)) == 1      # same code as b200f_search
+    a.k = 10
+    a.nq = -1
+    assert fm.lib().b200f_search_small_noalloc(ctypes.byref(a)) == 1
+
+
+def test_noalloc_leaves_device_memory_untouched(fm, res):
+    """The property in the name: over many calls the driver's count of free device memory does
+    not move (cudaMemGetInfo), so nothing was allocated, from any pool."""
+    from test_gpu_ops import Stored
+    xb = H.uniform_pm1(40_000, 64, 3)
+    st = Stored(fm, xb, 1)
+    xq = torch.from_numpy(H.uniform_pm1(2, 64, 4)).cuda()
+    out_d = torch.empty((2, 10), dtype=torch.float32, device="cuda:0")
+    out_l = torch.empty((2, 10), dtype=torch.int64, device="cuda:0")
+    a = st.args(fm, xq, O.METRIC_L2, 10, 1, out_d, out_l)
+    a.scratch = None
+    a.scratch_bytes = 0
+    L = fm.lib()
+    for _ in range(3):   # first call on the device looks the array's address up; warm everything
+        fm.abi.check_op(L.b200f_search_small_noalloc(ctypes.byref(a)), "noalloc")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(100):
+        fm.abi.check_op(L.b200f_search_small_noalloc(ctypes.byref(a)), "noalloc")
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert int(st.status[0]) == 0
