@@ -136,6 +136,8 @@ def parse_args():
     ap.add_argument("--nq", type=int, default=0, help="override queries per step (not the headline config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-label-check", action="store_true", help="skip the full-shard oracle label check")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only (no c5 / c2 / c4 legs)")
     return ap.parse_args()
 
 
@@ -244,9 +246,144 @@ def build_shard(fm, torch, res, w, lo, hi, seed):
     return idx
 
 
+TOL_STRICT = 2e-4   # GPU against the oracle on the SAME (stored) operands: only fp32 accumulation differs
+
+
+def exact_shard_topk(fm, torch, O, w, index_local, lo, hi, xq_sel, rounds_query):
+    """The oracle over the WHOLE shard for a few queries, outside the timed region.
+
+    The stored rows are streamed back chunk by chunk (reconstruct_n: the dequantised rows the
+    kernels multiply), each chunk goes through the oracle's sgemm search for 2k candidates per
+    query, and the union of candidates is re-scored exactly in float64 from the same rows.
+    Returns (ref_d float64 [n, k], ref_i int64 [n, k] global labels, fetch) where fetch(labels)
+    gives the exact float64 score of arbitrary (query, local-or-global label) pairs of this shard.
+    """
+    import numpy as np
+    d, k, metric = w["d"], w["k"], w["metric"]
+    n = xq_sel.shape[0]
+    nb = hi - lo
+    xq_eff = O.round_storage(xq_sel, w["storage"]) if rounds_query else xq_sel
+    kk = min(2 * k, max(nb, 1))
+    chunk_rows = max(1, min(nb, (256 << 20) // (d * 4)))
+    stage = torch.empty((chunk_rows, d), dtype=torch.float32, pin_memory=True).numpy()
+    cand_key = np.empty((n, 0), dtype=np.float32)
+    cand_id = np.empty((n, 0), dtype=np.int64)
+    for r0 in range(0, nb, chunk_rows):
+        nr = min(chunk_rows, nb - r0)
+        rows = index_local.reconstruct_n(r0, nr, stage[:nr])
+        cd, ci = O.blas_search(metric, rows, xq_eff, min(kk, nr))
+        key = cd if metric == O.METRIC_L2 else -cd
+        cand_key = np.concatenate([cand_key, key], axis=1)
+        cand_id = np.concatenate([cand_id, np.where(ci >= 0, ci + r0, -1)], axis=1)
+        if cand_key.shape[1] > 8 * kk:
+            sel = np.argpartition(cand_key, kk - 1, axis=1)[:, :kk]
+            cand_key = np.take_along_axis(cand_key, sel, axis=1)
+            cand_id = np.take_along_axis(cand_id, sel, axis=1)
+    if cand_key.shape[1] > kk:
+        sel = np.argpartition(cand_key, kk - 1, axis=1)[:, :kk]
+        cand_id = np.take_along_axis(cand_id, sel, axis=1)
+
+    q64 = xq_eff.astype(np.float64)
+    # the kernel adds the exact ||q||^2 of the unrounded query to -2 q~.x + ||x||^2
+    corr = (np.einsum("ij,ij->i", xq_sel.astype(np.float64), xq_sel.astype(np.float64))
+            - np.einsum("ij,ij->i", q64, q64)) if (metric == O.METRIC_L2 and rounds_query) else np.zeros(n)
+    cache = {}
+
+    def row64(local):
+        r = cache.get(local)
+        if r is None:
+            r = index_local.reconstruct(int(local)).astype(np.float64)
+            cache[local] = r
+        return r
+
+    def fetch(labels_global):
+        out = np.full(labels_global.shape, np.inf if metric == O.METRIC_L2 else -np.inf, dtype=np.float64)
+        for qi in range(labels_global.shape[0]):
+            for j in range(labels_global.shape[1]):
+                lab = int(labels_global[qi, j])
+                if lo <= lab < hi:
+                    r = row64(lab - lo)
+                    out[qi, j] = (((q64[qi] - r) ** 2).sum() + corr[qi]) if metric == O.METRIC_L2 else (q64[qi] * r).sum()
+        return out
+
+    pad = np.inf if metric == O.METRIC_L2 else -np.inf
+    ref_d = np.full((n, k), pad, dtype=np.float64)
+    ref_i = np.full((n, k), -1, dtype=np.int64)
+    for qi in range(n):
+        ids = np.unique(cand_id[qi][cand_id[qi] >= 0])
+        if ids.size == 0:
+            continue
+        exact = np.array([(((q64[qi] - row64(i)) ** 2).sum() + corr[qi]) if metric == O.METRIC_L2
+                          else (q64[qi] * row64(i)).sum() for i in ids])
+        key = exact if metric == O.METRIC_L2 else -exact
+        order = np.lexsort((ids, key))[:k]
+        ref_i[qi, :order.size] = ids[order] + lo
+        ref_d[qi, :order.size] = exact[order]
+    return ref_d, ref_i, fetch
+
+
+def label_check(fm, torch, dist, O, w, index_local, lo, hi, rank, world, xq_host, D_host, I_host, nsample=16):
+    """Label parity at the size the step ran on: for `nsample` of the step's queries the merged
+    GPU result must equal the oracle's exact top-k over the whole database (strict tolerance:
+    same stored rows, same rounded queries; a differing label must be a proven tie).  With
+    several ranks each rank also checks its own shard's list against the oracle over its
+    shard, and rank 0 merges the ranks' exact lists on the host."""
+    import numpy as np
+    nq, k, metric = xq_host.shape[0], w["k"], w["metric"]
+    sel = np.unique(np.linspace(0, nq - 1, num=min(nsample, nq)).astype(np.int64))
+    xq_sel = np.ascontiguousarray(xq_host[sel])
+    # 16-bit rows: the tensor path and the streaming scan multiply the query rounded to the storage format
+    rounds_query = w["storage"] != 0 and (nq > 8 or (hi - lo) >= 65536)
+    t0 = time.perf_counter()
+    ref_d, ref_i, fetch = exact_shard_topk(fm, torch, O, w, index_local, lo, hi, xq_sel, rounds_query)
+    out = {"label_queries": int(sel.size), "labels_checked": int(sel.size * k), "label_tolerance": TOL_STRICT}
+    finite = np.isfinite(ref_d)
+    eps = max(1e-2 * float(np.abs(ref_d[finite]).max()) if finite.any() else 1e-6, 1e-6)
+    if world > 1:
+        # this rank's own list over its shard
+        Dl, Il = index_local.search(xq_sel, k)
+        r = O.compare_results(metric, Dl, Il, ref_d, ref_i, fetch(Il), TOL_STRICT, eps=eps)
+        local_bad = 0 if O.passed(r) else 1
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (ref_d, ref_i, local_bad, r))
+        out["shard_lists_bad"] = int(sum(g[2] for g in gathered))
+        if rank == 0:
+            d_all = np.stack([g[0] for g in gathered])
+            i_all = np.stack([g[1] for g in gathered])
+            key = d_all if metric == O.METRIC_L2 else -d_all
+            key = np.transpose(key, (1, 0, 2)).reshape(sel.size, -1)
+            ids = np.transpose(i_all, (1, 0, 2)).reshape(sel.size, -1)
+            key = np.where(ids >= 0, key, np.inf)
+            order = np.stack([np.lexsort((ids[q], key[q]))[:k] for q in range(sel.size)])
+            ref_i = np.take_along_axis(ids, order, axis=1)
+            ref_d = np.take_along_axis(np.transpose(d_all, (1, 0, 2)).reshape(sel.size, -1), order, axis=1)
+        # exact scores of the labels the merged result holds: each rank scores the labels that
+        # are rows of its shard (+/-INF elsewhere), rank 0 combines
+        share = [I_host[sel] if rank == 0 else None]
+        dist.broadcast_object_list(share, src=0)
+        box = [None] * world
+        dist.all_gather_object(box, fetch(share[0]))
+        if rank == 0:
+            true_d = np.min(np.stack(box), axis=0) if metric == O.METRIC_L2 else np.max(np.stack(box), axis=0)
+    else:
+        true_d = fetch(I_host[sel])
+    if rank == 0:
+        r = O.compare_results(metric, D_host[sel], I_host[sel], ref_d, ref_i, true_d, TOL_STRICT, eps=eps)
+        out.update({"label_diff": r["label_diff"], "label_bad": r["label_bad"], "dist_bad": r["dist"],
+                    "pad_mismatch": r["pad_mismatch"], "duplicates": r["duplicates"],
+                    "max_rel_dist_err_vs_stored_operands": r["max_rel_dist_err"],
+                    "label_check_seconds": round(time.perf_counter() - t0, 2),
+                    "label_check": "GPU top-k of %d queries against the oracle's exact top-k over all %d rows "
+                            "(stored rows read back, float64 re-score)" % (sel.size, w["nb"])})
+        if not O.passed(r) or out.get("shard_lists_bad", 0):
+            raise AssertionError("label check failed: %r" % (out,))
+    return out
+
+
 def spot_check(fm, torch, w, index_local, lo, hi, xq_host, D, I, nsample=8):
     """Outside the timed region: exact re-score (float64, from the stored rows) of the labels
-    returned for a few queries that fall in this rank's shard, order and tolerance check."""
+    returned for a few queries that fall in this rank's shard against the UNROUNDED queries:
+    the north-star distance tolerance (1e-4 FP32 storage, 2e-2 16-bit storage) and the order."""
     import numpy as np
     worst = 0.0
     checked = 0
@@ -274,28 +411,23 @@ def spot_check(fm, torch, w, index_local, lo, hi, xq_host, D, I, nsample=8):
     return {"pairs_rescored": checked, "max_rel_dist_err": worst, "tolerance": tol}
 
 
-def run_b200(args, w, rank, world, local_rank):
+def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_label_check=True):
+    """Builds the workload's index on this rank's shard, times it, checks it, frees it.
+    Returns the dict of everything measured (rank 0) or None."""
     import ctypes
 
     import numpy as np
-    import torch
-    import torch.distributed as dist
 
-    import faiss_metal_b200 as fm
-
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    peaks = load_peaks()
-    res = fm.StandardB200Resources(local_rank)
-    ext = torch.cuda.ExternalStream(res.stream, device=torch.device("cuda", local_rank))
-    lo, hi = fm.shard_range(w["nb"], rank, world)
+    fm, torch, dist, O = ctx["fm"], ctx["torch"], ctx["dist"], ctx["O"]
+    rank, world, local_rank, res, ext, peaks = (ctx[k] for k in ("rank", "world", "local_rank", "res", "ext", "peaks"))
     L = fm.lib()
+    lo, hi = fm.shard_range(w["nb"], rank, world)
+    nq, d, k = w["nq"], w["d"], w["k"]
+    root = rank == 0
 
     with torch.cuda.stream(ext):
         index = build_shard(fm, torch, res, w, lo, hi, seed=1)
         sharded = fm.ShardedIndexFlat(index, rank, world)
-        nq, d, k = w["nq"], w["d"], w["k"]
         xq_dev = torch.empty((nq, d), dtype=torch.float32, device="cuda")
         fm.abi.check_op(L.b200f_fill_synthetic(ctypes.c_void_p(xq_dev.data_ptr()), nq, d, 0, 2, w["dist"], w["scale"],
                                                ctypes.c_void_p(ext.cuda_stream)), "fill queries")
@@ -310,46 +442,45 @@ def run_b200(args, w, rank, world, local_rank):
                 dist.barrier()
             torch.cuda.synchronize()
 
-        single_batch = nq <= (16384 if k <= 32 else 1024)
+        batch = 16384 if k <= 1024 else 1024   # queries per launch of the library
 
         def step_device():
-            if single_batch:   # queued back to back on one stream, one host sync per step
-                return sharded.search_device(xq_dev, k)
-            return sharded.search(xq_dev, k)
+            # queries and results resident in HBM; every launch of a step queued back to back,
+            # one host synchronisation per step; only rank 0 merges
+            if nq <= batch:
+                return sharded.search_device(xq_dev, k, want_result=root)
+            return sharded.search(xq_dev, k, want_result=root)
 
         def step_e2e():
-            # public API with HOST buffers: H2D of the queries and D2H of the results inside
+            # the public call with HOST buffers: each rank uploads its slice of the queries, the
+            # slices are all-gathered over NVLink, rank 0 alone merges and downloads the result
             if world == 1:
                 index.search(xq_pin.numpy(), k, d_pin.numpy(), l_pin.numpy())
+            elif root:
+                sharded.search(xq_pin.numpy(), k, d_pin.numpy(), l_pin.numpy())
             else:
-                if single_batch:
-                    dd, ll = sharded.search_device(xq_dev.copy_(xq_pin, non_blocking=True), k, sync=False)
-                else:
-                    dd, ll = sharded.search(xq_dev.copy_(xq_pin, non_blocking=True), k)
-                d_pin.copy_(dd, non_blocking=True)
-                l_pin.copy_(ll, non_blocking=True)
-                index.synchronize()
+                sharded.search(xq_pin.numpy(), k, want_result=False)
 
         # ---- device-resident timing ------------------------------------------------------
         sampler = ClockSampler(local_rank)
-        if rank == 0:
+        if root:
             sampler.start()  # started before the warm-up so that its own start-up is not timed
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(max(warmup, 3)):
             step_device()
         barrier()
         L.b200f_profile_enable(1)
         L.b200f_profile_read(None, None, None, 1)
         sampler.lines.clear()
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         barrier()
         evs[0].record(ext)
-        for i in range(args.steps):
+        for i in range(steps):
             D_dev, I_dev = step_device()
             evs[i + 1].record(ext)
         barrier()
-        clocks = sampler.stop() if rank == 0 else None
+        clocks = sampler.stop() if root else None
         ms_total = evs[0].elapsed_time(evs[-1])
-        step_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+        step_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
         launches = ctypes.c_int64(0)
         main_launches = ctypes.c_int64(0)
         main_ms = ctypes.c_double(0.0)
@@ -358,28 +489,30 @@ def run_b200(args, w, rank, world, local_rank):
         t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step = float(t.item()) / args.steps
+        ms_step = float(t.item()) / steps
 
         # ---- end-to-end timing -------------------------------------------------------------
         e2e = None
-        if not args.no_e2e:
-            for _ in range(2):
+        if with_e2e:
+            for _ in range(3):
                 step_e2e()
             barrier()
             t0 = time.perf_counter()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 step_e2e()
             barrier()
             dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-            e2e_s = float(dt.item()) / args.steps
+            e2e_s = float(dt.item()) / steps
             e2e = {"value": nq / e2e_s, "unit": "queries/s", "ms_per_step": e2e_s * 1e3,
-                   "h2d_bytes_per_step": world * nq * d * 4, "d2h_bytes_per_step": world * nq * k * 12}
+                   "h2d_bytes_per_step": nq * d * 4, "d2h_bytes_per_step": nq * k * 12,
+                   "what": "index search() with pinned host buffers; each GPU uploads 1/%d of the queries, "
+                           "GPU 0 alone downloads the merged result" % world}
 
         # ---- latency distribution of a stream of single searches (small-nq workloads) ------
         latency = None
-        if nq <= 4 and not args.no_e2e:
+        if nq <= 4 and with_e2e:
             # 10,000 calls unless that would take much longer than ~25 s
             ncalls = max(1000, min(10000, int(25000.0 / max(ms_step, 0.05))))
             qbank = torch.empty((64 * nq, d), dtype=torch.float32, device="cuda")
@@ -388,60 +521,59 @@ def run_b200(args, w, rank, world, local_rank):
             ext.synchronize()
             qbank_pin = torch.empty((64 * nq, d), dtype=torch.float32, pin_memory=True)
             qbank_pin.copy_(qbank)
+            qb = qbank_pin.numpy()
             lat = []
+            lat_sampler = ClockSampler(local_rank)
+            if root:
+                lat_sampler.start()
             barrier()
             for i in range(ncalls):
                 j = (i % 64) * nq
                 t0 = time.perf_counter()
                 if world == 1:
-                    index.search(qbank_pin[j:j + nq].numpy(), k, d_pin.numpy(), l_pin.numpy())
+                    index.search(qb[j:j + nq], k, d_pin.numpy(), l_pin.numpy())
+                elif root:
+                    sharded.search(qb[j:j + nq], k, d_pin.numpy(), l_pin.numpy())
                 else:
-                    dd, ll = sharded.search_device(xq_dev.copy_(qbank_pin[j:j + nq], non_blocking=True), k, sync=False)
-                    d_pin.copy_(dd, non_blocking=True)
-                    l_pin.copy_(ll, non_blocking=True)
-                    index.synchronize()
+                    sharded.search(qb[j:j + nq], k, want_result=False)
                 lat.append((time.perf_counter() - t0) * 1e3)
             lat_t = torch.tensor(lat, dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(lat_t, op=dist.ReduceOp.MAX)   # a call ends when the slowest rank has it
-            lat_s = sorted(lat_t.cpu().tolist())
+            lat_all = lat_t.cpu().tolist()
+            lat_s = sorted(lat_all)
+            head, tail = sorted(lat_all[:500]), sorted(lat_all[-500:])
             latency = {"calls": ncalls, "p50_ms": lat_s[len(lat_s) // 2], "p99_ms": lat_s[int(len(lat_s) * 0.99)],
-                       "max_ms": lat_s[-1], "what": "host-timed search() with host buffers, one query batch per call"}
+                       "max_ms": lat_s[-1], "p50_first_500_ms": head[len(head) // 2], "p50_last_500_ms": tail[len(tail) // 2],
+                       "clocks": lat_sampler.stop() if root else None,
+                       "what": "host-timed search() with host buffers, one query batch per call"}
             qbank = qbank_pin = lat_t = None
-            # restore the benchmark queries for the checks below
-            fm.abi.check_op(L.b200f_fill_synthetic(ctypes.c_void_p(xq_dev.data_ptr()), nq, d, 0, 2, w["dist"],
-                                                   w["scale"], ctypes.c_void_p(ext.cuda_stream)), "fill queries")
-            ext.synchronize()
-            D_dev, I_dev = step_device()
-            step_e2e()
+            step_e2e()   # leaves the benchmark queries' result in the pinned arrays again
 
         # ---- checks outside the timed region ---------------------------------------------
-        D_host = D_dev.cpu().numpy()
-        I_host = I_dev.cpu().numpy()
-        check = spot_check(fm, torch, w, index, lo, hi, xq_pin.numpy(), D_host, I_host)
-        if not args.no_e2e:
-            assert np.array_equal(l_pin.numpy(), I_host), "end-to-end labels differ from device-resident labels"
+        D_host = D_dev.cpu().numpy() if root else None
+        I_host = I_dev.cpu().numpy() if root else None
+        check = None
+        if root:
+            check = spot_check(fm, torch, w, index, lo, hi, xq_pin.numpy(), D_host, I_host)
+            if with_e2e:
+                assert np.array_equal(l_pin.numpy(), I_host), "end-to-end labels differ from device-resident labels"
+        if with_label_check:
+            lc = label_check(fm, torch, dist, O, w, index, lo, hi, rank, world, xq_pin.numpy(), D_host, I_host)
+            if root:
+                check.update(lc)
 
     # every torch tensor that lived on the library's stream must be released before that stream
     # is destroyed (torch records an event on the allocation stream when it frees a block)
-    D_dev = I_dev = xq_dev = xq_pin = d_pin = l_pin = t = dt = sharded = evs = ev_unused = None  # noqa: F841
+    D_dev = I_dev = xq_dev = xq_pin = d_pin = l_pin = t = evs = None  # noqa: F841
+    sharded.close()
+    index.close()
     import gc
     gc.collect()
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
-
-    def teardown():
-        # ordered: index, resources, then the process group
-        torch.cuda.synchronize()
-        index.close()
-        res.close()
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-
-    if rank != 0:
-        teardown()
-        return
+    if not root:
+        return None
 
     nb_local = hi - lo
     # DRAM bytes of the dominant kernel from ncu captures on smaller shards of the same workload
@@ -450,9 +582,9 @@ def run_b200(args, w, rank, world, local_rank):
     #   c3: filter-mode gemm_topk_kernel, 1,250,000 rows: 4,694.8 MB + 25.2 MB
     #   c5: scan_mma_kernel, 8,000,000 rows: 2,176 MB + 3.7 MB
     traffic = None
-    if args.workload == "c3" and w["nq"] == WORKLOADS["c3"]["nq"]:
+    if name == "c3" and w["nq"] == WORKLOADS["c3"]["nq"]:
         traffic = (4694.8e6 + 25.2e6) / 1_250_000 * nb_local
-    elif args.workload == "c5":
+    elif name == "c5":
         traffic = (2176.0e6 + 3.7e6) / 8_000_000 * nb_local
     flops_per_launch = 2.0 * nq * nb_local * d
     bytes_per_launch = nb_local * d * ELEM_BYTES[w["storage"]] + nq * d * 4 + nq * k * 12
@@ -460,11 +592,11 @@ def run_b200(args, w, rank, world, local_rank):
     main_avg_ms = main_ms.value / n_main
     tensor_bound = nq > 64
     if tensor_bound:
-        # a step may launch the kernel several times (column chunks, query batches): credit the
-        # step's algorithmic FLOPs against the summed duration of its launches
-        launches_per_step = max(1.0, main_launches.value / max(1, args.steps))
+        # a step may launch the kernel several times (pilot pass, filter pass, query batches):
+        # credit the step's algorithmic FLOPs against the summed duration of its launches
+        launches_per_step = max(1.0, main_launches.value / max(1, steps))
         achieved = flops_per_launch / (main_avg_ms * launches_per_step * 1e-3) / 1e12 if main_avg_ms > 0 else 0.0
-        peak = peaks["bf16_tflops_sustained"] if ms_step * args.steps > 1000 else peaks["bf16_tflops"]
+        peak = peaks["bf16_tflops_sustained"] if ms_step * steps > 1000 else peaks["bf16_tflops"]
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per step (scaled from an ncu capture)", "kernel": "gemm_topk_kernel",
                     "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
@@ -475,29 +607,74 @@ def run_b200(args, w, rank, world, local_rank):
     else:
         achieved = bytes_per_launch / (main_avg_ms * 1e-3) / 1e9 if main_avg_ms > 0 else 0.0
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "traffic_unit": "bytes per launch (scaled from an ncu capture)", "kernel": "scan_mma_kernel",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "traffic_unit": "bytes per launch (scaled from an ncu capture)",
+                    "kernel": "scan_mma_kernel" if w["storage"] != 0 else "scan_kernel",
                     "kernel_ms_avg": main_avg_ms, "kernel_launches": main_launches.value,
                     "peak_source": peaks["source"], "frac_of_nominal_8000": achieved / 8000.0}
-
-    cpu = None
-    if world == 1 and not args.no_cpu_baseline:
-        qps_c, ms_c, cores, sample = cpu_time_steps(w, 3, 1)
-        cpu = {"value": qps_c, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample}
-
-    line = {
+    return {
         "metric": "QPS (flat kNN %s)" % w["desc"],
-        "value": nq / (ms_step * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "value": nq / (ms_step * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": steps,
+        "warmup": max(warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": DTYPE_NAME[w["storage"]].split(" ")[0], "data": "synthetic",
-        "config": {"workload": args.workload, "desc": w["desc"], "nb": w["nb"], "nq": nq, "d": d, "k": k,
+        "config": {"workload": name, "desc": w["desc"], "nb": w["nb"], "nq": nq, "d": d, "k": k,
                    "rows_per_gpu": nb_local, "parallelism": "row-sharded x%d, NCCL all-gather + k-way merge" % world,
                    "l2_policy": "inputs larger than L2 (database shard %.1f GB streams every step)"
                                 % (nb_local * d * ELEM_BYTES[w["storage"]] / 1e9),
                    "seeds": {"database": 1, "queries": 2},
-                   "headline": not (args.nb or args.nq)},
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches.value),
+                   "headline": headline},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches.value),
         "latency": latency, "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
     }
+
+
+def run_b200(args, w, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import faiss_metal_b200 as fm
+    from oracle import flat_oracle as O   # the checker of the label checks and the CPU baseline leg
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    res = fm.StandardB200Resources(local_rank)
+    ext = torch.cuda.ExternalStream(res.stream, device=torch.device("cuda", local_rank))
+    ctx = {"fm": fm, "torch": torch, "dist": dist, "O": O, "rank": rank, "world": world, "local_rank": local_rank,
+           "res": res, "ext": ext, "peaks": load_peaks()}
+    headline = not (args.nb or args.nq)
+    line = run_workload(ctx, args.workload, w, args.steps, args.warmup, headline, with_e2e=not args.no_e2e,
+                        with_label_check=not args.no_label_check)
+
+    # The other north-star configurations, a few steps each, attached to the same line: the
+    # headline keys above are untouched.
+    extras = {}
+    if headline and args.workload == "c3" and not args.no_extras:
+        for name in ("c5", "c2", "c4"):
+            try:
+                extras[name] = run_workload(ctx, name, dict(WORKLOADS[name]), max(3, min(args.steps, 10)), 3, False,
+                                            with_e2e=not args.no_e2e, with_label_check=not args.no_label_check)
+            except Exception as e:   # an extra must never take the headline down with it
+                extras[name] = {"error": "%s: %s" % (type(e).__name__, e)}
+                if world > 1:
+                    raise
+
+    def teardown():
+        torch.cuda.synchronize()
+        res.close()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+    if rank != 0:
+        teardown()
+        return
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        qps_c, ms_c, cores, sample = cpu_time_steps(w, 3, 1)
+        cpu = {"value": qps_c, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample}
+    line["cpu_baseline"] = cpu
+    if extras:
+        line["extra_configs"] = extras
     emit(line)
     teardown()
 

@@ -21,4 +21,5 @@ from .abi import (  # noqa: F401
     status_string,
 )
 from .index import B200IndexFlat, SearchToken, StandardB200Resources, device_caps  # noqa: F401
-from .sharded import ShardedIndexFlat, shard_range  # noqa: F401
+from .sharded import MultiGpuIndexFlat, ShardedIndexFlat, shard_range  # noqa: F401
+from . import abi  # noqa: F401

@@ -76,6 +76,7 @@ SIGNATURES = {
     "b200f_select_rows": (c_int, [c_vp, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "b200f_merge_lists": (c_int, [c_vp, c_vp, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
     "b200f_merge_lists_strided": (c_int, [c_vp, c_vp, c_i64, c_i64, c_int, c_i64, c_int, c_int, c_vp, c_vp, c_vp]),
+    "b200f_remap_labels_block_cyclic": (c_int, [c_vp, c_i64, c_i64, c_int, c_int, c_vp]),
     "b200f_fill_synthetic": (c_int, [c_vp, c_i64, c_int, c_i64, ctypes.c_uint64, c_int, ctypes.c_float, c_vp]),
     "b200f_profile_enable": (c_int, [c_int]),
     "b200f_profile_read": (c_int, [ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(ctypes.c_double), c_int]),
@@ -112,6 +113,19 @@ SIGNATURES = {
     "b200f_index_device_rows": (c_vp, [c_vp]),
     "b200f_index_last_device_status": (c_int, [c_vp]),
     "b200f_index_debug_wait_expiry": (c_int, [c_vp, c_i64]),
+    "b200f_comm_id_create": (c_int, [c_vp]),
+    "b200f_sharded_create": (c_int, [ctypes.POINTER(c_vp), c_int, c_int, c_int, c_int, c_i64, ctypes.POINTER(c_vp)]),
+    "b200f_sharded_create_rank": (c_int, [c_vp, c_int, c_int, c_vp, ctypes.POINTER(c_vp)]),
+    "b200f_sharded_destroy": (None, [c_vp]),
+    "b200f_sharded_add": (c_int, [c_vp, c_i64, c_vp]),
+    "b200f_sharded_search": (c_int, [c_vp, c_i64, c_vp, c_i64, c_vp, c_vp]),
+    "b200f_sharded_search_enqueue": (c_int, [c_vp, c_i64, c_vp, c_i64, c_vp, c_vp]),
+    "b200f_sharded_synchronize": (c_int, [c_vp]),
+    "b200f_sharded_reset": (c_int, [c_vp]),
+    "b200f_sharded_reconstruct": (c_int, [c_vp, c_i64, c_vp]),
+    "b200f_sharded_ntotal": (c_i64, [c_vp]),
+    "b200f_sharded_num_shards": (c_int, [c_vp]),
+    "b200f_sharded_set_path": (c_int, [c_vp, c_int]),
 }
 
 

@@ -23,7 +23,7 @@ HOST_CXX = shutil.which("g++") or "g++"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CU_SOURCES = ["csrc/rows.cu", "csrc/scan.cu", "csrc/select.cu", "csrc/gemm_topk.cu", "csrc/search.cu"]
-CPP_SOURCES = ["host/Resources.cpp", "host/GrowableArray.cpp", "host/IndexFlat.cpp", "host/capi.cpp",
+CPP_SOURCES = ["host/Resources.cpp", "host/GrowableArray.cpp", "host/IndexFlat.cpp", "host/Sharded.cpp", "host/capi.cpp",
                "faiss_compat/compat_impl.cpp"]
 def _headers():
     """Every header an object may depend on (globbed, so that a new one cannot be forgotten)."""
@@ -88,7 +88,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
                 sys.stdout.write(o)
     if force or jobs or _newer(LIB_PATH, objs):
         _run([NVCC, "-ccbin", HOST_CXX, *ARCH_FLAGS, "-shared", "-o", LIB_PATH, *objs,
-              "-cudart", "static", "-Xlinker", "--no-undefined"])
+              "-cudart", "static", "-Xlinker", "--no-undefined", "-ldl"])
     return LIB_PATH
 
 

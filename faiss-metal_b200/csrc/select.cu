@@ -283,6 +283,20 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
 
         int64_t total = (SRC == SRC_MATRIX) ? p.ncand : (SRC == SRC_LISTS) ? (int64_t)p.P * p.k : p.ld;
         if (SRC == SRC_PARTS && p.cand_cnt) total = min((int64_t)__ldg(p.cand_cnt + q), p.ld);
+        // Merging result lists: equal keys must come out in label order, whichever list they
+        // sit in (lists of interleaved row shards do not hold ascending label ranges).  Labels
+        // below 2^32 ride in the low word of the sort key; should a row hold a larger one, its
+        // ties fall back to list order.
+        bool wide_labels = false;
+        if (SRC == SRC_LISTS) {
+            int big = 0;
+            for (int64_t c = tid; c < total; c += SS_THREADS) {
+                const int64_t l = c / p.k;
+                const int64_t lab = __ldg(p.labels + l * p.list_stride_l + q * p.k + (c - l * p.k));
+                big |= (lab >= 0 && (lab >> 32) != 0) ? 1 : 0;   // -1 marks an empty slot
+            }
+            wide_labels = __syncthreads_or(big) != 0;
+        }
         // Wide streaming path (key matrix with 16-byte aligned rows): every thread loads
         // 8 x float4 = 32 columns up front, counts its hits against the current threshold, and
         // the CTA appends them after ONE count check per 32,768 columns.  Only when the buffer
@@ -428,8 +442,9 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                         const int64_t j = c - l * p.k;
                         const int64_t off = q * p.k + j;
                         key = p.key_sign * __ldg(p.keys + l * p.list_stride_k + off);
-                        live = __ldg(p.labels + l * p.list_stride_l + off) >= 0;
-                        payload = (uint32_t)c;
+                        const int64_t lab = __ldg(p.labels + l * p.list_stride_l + off);
+                        live = lab >= 0;
+                        payload = wide_labels ? (uint32_t)c : (uint32_t)lab;
                     }
                     const uint64_t w = pack(key, payload);
                     if (live && w < thr) {
@@ -461,6 +476,8 @@ __global__ void __launch_bounds__(SS_THREADS) sort_select_kernel(const SortSelec
                     if (p.clamp && dist < 0.f) dist = 0.f;
                     if (SRC != SRC_LISTS) {
                         label = (int64_t)payload + p.label_base;
+                    } else if (!wide_labels) {
+                        label = (int64_t)payload;
                     } else {
                         const int64_t l = payload / p.k;
                         const int64_t jj = payload - l * p.k;
@@ -867,6 +884,30 @@ extern "C" int b200f_select_rows(const float* scores, int64_t nq, int64_t ncols,
     p.out_dist = out_dist;
     p.out_labels = out_labels;
     return launch_sort_select<SRC_MATRIX>(p, static_cast<cudaStream_t>(stream));
+}
+
+// Row shards laid out block-cyclically: global row g lives on shard (g / B) % S at local row
+// (g / (B * S)) * B + g % B.  The inverse, applied to the labels a shard-local search returned.
+__global__ void remap_labels_kernel(int64_t* __restrict__ labels, int64_t n, int64_t block, int64_t nshards,
+                                    int64_t shard) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t l = labels[i];
+        if (l >= 0) labels[i] = ((l / block) * nshards + shard) * block + l % block;
+    }
+}
+
+extern "C" int b200f_remap_labels_block_cyclic(int64_t* labels, int64_t count, int64_t block_rows, int nshards,
+                                               int shard, void* stream) {
+    if (count < 0 || block_rows < 1 || nshards < 1 || shard < 0 || shard >= nshards) return B200F_ERR_BAD_ARG;
+    if (count == 0) return B200F_OK;
+    if (!labels) return B200F_ERR_BAD_ARG;
+    int64_t g = ceil_div64(count, 256);
+    const int64_t cap = (int64_t)cached_sm_count() * 8;
+    if (g > cap) g = cap;
+    remap_labels_kernel<<<(int)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(labels, count, block_rows, nshards, shard);
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
 }
 
 extern "C" int b200f_merge_lists_strided(const float* dist, const int64_t* labels,

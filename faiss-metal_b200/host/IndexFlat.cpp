@@ -656,6 +656,7 @@ void B200IndexFlat::setLabelBase(faiss::idx_t base) {
     impl_->labelBase = base;
 }
 const void* B200IndexFlat::getDeviceRows() const { return impl_->rows; }
+std::shared_ptr<B200Resources> B200IndexFlat::getResources() const { return impl_->res; }
 int B200IndexFlat::lastDeviceStatus() const { return impl_->lastStatus; }
 void B200IndexFlat::debugWaitExpiry(int64_t limitCycles) {
     DeviceGuard g(impl_->res->getDevice());

@@ -4,8 +4,10 @@
 #include <cuda_runtime.h>
 #include <faiss/impl/FaissAssert.h>
 
+#include <cstring>
 #include <memory>
 #include <new>
+#include <vector>
 #include <stdexcept>
 #include <string>
 
@@ -18,7 +20,10 @@ struct B200FResources {
     std::shared_ptr<StandardB200Resources> res;
 };
 struct B200FIndex {
-    std::unique_ptr<B200IndexFlat> index;
+    std::shared_ptr<B200IndexFlat> index;   // shared with a sharded index built over it
+};
+struct B200FSharded {
+    std::unique_ptr<B200ShardedIndexFlat> index;
 };
 struct B200FToken {
     std::unique_ptr<B200SearchToken> token;
@@ -285,6 +290,119 @@ int b200f_index_debug_wait_expiry(B200FIndex* index, int64_t limit_cycles) {
     if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
     B200F_GUARD_BEGIN
     index->index->debugWaitExpiry(limit_cycles);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+// ---- sharded index ------------------------------------------------------------------------
+
+int b200f_comm_id_create(void* id128) {
+    if (!id128) return fail(B200F_ERR_BAD_ARG, "null output pointer");
+    B200F_GUARD_BEGIN
+    const B200CommId id = createCommId();
+    std::memcpy(id128, id.bytes, sizeof(id.bytes));
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_create(B200FResources* const* res, int nshards, int d, int metric, int storage,
+                         int64_t block_rows, B200FSharded** out) {
+    if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");
+    *out = nullptr;
+    if (!res || nshards < 1) return fail(B200F_ERR_BAD_ARG, "at least one resources handle is needed");
+    if (metric != B200F_METRIC_L2 && metric != B200F_METRIC_INNER_PRODUCT)
+        return fail(B200F_ERR_BAD_ARG, "metric must be L2 or inner product");
+    if (storage < 0 || storage > 2) return fail(B200F_ERR_BAD_ARG, "invalid storage type");
+    B200F_GUARD_BEGIN
+    std::vector<std::shared_ptr<B200Resources>> rs;
+    for (int i = 0; i < nshards; i++) {
+        if (!res[i]) return fail(B200F_ERR_BAD_ARG, "null resources");
+        rs.push_back(res[i]->res);
+    }
+    std::unique_ptr<B200FSharded> h(new B200FSharded);
+    h->index.reset(new B200ShardedIndexFlat(std::move(rs), d,
+                                            metric == B200F_METRIC_L2 ? faiss::METRIC_L2 : faiss::METRIC_INNER_PRODUCT,
+                                            static_cast<StorageType>(storage), block_rows));
+    *out = h.release();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_create_rank(B200FIndex* local, int rank, int world, const void* id128, B200FSharded** out) {
+    if (!out) return fail(B200F_ERR_BAD_ARG, "null output pointer");
+    *out = nullptr;
+    if (!local) return fail(B200F_ERR_BAD_ARG, "null index");
+    if (world > 1 && !id128) return fail(B200F_ERR_BAD_ARG, "null communicator id");
+    B200F_GUARD_BEGIN
+    B200CommId id;
+    std::memset(id.bytes, 0, sizeof(id.bytes));
+    if (id128) std::memcpy(id.bytes, id128, sizeof(id.bytes));
+    std::unique_ptr<B200FSharded> h(new B200FSharded);
+    h->index.reset(new B200ShardedIndexFlat(local->index, rank, world, id));
+    *out = h.release();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+void b200f_sharded_destroy(B200FSharded* index) { delete index; }
+
+int b200f_sharded_add(B200FSharded* index, int64_t n, const float* x) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->add(n, x);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_search(const B200FSharded* index, int64_t n, const float* x, int64_t k, float* distances,
+                         int64_t* labels) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->search(n, x, k, distances, reinterpret_cast<faiss::idx_t*>(labels));
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_search_enqueue(const B200FSharded* index, int64_t n, const float* x, int64_t k, float* distances,
+                                 int64_t* labels) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->searchDeviceEnqueue(n, x, k, distances, reinterpret_cast<faiss::idx_t*>(labels));
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_synchronize(const B200FSharded* index) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->synchronize();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_reset(B200FSharded* index) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->reset();
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_sharded_reconstruct(const B200FSharded* index, int64_t key, float* recons) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->reconstruct(key, recons);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int64_t b200f_sharded_ntotal(const B200FSharded* index) { return index ? index->index->ntotal : -1; }
+int b200f_sharded_num_shards(const B200FSharded* index) { return index ? index->index->numShards() : -1; }
+
+int b200f_sharded_set_path(B200FSharded* index, int path) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->setForcePath(path);
     return B200F_OK;
     B200F_GUARD_END
 }

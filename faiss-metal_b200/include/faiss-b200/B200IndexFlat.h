@@ -96,6 +96,8 @@ class B200IndexFlat : public faiss::Index {
     void setLabelBase(faiss::idx_t base);
     /// Device pointers of the shard (rows in storage precision).
     const void* getDeviceRows() const;
+    /// The resources this index was built on.
+    std::shared_ptr<B200Resources> getResources() const;
     /// Enqueue a search whose queries and outputs are all DEVICE pointers on the resources'
     /// stream and return without synchronising (single batch: n <= 16384 for k <= 32,
     /// n <= 1024 otherwise).  The multi-GPU layer chains the candidate exchange and the merge

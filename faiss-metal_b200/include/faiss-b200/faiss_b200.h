@@ -4,4 +4,5 @@
 #include "B200Exception.h"
 #include "B200IndexFlat.h"
 #include "B200Resources.h"
+#include "B200ShardedIndexFlat.h"
 #include "StandardB200Resources.h"

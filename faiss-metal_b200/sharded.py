@@ -1,16 +1,21 @@
-"""Row-sharded flat index over the GPUs of one box: one process per GPU.
+"""Row-sharded flat index over the GPUs of one box: Python mirrors of
+faiss_b200::B200ShardedIndexFlat (the reference is single-device,
+src/StandardMetalResources.mm:17-23, and has no counterpart).
 
-Each rank holds rows [lo, hi) of the database (``shard_range``) in its own
-B200IndexFlat with ``label_base = lo``; a search runs the shard-local search on
-every rank, exchanges the per-rank (distance, label) candidate lists with one
-all-gather over NCCL (NVLink / NVSwitch) and merges the ``world_size`` sorted
-lists per query with the k-way merge kernel (b200f_merge_lists).  The reference
-is single-device (src/StandardMetalResources.mm:17-23); this layer has no
-counterpart there.
+``MultiGpuIndexFlat``   one process drives several GPUs: add() places rows block-cyclically,
+                        search() copies the queries up in slices, all-gathers them, searches
+                        every shard, all-gathers the candidates and merges.
+``ShardedIndexFlat``    one process per GPU (what torchrun launches): each rank holds rows
+                        [lo, hi) (``shard_range``) in its own B200IndexFlat with
+                        ``label_base = lo``; search is a collective call.
 
-With ``backend="gloo"`` process groups the exchange runs on CPU tensors so the
-shard / offset / merge logic can be tested without GPUs (``merge_fn`` must then
-be a host merge supplied by the test).
+In both the exchange is one ncclAllGather issued by the C++ library on the resources' own stream
+between the shard search and the k-way merge kernel; torch.distributed is used for one thing
+only, to hand rank 0's NCCL id to the other ranks.
+
+With a CPU process group (``backend="gloo"``) and a ``merge_fn`` the exchange of
+``ShardedIndexFlat.search`` runs on CPU tensors through torch.distributed, so the shard / offset /
+merge logic can be tested without GPUs.
 """
 from __future__ import annotations
 
@@ -19,6 +24,7 @@ import ctypes
 import numpy as np
 
 from . import abi
+from .index import _check, _is_cuda, _ptr
 
 
 def shard_range(nb: int, rank: int, world: int):
@@ -31,7 +37,7 @@ def shard_range(nb: int, rank: int, world: int):
 
 def pack_candidates(dist, labels):
     """Pack (float32 distance, int64 label) lists [nq, k] into one int32 [nq, k, 3] buffer so
-    a single all-gather moves both."""
+    a single all-gather moves both (CPU process groups)."""
     import torch
     nq, k = dist.shape
     buf = torch.empty((nq, k, 3), dtype=torch.int32, device=dist.device)
@@ -48,8 +54,119 @@ def unpack_candidates(buf):
     return dist, labels
 
 
-class ShardedIndexFlat:
-    """Data-parallel flat index: database rows sharded over the ranks of a process group."""
+class _ShardedHandle:
+    """Calls shared by the two mirrors (a B200FSharded handle)."""
+
+    _h = None
+    d = 0
+    metric_type = abi.METRIC_L2
+    resources = None
+
+    def _search(self, x, k, distances, labels, want_result=True):
+        if len(x.shape) != 2:
+            raise ValueError("search: expected a 2-d array [n, %d]" % self.d)
+        n = int(x.shape[0])
+        _check(x, "search: x", "float32", (n, self.d))
+        if want_result and (distances is None or labels is None):
+            if isinstance(x, np.ndarray):
+                distances = np.empty((n, k), dtype=np.float32)
+                labels = np.empty((n, k), dtype=np.int64)
+            else:
+                import torch
+                distances = torch.empty((n, k), dtype=torch.float32, device=x.device)
+                labels = torch.empty((n, k), dtype=torch.int64, device=x.device)
+        if want_result and int(k) >= 1:
+            _check(distances, "search: distances", "float32", (n, int(k)))
+            _check(labels, "search: labels", "int64", (n, int(k)))
+        self.resources._order_after_torch(x, distances, labels)
+        abi.check(abi.lib().b200f_sharded_search(self._h, n, _ptr(x) if n else None, int(k),
+                                                 _ptr(distances) if want_result else None,
+                                                 _ptr(labels) if want_result else None), "sharded search")
+        return distances, labels
+
+    def search_enqueue(self, x, k: int, distances=None, labels=None):
+        """Device tensors only, one batch; queued on the resources' stream(s), no host wait."""
+        n = int(x.shape[0])
+        _check(x, "search_enqueue: x", "float32", (n, self.d))
+        if distances is not None:
+            _check(distances, "search_enqueue: distances", "float32", (n, int(k)))
+            _check(labels, "search_enqueue: labels", "int64", (n, int(k)))
+        self.resources._order_after_torch(x, distances, labels)
+        abi.check(abi.lib().b200f_sharded_search_enqueue(self._h, n, _ptr(x) if n else None, int(k),
+                                                         _ptr(distances), _ptr(labels)), "sharded search_enqueue")
+
+    def synchronize(self):
+        abi.check(abi.lib().b200f_sharded_synchronize(self._h), "sharded synchronize")
+
+    def set_path(self, path: int):
+        abi.check(abi.lib().b200f_sharded_set_path(self._h, int(path)), "sharded set_path")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            abi.lib().b200f_sharded_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class MultiGpuIndexFlat(_ShardedHandle):
+    """One process, several GPUs (or several shards on one GPU: a single-GPU rehearsal of the
+    same code).  ``resources``: one StandardB200Resources per shard."""
+
+    def __init__(self, resources, d: int, metric: int = abi.METRIC_L2, storage: int = abi.STORAGE_F32,
+                 block_rows: int = 65536):
+        arr = (ctypes.c_void_p * len(resources))(*[r._h for r in resources])
+        h = ctypes.c_void_p()
+        abi.check(abi.lib().b200f_sharded_create(arr, len(resources), d, metric, storage, int(block_rows),
+                                                 ctypes.byref(h)), "sharded create")
+        self._h = h
+        self._res_list = list(resources)
+        self.resources = resources[0]
+        self.d = d
+        self.metric_type = metric
+        self.storage = storage
+        self.block_rows = int(block_rows)
+
+    @property
+    def ntotal(self) -> int:
+        return abi.lib().b200f_sharded_ntotal(self._h)
+
+    @property
+    def num_shards(self) -> int:
+        return abi.lib().b200f_sharded_num_shards(self._h)
+
+    def add(self, x):
+        if len(x.shape) != 2:
+            raise ValueError("add: expected a 2-d array [n, %d]" % self.d)
+        n = int(x.shape[0])
+        _check(x, "add: x", "float32", (n, self.d))
+        if _is_cuda(x):
+            raise ValueError("add: the several-GPU index takes host rows (each shard uploads its own blocks)")
+        abi.check(abi.lib().b200f_sharded_add(self._h, n, _ptr(x) if n else None), "sharded add")
+
+    def search(self, x, k: int, distances=None, labels=None):
+        return self._search(x, k, distances, labels)
+
+    def reset(self):
+        abi.check(abi.lib().b200f_sharded_reset(self._h), "sharded reset")
+
+    def reconstruct(self, key: int) -> np.ndarray:
+        out = np.empty(self.d, dtype=np.float32)
+        abi.check(abi.lib().b200f_sharded_reconstruct(self._h, int(key), _ptr(out)), "sharded reconstruct")
+        return out
+
+
+class ShardedIndexFlat(_ShardedHandle):
+    """One process per GPU: database rows sharded over the ranks of a process group.
+
+    GPU ranks: ``local_index`` is this rank's B200IndexFlat.  world > 1 needs an initialised
+    torch.distributed process group (any backend), used once to broadcast rank 0's NCCL id.
+    CPU ranks (tests): ``merge_fn`` given, ``local_index`` any object with ``search`` and
+    ``set_label_base``."""
 
     def __init__(self, local_index, rank: int, world: int, group=None, merge_fn=None):
         self.local = local_index
@@ -58,71 +175,56 @@ class ShardedIndexFlat:
         self.group = group
         self.merge_fn = merge_fn
         self.metric_type = local_index.metric_type
+        self._bufs = {}
+        self._h = None
+        if merge_fn is not None:
+            return
+        self.d = local_index.d
+        self.resources = local_index.resources
+        ident = ctypes.create_string_buffer(128)
+        if world > 1:
+            import torch.distributed as dist
+            box = [None]
+            if rank == 0:
+                abi.check(abi.lib().b200f_comm_id_create(ident), "comm id")
+                box[0] = ident.raw
+            dist.broadcast_object_list(box, src=0, group=group)
+            ident = ctypes.create_string_buffer(box[0], 128)
+        h = ctypes.c_void_p()
+        abi.check(abi.lib().b200f_sharded_create_rank(local_index._h, rank, world, ident, ctypes.byref(h)),
+                  "sharded create_rank")
+        self._h = h
 
     def set_shard(self, lo: int):
         self.local.set_label_base(lo)
 
-    def _merge_device(self, dist_all, labels_all, k, stream):
+    def search_device(self, x, k: int, sync: bool = True, want_result: bool = True):
+        """x: fp32 CUDA tensor [nq, d] on this rank's GPU, identical on every rank, one batch.
+        Shard search, one all-gather of [distances | labels] and the k-way merge are queued back
+        to back on the resources' stream.  Returns this rank's merged (distances, labels) device
+        tensors, reused by the next call with the same (nq, k); (None, None) with
+        want_result=False (the rank takes part in the exchange, merges nothing)."""
         import torch
-        P, nq, _ = dist_all.shape
-        out_d = torch.empty((nq, k), dtype=torch.float32, device=dist_all.device)
-        out_l = torch.empty((nq, k), dtype=torch.int64, device=dist_all.device)
-        abi.check_op(abi.lib().b200f_merge_lists(
-            ctypes.c_void_p(dist_all.data_ptr()), ctypes.c_void_p(labels_all.data_ptr()), P, nq, k,
-            self.metric_type, ctypes.c_void_p(out_d.data_ptr()), ctypes.c_void_p(out_l.data_ptr()),
-            ctypes.c_void_p(stream)), "merge_lists")
-        return out_d, out_l
-
-    # -- device path: no allocation, no host synchronisation between the three steps ------
-    def _buffers(self, nq: int, k: int, device):
-        import torch
-        key = (nq, k)
-        b = self._bufs.get(key) if hasattr(self, "_bufs") else None
-        if b is None:
-            if not hasattr(self, "_bufs"):
-                self._bufs = {}
-            dist_bytes = (nq * k * 4 + 15) // 16 * 16
-            rank_bytes = (dist_bytes + nq * k * 8 + 15) // 16 * 16
-            mine = torch.empty(rank_bytes, dtype=torch.uint8, device=device)
-            allb = torch.empty(self.world * rank_bytes, dtype=torch.uint8, device=device)
-            b = {
-                "rank_bytes": rank_bytes, "dist_bytes": dist_bytes, "mine": mine, "all": allb,
-                "d_loc": mine[: nq * k * 4].view(torch.float32).view(nq, k),
-                "l_loc": mine[dist_bytes: dist_bytes + nq * k * 8].view(torch.int64).view(nq, k),
-                "out_d": torch.empty((nq, k), dtype=torch.float32, device=device),
-                "out_l": torch.empty((nq, k), dtype=torch.int64, device=device),
-            }
-            self._bufs[key] = b
-        return b
-
-    def search_device(self, x, k: int, sync: bool = True):
-        """x: fp32 CUDA tensor [nq, d] on this rank's GPU, identical on every rank; torch's current
-        stream must be the resources' stream (wrap it with torch.cuda.ExternalStream).  Shard
-        search, one all-gather of [distances | labels] per rank and the k-way merge are queued
-        back to back; the returned tensors are reused by the next call with the same (nq, k)."""
-        import torch
-        import torch.distributed as dist
         nq = int(x.shape[0])
-        b = self._buffers(nq, k, x.device)
-        if self.world == 1:
-            self.local.search_enqueue(x, k, b["out_d"], b["out_l"])
-        else:
-            self.local.search_enqueue(x, k, b["d_loc"], b["l_loc"])
-            dist.all_gather_into_tensor(b["all"], b["mine"], group=self.group)
-            base = b["all"].data_ptr()
-            abi.check_op(abi.lib().b200f_merge_lists_strided(
-                ctypes.c_void_p(base), ctypes.c_void_p(base + b["dist_bytes"]),
-                b["rank_bytes"] // 4, b["rank_bytes"] // 8, self.world, nq, k, self.metric_type,
-                ctypes.c_void_p(b["out_d"].data_ptr()), ctypes.c_void_p(b["out_l"].data_ptr()),
-                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "merge_lists_strided")
+        out = (None, None)
+        if want_result:
+            out = self._bufs.get((nq, k))
+            if out is None:
+                out = (torch.empty((nq, k), dtype=torch.float32, device=x.device),
+                       torch.empty((nq, k), dtype=torch.int64, device=x.device))
+                self._bufs[(nq, k)] = out
+        self.search_enqueue(x, k, out[0], out[1])
         if sync:
-            self.local.synchronize()
-        return b["out_d"], b["out_l"]
+            self.synchronize()
+        return out
 
-    def search(self, x, k: int):
-        """x: fp32 queries [nq, d], identical on every rank (torch tensor on this rank's GPU,
-        or a CPU tensor / numpy array with a gloo group).  Returns the merged
-        (distances, labels) on every rank."""
+    def search(self, x, k: int, distances=None, labels=None, want_result: bool = True):
+        """x: fp32 queries [nq, d], identical on every rank: numpy (host) or a CUDA tensor on this
+        rank's GPU.  Returns (distances, labels) in the memory space of x; with want_result=False
+        the rank only takes part (returns (None, None)).  With a CPU process group and a
+        merge_fn: x numpy / CPU tensor, the exchange runs through torch.distributed."""
+        if self.merge_fn is None:
+            return self._search(x, k, distances, labels, want_result)
         import torch
         import torch.distributed as dist
         d_loc, l_loc = self.local.search(x, k)
@@ -133,15 +235,6 @@ class ShardedIndexFlat:
             l_loc = torch.from_numpy(l_loc)
         packed = pack_candidates(d_loc, l_loc)
         gathered = torch.empty((self.world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
-        if packed.is_cuda:
-            dist.all_gather_into_tensor(gathered, packed, group=self.group)
-        else:  # gloo
-            dist.all_gather([gathered[r] for r in range(self.world)], packed, group=self.group)
+        dist.all_gather([gathered[r] for r in range(self.world)], packed, group=self.group)
         d_all, l_all = unpack_candidates(gathered)
-        if d_all.is_cuda:
-            stream = torch.cuda.current_stream().cuda_stream
-            return self._merge_device(d_all.contiguous(), l_all.contiguous(), k, stream)
-        if self.merge_fn is None:
-            raise RuntimeError("CPU process group: a host merge_fn must be supplied (tests only)")
-        out_d, out_l = self.merge_fn(self.metric_type, d_all.numpy(), l_all.numpy())
-        return out_d, out_l
+        return self.merge_fn(self.metric_type, d_all.numpy(), l_all.numpy())

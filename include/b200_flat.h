@@ -258,6 +258,13 @@ int b200f_merge_lists_strided(const float* dist, const int64_t* labels, int64_t 
                               int64_t list_stride_labels, int P, int64_t nq, int k, int metric,
                               float* out_dist, int64_t* out_labels, void* stream);
 
+/* Labels of a shard-local search -> global labels when rows are placed block-cyclically over
+ * nshards shards (global row g on shard (g / B) % nshards at local row (g / (B * nshards)) * B +
+ * g % B): labels[i] >= 0 becomes ((l / B) * nshards + shard) * B + l % B, -1 stays.  Device
+ * pointer, in place.  No counterpart in the reference (single device). */
+int b200f_remap_labels_block_cyclic(int64_t* labels, int64_t count, int64_t block_rows, int nshards, int shard,
+                                    void* stream);
+
 /* Deterministic synthetic rows on the device (benchmark inputs): element
  * (row, col) depends only on (seed, row0 + row, col).
  * dist: 0 = U[0,1), 1 = N(0,1) * scale, 2 = N(0,1) then row-normalised,
@@ -377,6 +384,46 @@ int b200f_index_last_device_status(const B200FIndex* index);
  * b200f_index_synchronize then reports B200F_ERR_DEVICE_WAIT, and the search after it runs
  * normally (every search clears the word first).  For tests of the error path. */
 int b200f_index_debug_wait_expiry(B200FIndex* index, int64_t limit_cycles);
+
+/* ---- sharded index: rows over the GPUs of one box ------------------------------------------ */
+/* Mirror of faiss_b200::B200ShardedIndexFlat.  The reference is single-device
+ * (src/StandardMetalResources.mm:17-23) and has no counterpart; the surface is the same
+ * faiss::Index contract as above (include/faiss-metal/MetalIndexFlat.h:47-111).  Every GPU
+ * searches its own rows; the per-GPU candidates are exchanged with one ncclAllGather issued by
+ * the library on the resources' own stream and merged by b200f_merge_lists_strided.  NCCL is
+ * loaded at run time (libnccl.so.2), only when more than one GPU takes part. */
+typedef struct B200FSharded B200FSharded;
+
+/* 128 bytes (an ncclUniqueId) that rank 0 creates and every rank of a one-process-per-GPU
+ * group passes to b200f_sharded_create_rank. */
+int b200f_comm_id_create(void* id128);
+/* One process drives nshards GPUs (one resources handle each; several handles of ONE device
+ * rehearse the same code on a single GPU with device copies in the place of NCCL).  Rows are
+ * placed block-cyclically in blocks of block_rows. */
+int b200f_sharded_create(B200FResources* const* res, int nshards, int d, int metric, int storage,
+                         int64_t block_rows, B200FSharded** out);
+/* One process per GPU: `local` holds this rank's rows (label base set by the caller) and must
+ * outlive nothing: the sharded index shares its ownership.  Collective over the group when
+ * world > 1 (ncclCommInitRank). */
+int b200f_sharded_create_rank(B200FIndex* local, int rank, int world, const void* id128, B200FSharded** out);
+void b200f_sharded_destroy(B200FSharded* index);
+/* several-GPU form only (B200F_ERR_STATE otherwise) */
+int b200f_sharded_add(B200FSharded* index, int64_t n, const float* x);
+/* x host or device.  Host queries cross PCIe once: part i's GPU takes the i-th slice and the
+ * slices are all-gathered over NVLink.  One process per GPU: collective, identical n, k, x on
+ * every rank; distances = labels = NULL on ranks that do not want the result (no merge, no
+ * copy back there). */
+int b200f_sharded_search(const B200FSharded* index, int64_t n, const float* x, int64_t k, float* distances,
+                         int64_t* labels);
+/* Device pointers, one batch, no host synchronisation (see b200f_index_search_enqueue). */
+int b200f_sharded_search_enqueue(const B200FSharded* index, int64_t n, const float* x, int64_t k,
+                                 float* distances, int64_t* labels);
+int b200f_sharded_synchronize(const B200FSharded* index);
+int b200f_sharded_reset(B200FSharded* index);
+int b200f_sharded_reconstruct(const B200FSharded* index, int64_t key, float* recons);
+int64_t b200f_sharded_ntotal(const B200FSharded* index);   /* one process per GPU: this rank's rows */
+int b200f_sharded_num_shards(const B200FSharded* index);
+int b200f_sharded_set_path(B200FSharded* index, int path);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,7 @@
 // Contract test of the C++ plugin classes, written the way the reference's own test
 // binary is (tests/test_metal_flat.mm): a faiss::Index* holder, the CPU IndexFlat as the
 // comparison, std::mt19937(42) + uniform(-1, 1) data.  Exits non-zero on the first failure.
+#include <b200_flat.h>
 #include <faiss-b200/faiss_b200.h>
 #include <faiss/IndexFlat.h>
 #include <faiss/impl/FaissAssert.h>
@@ -153,6 +154,98 @@ static void testErrorsAndTokens(std::shared_ptr<B200Resources> res) {
     std::printf("errors/tokens PASS\n");
 }
 
+// The sharded index through a faiss::Index*: S shards (all on the one GPU a test box is sure to
+// have: the exchange then runs on device copies; on different GPUs when the box has them:
+// NCCL), rows placed block-cyclically over several add() calls, results bit-equal to the
+// unsharded index, labels global.
+static void testSharded(std::vector<std::shared_ptr<B200Resources>> shardRes, std::shared_ptr<B200Resources> res,
+                        StorageType storage, faiss::MetricType metric, size_t k, const char* what) {
+    const size_t nv = 5000, nq = 37, d = 48;
+    std::mt19937 rng(7);
+    auto vectors = randomVectors(nv, d, rng);
+    auto queries = randomVectors(nq, d, rng);
+    for (size_t i = 100; i < 140; i++)   // exact duplicates that land on different shards
+        for (size_t j = 0; j < d; j++) vectors[i * d + j] = vectors[(3000 + i) * d + j];
+    B200IndexFlat plain(res, (int)d, metric, storage);
+    plain.add(nv, vectors.data());
+    std::vector<float> pd(nq * k), gd(nq * k);
+    std::vector<faiss::idx_t> pl(nq * k), gl(nq * k);
+    plain.search(nq, queries.data(), k, pd.data(), pl.data());
+
+    std::unique_ptr<faiss::Index> gpu(new B200ShardedIndexFlat(shardRes, (int)d, metric, storage, 64));
+    CHECK(gpu->is_trained && gpu->ntotal == 0);
+    gpu->add(10, vectors.data());                        // partial block
+    gpu->add(1990, vectors.data() + 10 * d);             // finishes it, many whole blocks
+    gpu->add(nv - 2000, vectors.data() + 2000 * d);
+    CHECK(gpu->ntotal == (faiss::idx_t)nv);
+    gpu->search(nq, queries.data(), k, gd.data(), gl.data());
+    for (size_t i = 0; i < nq * k; i++) {
+        CHECK(gl[i] == pl[i]);
+        CHECK(gd[i] == pd[i]);
+    }
+    std::vector<float> row(d);
+    for (faiss::idx_t key : {0, 63, 64, 65, 1999, 2000, 4999}) {
+        gpu->reconstruct(key, row.data());
+        std::vector<float> want(d);
+        plain.reconstruct(key, want.data());
+        for (size_t j = 0; j < d; j++) CHECK(row[j] == want[j]);
+    }
+    bool threw = false;
+    try {
+        gpu->reconstruct(nv, row.data());
+    } catch (const faiss::FaissException&) {
+        threw = true;
+    }
+    CHECK(threw);
+    gpu->reset();
+    CHECK(gpu->ntotal == 0);
+    gpu->add(300, vectors.data());
+    gpu->search(nq, queries.data(), 5, gd.data(), gl.data());
+    for (size_t i = 0; i < nq; i++) CHECK(gl[i * 5] >= 0 && gl[i * 5] < 300);
+    std::printf("sharded %s shards=%zu storage=%d metric=%d k=%zu PASS\n", what, shardRes.size(), (int)storage,
+                (int)metric, k);
+}
+
+static void testShardedAll(std::shared_ptr<B200Resources> res) {
+    // one GPU, several shards
+    for (size_t S : {1, 3, 8}) {
+        std::vector<std::shared_ptr<B200Resources>> same(S, res);
+        testSharded(same, res, StorageType::BFloat16, faiss::METRIC_L2, 10, "one-gpu");
+        testSharded(same, res, StorageType::Float32, faiss::METRIC_INNER_PRODUCT, 100, "one-gpu");
+    }
+    // one process per GPU with a world of one: the rank form without a communicator
+    {
+        auto local = std::make_shared<B200IndexFlat>(res, 32, faiss::METRIC_L2, StorageType::Float16);
+        std::mt19937 rng(9);
+        auto v = randomVectors(2000, 32, rng);
+        local->add(2000, v.data());
+        local->setLabelBase(500);
+        B200CommId id{};
+        B200ShardedIndexFlat sh(local, 0, 1, id);
+        std::vector<float> d1(4 * 7), d2(4 * 7);
+        std::vector<faiss::idx_t> l1(4 * 7), l2(4 * 7);
+        local->search(4, v.data(), 7, d1.data(), l1.data());
+        sh.search(4, v.data(), 7, d2.data(), l2.data());
+        for (int i = 0; i < 28; i++) CHECK(l1[i] == l2[i] && d1[i] == d2[i]);
+        CHECK(l2[0] == 500);
+        sh.search(4, v.data(), 7, nullptr, nullptr);   // a rank that wants no result
+        std::printf("sharded rank-form world=1 PASS\n");
+    }
+    // every GPU of the box, when there are several
+    int ndev = 0;
+    if (b200f_device_count(&ndev) == B200F_OK && ndev >= 2) {
+        std::vector<std::shared_ptr<B200Resources>> all;
+        for (int i = 0; i < ndev; i++) all.push_back(std::make_shared<StandardB200Resources>(i));
+        testSharded(all, all[0], StorageType::BFloat16, faiss::METRIC_L2, 10, "multi-gpu");
+        testSharded(all, all[0], StorageType::Float16, faiss::METRIC_INNER_PRODUCT, 100, "multi-gpu");
+        // a plain index on the LAST device of the process: per-device kernel attributes
+        testFlat(all.back(), 3000, 200, 128, 10, faiss::METRIC_L2, StorageType::BFloat16, 5e-2f);
+        testFlat(all.back(), 3000, 200, 96, 100, faiss::METRIC_L2, StorageType::Float32, 1e-3f);
+    } else {
+        std::printf("sharded multi-gpu SKIPPED (one device)\n");
+    }
+}
+
 int main() {
     std::shared_ptr<B200Resources> res;
     try {
@@ -171,6 +264,7 @@ int main() {
     testFlat(res, 1000, 10, 128, 10, faiss::METRIC_L2, StorageType::BFloat16, 5e-2f);
     testConversion(res);
     testErrorsAndTokens(res);
+    testShardedAll(res);
     std::printf("ALL PASS\n");
     return 0;
 }
