@@ -134,6 +134,7 @@ def parse_args():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--nb", type=int, default=0, help="override database rows (not the headline config)")
     ap.add_argument("--nq", type=int, default=0, help="override queries per step (not the headline config)")
+    ap.add_argument("--storage", type=int, default=-1, help="override the storage type 0/1/2 (not the headline config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-label-check", action="store_true", help="skip the full-shard oracle label check")
@@ -212,7 +213,7 @@ def run_reference(args, w, rank, world):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "desc": w["desc"], "nb": w["nb"], "nq": w["nq"], "d": w["d"],
-                   "k": w["k"], "seeds": {"database": 1, "queries": 2}, "headline": not (args.nb or args.nq),
+                   "k": w["k"], "seeds": {"database": 1, "queries": 2}, "headline": not (args.nb or args.nq or args.storage >= 0),
                    "note": "the reference's own CPU comparison is CPU FAISS, which is not installed and whose "
                            "Metal shaders cannot run here; this arm times the oracle's sgemm + partial-select "
                            "port (the algorithm CPU FAISS uses for query batches) on all host cores"},
@@ -526,6 +527,12 @@ def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_labe
             lat_sampler = ClockSampler(local_rank)
             if root:
                 lat_sampler.start()
+            for i in range(4):   # the second call of a shape captures its graph: keep that out of the record
+                (index.search(qb[:nq], k, d_pin.numpy(), l_pin.numpy()) if world == 1 else
+                 sharded.search(qb[:nq], k, d_pin.numpy() if root else None, l_pin.numpy() if root else None,
+                                want_result=root))
+            if world > 1:
+                sharded.trace(True)
             barrier()
             for i in range(ncalls):
                 j = (i % 64) * nq
@@ -537,6 +544,32 @@ def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_labe
                 else:
                     sharded.search(qb[j:j + nq], k, want_result=False)
                 lat.append((time.perf_counter() - t0) * 1e3)
+            trace = None
+            if world > 1:
+                # Where does a slow call lose its time?  Per call and rank: microseconds on the host
+                # until everything was enqueued, then microseconds waiting for the device.  A call
+                # is only as fast as its slowest rank (the all-gather waits for every shard), so
+                # one rank that is late on the host shows as a long device wait on all the others.
+                enq, wait = sharded.read_trace()
+                sharded.trace(False)
+                per_rank = [None] * world
+                dist.all_gather_object(per_rank, (enq[:ncalls].tolist(), wait[:ncalls].tolist()))
+                if root:
+                    enq_all = np.array([p[0] for p in per_rank])      # [world, calls]
+                    wait_all = np.array([p[1] for p in per_rank])
+                    total = (enq_all + wait_all).max(axis=0)
+                    med = float(np.median(total))
+                    slow = total > 1.5 * med
+                    late_host = enq_all.max(axis=0) > np.median(enq_all) + 50.0   # some rank enqueued > 50 us late
+                    trace = {"calls": int(total.size), "median_call_us": med,
+                             "median_enqueue_us": float(np.median(enq_all)),
+                             "p99_enqueue_us_worst_rank": float(np.percentile(enq_all.max(axis=0), 99)),
+                             "slow_calls": int(slow.sum()),
+                             "slow_calls_with_a_rank_late_on_the_host": int((slow & late_host).sum()),
+                             "slow_calls_per_rank_latest": np.bincount(enq_all[:, slow].argmax(axis=0), minlength=world).tolist()
+                             if slow.any() else [0] * world,
+                             "what": "slow = call longer than 1.5 x the median; late = a rank took > 50 us longer than "
+                                     "the median to enqueue its work"}
             lat_t = torch.tensor(lat, dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(lat_t, op=dist.ReduceOp.MAX)   # a call ends when the slowest rank has it
@@ -545,7 +578,7 @@ def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_labe
             head, tail = sorted(lat_all[:500]), sorted(lat_all[-500:])
             latency = {"calls": ncalls, "p50_ms": lat_s[len(lat_s) // 2], "p99_ms": lat_s[int(len(lat_s) * 0.99)],
                        "max_ms": lat_s[-1], "p50_first_500_ms": head[len(head) // 2], "p50_last_500_ms": tail[len(tail) // 2],
-                       "clocks": lat_sampler.stop() if root else None,
+                       "clocks": lat_sampler.stop() if root else None, "trace": trace,
                        "what": "host-timed search() with host buffers, one query batch per call"}
             qbank = qbank_pin = lat_t = None
             step_e2e()   # leaves the benchmark queries' result in the pinned arrays again
@@ -641,7 +674,7 @@ def run_b200(args, w, rank, world, local_rank):
     ext = torch.cuda.ExternalStream(res.stream, device=torch.device("cuda", local_rank))
     ctx = {"fm": fm, "torch": torch, "dist": dist, "O": O, "rank": rank, "world": world, "local_rank": local_rank,
            "res": res, "ext": ext, "peaks": load_peaks()}
-    headline = not (args.nb or args.nq)
+    headline = not (args.nb or args.nq or args.storage >= 0)
     line = run_workload(ctx, args.workload, w, args.steps, args.warmup, headline, with_e2e=not args.no_e2e,
                         with_label_check=not args.no_label_check)
 
@@ -705,6 +738,8 @@ def main():
         w["nb"] = args.nb
     if args.nq:
         w["nq"] = args.nq
+    if args.storage >= 0:
+        w["storage"] = args.storage
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

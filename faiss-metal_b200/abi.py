@@ -126,6 +126,9 @@ SIGNATURES = {
     "b200f_sharded_ntotal": (c_i64, [c_vp]),
     "b200f_sharded_num_shards": (c_int, [c_vp]),
     "b200f_sharded_set_path": (c_int, [c_vp, c_int]),
+    "b200f_sharded_set_use_graphs": (c_int, [c_vp, c_int]),
+    "b200f_sharded_trace": (c_int, [c_vp, c_int]),
+    "b200f_sharded_trace_read": (c_i64, [c_vp, c_vp, c_vp, c_i64]),
 }
 
 

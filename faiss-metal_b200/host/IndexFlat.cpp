@@ -192,7 +192,9 @@ struct B200IndexFlat::Impl {
         g = SearchGraph{};
     }
     // The stored rows / label base / path changed: nothing captured so far is valid.
+    mutable uint64_t generation = 1;   // bumped with every change that makes captured work stale
     void invalidateGraphs() const {
+        generation++;
         if (graphs.empty() && seenShapes.empty()) return;
         (void)cudaStreamSynchronize(stream());
         for (auto& g : graphs) destroyGraph(g);
@@ -836,8 +838,15 @@ bool B200IndexFlat::searchFromGraph(faiss::idx_t n, const float* x, faiss::idx_t
     return true;
 }
 
+size_t B200IndexFlat::searchScratchBytes(faiss::idx_t n, faiss::idx_t k) const {
+    return align256(b200f_search_scratch_bytes(n, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath));
+}
+
+uint64_t B200IndexFlat::generation() const { return impl_->generation; }
+
 void B200IndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::idx_t k,
-                                        float* distances, faiss::idx_t* labels) const {
+                                        float* distances, faiss::idx_t* labels, void* scratch,
+                                        size_t scratchSize) const {
     checkSearchArgs(n, x, k, distances, labels, ntotal);
     if (n == 0) return;
     const int64_t batch = k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch;
@@ -846,7 +855,10 @@ void B200IndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::i
     const size_t scratchBytes =
             b200f_search_scratch_bytes(n, ntotal, d, (int)k, impl_->storageCode(), impl_->forcePath);
     B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, scratchBytes > 0, "searchDeviceEnqueue: cannot plan this shape");
-    uint8_t* region = static_cast<uint8_t*>(impl_->res->getScratch(align256(scratchBytes)));
+    if (scratch) B200_THROW_ARG_IF_NOT(B200F_ERR_SCRATCH, scratchSize >= align256(scratchBytes), "scratch too small");
+    // the caller's scratch (a captured graph must own what it touches), else the shared arena
+    uint8_t* region = scratch ? static_cast<uint8_t*>(scratch)
+                              : static_cast<uint8_t*>(impl_->res->getScratch(align256(scratchBytes)));
     B200FSearchArgs a;
     impl_->fillArgs(a, ntotal);
     a.queries = x;

@@ -7,6 +7,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -23,6 +24,9 @@ namespace {
 
 constexpr int64_t kFusedBatch = 16384;   // queries per launch, k <= B200F_LIST_MAX_K
 constexpr int64_t kSelectBatch = 1024;   // beyond: few rows, wide column chunks
+constexpr size_t kSmallQueryBytes = 64 * 1024;
+constexpr int64_t kGraphMaxQueries = 8;  // searches this small are replayed from a CUDA graph
+constexpr size_t kMaxGraphs = 8;
 
 size_t alignUp(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -147,6 +151,43 @@ struct B200ShardedIndexFlat::Impl {
     };
     std::vector<Buffers> buf;
 
+    // One process per GPU, host buffers, at most kGraphMaxQueries queries: the whole call
+    // (query upload, shard search, candidate all-gather, merge, result download) is captured
+    // into a CUDA graph the second time a shape is seen and replayed afterwards.  A graph owns
+    // every buffer it touches and is tied to the local index as it was (generation).
+    struct CallGraph {
+        int64_t n = 0, k = 0;
+        bool wantResult = false;
+        int selectMode = 0;
+        uint64_t generation = 0;
+        void* dev = nullptr;        // queries | candidates of all parts | merged result | search scratch
+        uint8_t* host = nullptr;    // pinned: queries | distances | labels
+        size_t hostDistOff = 0, hostLabOff = 0;
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        uint64_t lastUse = 0;
+    };
+    std::vector<CallGraph> graphs;
+    std::vector<std::pair<int64_t, int64_t>> seenShapes;
+    uint64_t useCounter = 0;
+    bool useGraphs = true;
+
+    // Host-side trace of the calls (off by default): microseconds from entry until everything
+    // was enqueued, and from there until the stream had drained.  A rank whose enqueue time is
+    // large was late on the host; large waits with small enqueue times on every rank point at
+    // the device or the exchange.
+    bool trace = false;
+    std::vector<float> traceEnqueueUs, traceWaitUs;
+
+    void destroyGraph(CallGraph& g) {
+        if (g.exec) (void)cudaGraphExecDestroy(g.exec);
+        if (g.graph) (void)cudaGraphDestroy(g.graph);
+        if (g.dev) res[0]->deallocBuffer(g.dev);
+        if (g.host) res[0]->releasePinnedTemp(g.host);
+        g = CallGraph{};
+    }
+    bool searchFromGraph(int64_t n, const float* x, int64_t k, float* distances, faiss::idx_t* labels);
+
     int localShards() const { return (int)shards.size(); }
     int parts() const { return ranks ? world : localShards(); }   // lists merged per query
     int partOf(int s) const { return ranks ? rank : s; }
@@ -168,6 +209,15 @@ struct B200ShardedIndexFlat::Impl {
     }
 
     void destroy() {
+        if (!graphs.empty()) {
+            try {
+                DeviceGuard g(res[0]->getDevice());
+                (void)cudaStreamSynchronize(stream(0));
+                for (auto& gr : graphs) destroyGraph(gr);
+            } catch (...) {
+            }
+            graphs.clear();
+        }
         for (size_t s = 0; s < buf.size(); s++) {
             if (!res[s]) continue;
             try {
@@ -372,6 +422,10 @@ void B200ShardedIndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k
     const int64_t batch = std::min<int64_t>(n, k <= B200F_LIST_MAX_K ? kFusedBatch : kSelectBatch);
     const int m = 0;   // merging shard
     DeviceGuard g(im.res[m]->getDevice());
+    const auto t0 = std::chrono::steady_clock::now();
+    if (im.ranks && im.useGraphs && n <= kGraphMaxQueries && !xOnDevice && !outOnDevice &&
+        im.searchFromGraph(n, x, k, distances, labels))
+        return;
     for (int64_t q0 = 0; q0 < n; q0 += batch) {
         const int64_t nq = std::min<int64_t>(batch, n - q0);
         float* dOut = nullptr;
@@ -397,8 +451,163 @@ void B200ShardedIndexFlat::search(faiss::idx_t n, const float* x, faiss::idx_t k
                       "search: device to host copy of labels");
         }
         // host buffers are the caller's again on return, and the next batch reuses the staging
+        const auto t1 = std::chrono::steady_clock::now();
         synchronize();
+        if (im.trace && im.traceEnqueueUs.size() < (size_t)1 << 20) {
+            const auto t2 = std::chrono::steady_clock::now();
+            im.traceEnqueueUs.push_back(std::chrono::duration<float, std::micro>(t1 - t0).count());
+            im.traceWaitUs.push_back(std::chrono::duration<float, std::micro>(t2 - t1).count());
+        }
     }
+}
+
+// The rank form's small search through a captured graph.  First call with a shape: ordinary
+// path (it also performs every lazy set-up of this library and of NCCL for that message size,
+// none of which belongs inside a capture); second call: capture; afterwards: one memcpy into
+// the pinned slot, one graph launch, one synchronisation, one memcpy out.  Every rank takes
+// the same decisions, because every rank sees the same sequence of (n, k); a rank whose capture
+// fails falls back to the ordinary path for good, which issues the same collective.
+bool B200ShardedIndexFlat::Impl::searchFromGraph(int64_t n, const float* x, int64_t k, float* distances,
+                                                 faiss::idx_t* labels) {
+    const auto t0 = std::chrono::steady_clock::now();
+    Impl& im = *this;
+    cudaStream_t st = im.stream(0);
+    const bool wantResult = distances != nullptr;
+    const int selectMode = b200f_get_selection_mode();
+    const uint64_t gen = im.shards[0]->generation();
+    CallGraph* g = nullptr;
+    for (size_t i = 0; i < im.graphs.size();) {
+        if (im.graphs[i].generation != gen) {   // the local index changed: stale
+            cudaCheck(cudaStreamSynchronize(st), "search: synchronize");
+            im.destroyGraph(im.graphs[i]);
+            im.graphs.erase(im.graphs.begin() + (long)i);
+            continue;
+        }
+        if (im.graphs[i].n == n && im.graphs[i].k == k && im.graphs[i].wantResult == wantResult &&
+            im.graphs[i].selectMode == selectMode)
+            g = &im.graphs[i];
+        i++;
+    }
+    if (!g) {
+        const std::pair<int64_t, int64_t> shape(n, k);
+        if (std::find(im.seenShapes.begin(), im.seenShapes.end(), shape) == im.seenShapes.end()) {
+            if (im.seenShapes.size() >= 64) im.seenShapes.clear();
+            im.seenShapes.push_back(shape);
+            return false;
+        }
+        if (im.graphs.size() >= kMaxGraphs) {
+            size_t oldest = 0;
+            for (size_t i = 1; i < im.graphs.size(); i++)
+                if (im.graphs[i].lastUse < im.graphs[oldest].lastUse) oldest = i;
+            cudaCheck(cudaStreamSynchronize(st), "search: synchronize");
+            im.destroyGraph(im.graphs[oldest]);
+            im.graphs.erase(im.graphs.begin() + (long)oldest);
+        }
+        const int P = im.parts();
+        const int d = im.d;
+        const size_t qBytes = alignUp((size_t)n * d * 4, 256);
+        const size_t distBytes = alignUp((size_t)n * k * 4, 16);
+        const size_t partBytes = alignUp(distBytes + (size_t)n * k * 8, 16);
+        const size_t candBytes = alignUp((size_t)P * partBytes, 256);
+        const size_t outDist = alignUp((size_t)n * k * 4, 256);
+        const size_t outBytes = outDist + alignUp((size_t)n * k * 8, 256);
+        const size_t scratchBytes = im.shards[0]->searchScratchBytes(n, k);
+        CallGraph e;
+        e.n = n;
+        e.k = k;
+        e.wantResult = wantResult;
+        e.selectMode = selectMode;
+        e.generation = gen;
+        e.hostDistOff = qBytes;
+        e.hostLabOff = qBytes + outDist;
+        try {
+            e.dev = im.res[0]->allocBuffer(qBytes + candBytes + outBytes + scratchBytes);
+            e.host = static_cast<uint8_t*>(im.res[0]->acquirePinnedTemp(qBytes + outBytes));
+            if (!e.host) throw B200RuntimeError(B200F_ERR_OOM, "faiss-b200: pinned allocation failed");
+            uint8_t* dev = static_cast<uint8_t*>(e.dev);
+            float* q = reinterpret_cast<float*>(dev);
+            uint8_t* cand = dev + qBytes;
+            uint8_t* mine = cand + (size_t)im.rank * partBytes;
+            float* outD = reinterpret_cast<float*>(dev + qBytes + candBytes);
+            faiss::idx_t* outL = reinterpret_cast<faiss::idx_t*>(dev + qBytes + candBytes + outDist);
+            void* scratch = dev + qBytes + candBytes + outBytes;
+            // relaxed: NCCL may make calls of its own while its collective is being captured
+            cudaCheck(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed), "search: begin capture");
+            bool ok = true;
+            try {
+                cudaCheck(cudaMemcpyAsync(q, e.host, (size_t)n * d * 4, cudaMemcpyHostToDevice, st), "capture: upload");
+                float* dLoc = reinterpret_cast<float*>(mine);
+                faiss::idx_t* lLoc = reinterpret_cast<faiss::idx_t*>(mine + distBytes);
+                if (P == 1) {
+                    dLoc = outD;
+                    lLoc = outL;
+                }
+                im.shards[0]->searchDeviceEnqueue(n, q, k, dLoc, lLoc, scratch, scratchBytes);
+                if (P > 1) {
+                    ncclCheck(NcclApi::get().AllGather(mine, cand, partBytes, ncclUint8, im.comms[0], st), "ncclAllGather");
+                    if (wantResult)
+                        abiCheck(b200f_merge_lists_strided(reinterpret_cast<const float*>(cand),
+                                                           reinterpret_cast<const int64_t*>(cand + distBytes),
+                                                           (int64_t)(partBytes / 4), (int64_t)(partBytes / 8), P, n, (int)k,
+                                                           im.l2 ? B200F_METRIC_L2 : B200F_METRIC_INNER_PRODUCT, outD,
+                                                           reinterpret_cast<int64_t*>(outL), st),
+                                 "merge lists");
+                }
+                if (wantResult) {
+                    cudaCheck(cudaMemcpyAsync(e.host + e.hostDistOff, outD, (size_t)n * k * 4, cudaMemcpyDeviceToHost, st),
+                              "capture: download");
+                    cudaCheck(cudaMemcpyAsync(e.host + e.hostLabOff, outL, (size_t)n * k * 8, cudaMemcpyDeviceToHost, st),
+                              "capture: download");
+                }
+            } catch (...) {
+                ok = false;
+            }
+            const cudaError_t ee = cudaStreamEndCapture(st, &e.graph);   // always ends the capture
+            if (!ok || ee != cudaSuccess || !e.graph || cudaGraphInstantiate(&e.exec, e.graph, 0) != cudaSuccess) {
+                (void)cudaGetLastError();
+                im.destroyGraph(e);
+                im.useGraphs = false;   // cannot capture here: the ordinary path from now on
+                return false;
+            }
+        } catch (...) {
+            im.destroyGraph(e);
+            throw;
+        }
+        im.graphs.push_back(e);
+        g = &im.graphs.back();
+    }
+    g->lastUse = ++im.useCounter;
+    std::memcpy(g->host, x, (size_t)n * im.d * 4);
+    cudaCheck(cudaGraphLaunch(g->exec, st), "search: graph launch");
+    const auto t1 = std::chrono::steady_clock::now();
+    im.shards[0]->synchronize();   // waits, and reports the search's device status word
+    if (wantResult) {
+        std::memcpy(distances, g->host + g->hostDistOff, (size_t)n * k * 4);
+        std::memcpy(labels, g->host + g->hostLabOff, (size_t)n * k * 8);
+    }
+    if (im.trace && im.traceEnqueueUs.size() < (size_t)1 << 20) {
+        const auto t2 = std::chrono::steady_clock::now();
+        im.traceEnqueueUs.push_back(std::chrono::duration<float, std::micro>(t1 - t0).count());
+        im.traceWaitUs.push_back(std::chrono::duration<float, std::micro>(t2 - t1).count());
+    }
+    return true;
+}
+
+void B200ShardedIndexFlat::setUseGraphs(bool on) { impl_->useGraphs = on; }
+
+void B200ShardedIndexFlat::setTrace(bool on) {
+    impl_->trace = on;
+    impl_->traceEnqueueUs.clear();
+    impl_->traceWaitUs.clear();
+}
+
+size_t B200ShardedIndexFlat::readTrace(float* enqueueUs, float* waitUs, size_t capacity) const {
+    const size_t n = std::min(capacity, impl_->traceEnqueueUs.size());
+    for (size_t i = 0; i < n; i++) {
+        if (enqueueUs) enqueueUs[i] = impl_->traceEnqueueUs[i];
+        if (waitUs) waitUs[i] = impl_->traceWaitUs[i];
+    }
+    return impl_->traceEnqueueUs.size();
 }
 
 void B200ShardedIndexFlat::searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::idx_t k, float* distances,
@@ -435,7 +644,10 @@ void B200ShardedIndexFlat::Impl::enqueueBatch(int64_t nq, const float* x, bool x
     const size_t sliceBytes = alignUp((size_t)slice * d * 4, 16);
     const size_t distBytes = alignUp((size_t)nq * k * 4, 16);
     const size_t partBytes = alignUp(distBytes + (size_t)nq * k * 8, 16);   // [distances | labels] of one part
-    const bool exchangeQueries = !xOnDevice && P > 1;
+    // Host queries are normally uploaded in slices and all-gathered; a query block this small is
+    // cheaper to upload whole on every GPU (one 5 us copy each) than to all-gather (a collective
+    // launch on the critical path of a single-query search).
+    const bool exchangeQueries = !xOnDevice && P > 1 && (size_t)nq * d * 4 > kSmallQueryBytes;
 
     // 1. queries: every GPU needs all of them.  From host memory each part's GPU takes one
     //    slice over PCIe and the slices are all-gathered over NVLink; device queries are

@@ -399,6 +399,23 @@ int b200f_sharded_reconstruct(const B200FSharded* index, int64_t key, float* rec
 int64_t b200f_sharded_ntotal(const B200FSharded* index) { return index ? index->index->ntotal : -1; }
 int b200f_sharded_num_shards(const B200FSharded* index) { return index ? index->index->numShards() : -1; }
 
+int b200f_sharded_set_use_graphs(B200FSharded* index, int on) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    index->index->setUseGraphs(on != 0);
+    return B200F_OK;
+}
+
+int b200f_sharded_trace(B200FSharded* index, int on) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    index->index->setTrace(on != 0);
+    return B200F_OK;
+}
+
+int64_t b200f_sharded_trace_read(const B200FSharded* index, float* enqueue_us, float* wait_us, int64_t capacity) {
+    if (!index || capacity < 0) return -1;
+    return (int64_t)index->index->readTrace(enqueue_us, wait_us, (size_t)capacity);
+}
+
 int b200f_sharded_set_path(B200FSharded* index, int path) {
     if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
     B200F_GUARD_BEGIN

@@ -102,8 +102,14 @@ class B200IndexFlat : public faiss::Index {
     /// stream and return without synchronising (single batch: n <= 16384 for k <= 32,
     /// n <= 1024 otherwise).  The multi-GPU layer chains the candidate exchange and the merge
     /// behind it on the same stream; call synchronize() before reading results on the host.
+    /// `scratch` (device, searchScratchBytes(n, k) bytes): used instead of the resources' shared
+    /// scratch arena, for callers that capture the call into a CUDA graph of their own.
     void searchDeviceEnqueue(faiss::idx_t n, const float* x, faiss::idx_t k, float* distances,
-                             faiss::idx_t* labels) const;
+                             faiss::idx_t* labels, void* scratch = nullptr, size_t scratchSize = 0) const;
+    size_t searchScratchBytes(faiss::idx_t n, faiss::idx_t k) const;
+    /// Changes whenever stored rows, label base or forced path change: work captured against an
+    /// older value must not be replayed.
+    uint64_t generation() const;
     /// Wait for the resources' stream and throw if a search reported a device-side error.
     void synchronize() const;
     /// Device status word of the most recent synchronous search (0 = fine).

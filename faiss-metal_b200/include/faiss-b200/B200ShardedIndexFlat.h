@@ -67,6 +67,13 @@ class B200ShardedIndexFlat : public faiss::Index {
     int world() const;   ///< one process per GPU: ranks in the group; else 1
     const B200IndexFlat* shard(int i) const;
     void setForcePath(int path);
+    /// One process per GPU: searches of at most 8 queries with host buffers are replayed from a
+    /// CUDA graph that holds the whole call, exchange included (default on).
+    void setUseGraphs(bool on);
+    /// Host-side trace of search() calls: per call, microseconds until everything was enqueued
+    /// and microseconds waiting for the device after that.  setTrace clears the record.
+    void setTrace(bool on);
+    size_t readTrace(float* enqueueUs, float* waitUs, size_t capacity) const;   ///< returns the number recorded
 
    private:
     struct Impl;

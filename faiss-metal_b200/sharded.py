@@ -101,6 +101,22 @@ class _ShardedHandle:
     def set_path(self, path: int):
         abi.check(abi.lib().b200f_sharded_set_path(self._h, int(path)), "sharded set_path")
 
+    def set_use_graphs(self, on: bool):
+        abi.check(abi.lib().b200f_sharded_set_use_graphs(self._h, 1 if on else 0), "sharded set_use_graphs")
+
+    def trace(self, on: bool):
+        """Start (and clear) or stop the host-side trace of search() calls."""
+        abi.check(abi.lib().b200f_sharded_trace(self._h, 1 if on else 0), "sharded trace")
+
+    def read_trace(self):
+        """(enqueue_us, wait_us) float32 arrays, one entry per traced search() call."""
+        n = abi.lib().b200f_sharded_trace_read(self._h, None, None, 0)
+        enq = np.empty(max(n, 0), dtype=np.float32)
+        wait = np.empty(max(n, 0), dtype=np.float32)
+        if n > 0:
+            abi.lib().b200f_sharded_trace_read(self._h, _ptr(enq), _ptr(wait), n)
+        return enq, wait
+
     def close(self):
         if getattr(self, "_h", None):
             abi.lib().b200f_sharded_destroy(self._h)

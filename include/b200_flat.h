@@ -424,6 +424,16 @@ int b200f_sharded_reconstruct(const B200FSharded* index, int64_t key, float* rec
 int64_t b200f_sharded_ntotal(const B200FSharded* index);   /* one process per GPU: this rank's rows */
 int b200f_sharded_num_shards(const B200FSharded* index);
 int b200f_sharded_set_path(B200FSharded* index, int path);
+/* One process per GPU: searches of at most 8 queries with host buffers are replayed from a
+ * CUDA graph holding the whole call (upload, shard search, ncclAllGather, merge, download);
+ * on = 0 switches that off. */
+int b200f_sharded_set_use_graphs(B200FSharded* index, int on);
+/* Host-side trace of b200f_sharded_search calls (off by default; switching it on or off
+ * clears the record): per call the microseconds from entry until everything was enqueued and
+ * the microseconds spent waiting for the device after that.  trace_read copies up to
+ * `capacity` entries and returns the number recorded (-1 on bad arguments). */
+int b200f_sharded_trace(B200FSharded* index, int on);
+int64_t b200f_sharded_trace_read(const B200FSharded* index, float* enqueue_us, float* wait_us, int64_t capacity);
 
 #ifdef __cplusplus
 }

@@ -156,19 +156,32 @@ def _rank_worker(rank, world, port, out_dir):
             idx.add(xb[lo:hi])
             idx.set_label_base(lo)
             sh = fm.ShardedIndexFlat(idx, rank, world)
-            for n_queries in (nq, 1):
-                q = xq[:n_queries]
-                D, I = sh.search(q, k, want_result=(rank == 0))          # host queries: slices + all-gather
+            full = None
+            if rank == 0:
+                full = fm.B200IndexFlat(res, d, metric, storage)
+                full.set_use_graphs(False)
+                full.add(xb)
+            # a batch, then single queries: the second single query captures the whole call
+            # (exchange included) into a graph, the following ones replay it
+            for first, n_queries in ((0, nq), (0, 1), (1, 1), (2, 1), (3, 1), (0, 3), (3, 3), (6, 3)):
+                q = xq[first:first + n_queries]
+                D, I = sh.search(q, k, want_result=(rank == 0))          # host queries
                 Dd, Id = sh.search_device(torch.from_numpy(q).cuda(), k)  # device queries, every rank merges
                 if rank == 0:
-                    full = fm.B200IndexFlat(res, d, metric, storage)
-                    full.add(xb)
                     Df, If = full.search(q, k)
-                    full.close()
                     assert_same(D, I, Df, If)
                     assert_same(Dd.cpu().numpy(), Id.cpu().numpy(), Df, If)
                 else:
                     assert D is None and I is None
+            enq, wait = sh.read_trace()
+            assert enq.size == 0                       # tracing is off unless asked for
+            sh.trace(True)
+            sh.search(xq[:1], k, want_result=(rank == 0))
+            enq, wait = sh.read_trace()
+            assert enq.size == 1 and enq[0] > 0 and wait[0] >= 0
+            sh.trace(False)
+            if full is not None:
+                full.close()
             sh.close()
             idx.close()
         res.close()
