@@ -135,6 +135,8 @@ def parse_args():
     ap.add_argument("--nb", type=int, default=0, help="override database rows (not the headline config)")
     ap.add_argument("--nq", type=int, default=0, help="override queries per step (not the headline config)")
     ap.add_argument("--storage", type=int, default=-1, help="override the storage type 0/1/2 (not the headline config)")
+    ap.add_argument("--ingest", type=float, default=0.0, metavar="GIB",
+                    help="only time add() of this many GiB of host rows against a plain pinned copy")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-label-check", action="store_true", help="skip the full-shard oracle label check")
@@ -660,6 +662,48 @@ def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_labe
     }
 
 
+def run_ingest(ctx, w, gib=4.0):
+    """Host -> index throughput of add() (the ingest pipeline: pinned or pageable host rows, 32 MiB
+    chunks, upload overlapped with the conversion kernel) against a plain pinned cudaMemcpyAsync
+    of the same bytes.  Rows are fp32 on the host, as a caller of add() has them."""
+    import numpy as np
+    fm, torch, res, ext = ctx["fm"], ctx["torch"], ctx["res"], ctx["ext"]
+    d = w["d"]
+    n = int(gib * (1 << 30) / (d * 4))
+    nbytes = n * d * 4
+    out = {"rows": n, "bytes": nbytes, "storage": DTYPE_NAME[w["storage"]].split(" ")[0]}
+    with torch.cuda.stream(ext):
+        pinned = torch.empty((n, d), dtype=torch.float32, pin_memory=True)
+        pinned.normal_(0.0, 0.05)
+        dev = torch.empty((n, d), dtype=torch.float32, device="cuda")
+        # the yardstick: one asynchronous copy from pinned memory
+        best = 1e9
+        for _ in range(3):
+            ext.synchronize()
+            t0 = time.perf_counter()
+            dev.copy_(pinned, non_blocking=True)
+            ext.synchronize()
+            best = min(best, time.perf_counter() - t0)
+        out["pinned_memcpy_gbs"] = nbytes / best / 1e9
+        del dev
+        pageable = pinned.numpy().copy()
+        for name, src in (("pinned", pinned.numpy()), ("pageable", pageable)):
+            best = 1e9
+            for _ in range(2):
+                idx = fm.B200IndexFlat(res, d, w["metric"], w["storage"])
+                idx.reserve(n)
+                ext.synchronize()
+                t0 = time.perf_counter()
+                idx.add(src)
+                best = min(best, time.perf_counter() - t0)
+                idx.close()
+            out["add_from_%s_gbs" % name] = nbytes / best / 1e9
+            out["add_from_%s_vs_memcpy" % name] = out["add_from_%s_gbs" % name] / out["pinned_memcpy_gbs"]
+        del pinned, pageable
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_b200(args, w, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -675,6 +719,11 @@ def run_b200(args, w, rank, world, local_rank):
     ctx = {"fm": fm, "torch": torch, "dist": dist, "O": O, "rank": rank, "world": world, "local_rank": local_rank,
            "res": res, "ext": ext, "peaks": load_peaks()}
     headline = not (args.nb or args.nq or args.storage >= 0)
+    if args.ingest:
+        if rank == 0:
+            emit({"ingest": run_ingest(ctx, w, args.ingest), "config": {"workload": args.workload, "d": w["d"]}})
+        res.close()
+        return
     line = run_workload(ctx, args.workload, w, args.steps, args.warmup, headline, with_e2e=not args.no_e2e,
                         with_label_check=not args.no_label_check)
 
@@ -690,6 +739,11 @@ def run_b200(args, w, rank, world, local_rank):
                 extras[name] = {"error": "%s: %s" % (type(e).__name__, e)}
                 if world > 1:
                     raise
+        if world == 1:
+            try:
+                extras["ingest"] = run_ingest(ctx, w)
+            except Exception as e:
+                extras["ingest"] = {"error": "%s: %s" % (type(e).__name__, e)}
 
     def teardown():
         torch.cuda.synchronize()

@@ -93,7 +93,7 @@ bool isDevicePointer(const void* p) { return pointerKind(p) == PtrKind::Device; 
 void hostCopy(void* dst, const void* src, size_t bytes) {
     constexpr size_t kPerThread = 4ull << 20;
     const unsigned hw = std::thread::hardware_concurrency();
-    size_t nthreads = std::min<size_t>({bytes / kPerThread, (size_t)4, (size_t)(hw > 1 ? hw - 1 : 1)});
+    size_t nthreads = std::min<size_t>({bytes / kPerThread, (size_t)8, (size_t)(hw > 1 ? hw - 1 : 1)});
     if (nthreads <= 1) {
         std::memcpy(dst, src, bytes);
         return;
