@@ -7,6 +7,7 @@ import os
 METRIC_INNER_PRODUCT, METRIC_L2 = 0, 1
 STORAGE_F32, STORAGE_F16, STORAGE_BF16 = 0, 1, 2
 PATH_AUTO, PATH_SCAN, PATH_TENSOR = 0, 1, 2
+PLANES_BF16X3, PLANES_FP16X2 = 0, 1
 MAX_K = 4096
 FUSED_MAX_K = 32
 SELECT_AUTO, SELECT_FILTER, SELECT_NO_FILTER, SELECT_MATRIX = 0, 1, 2, 3
@@ -49,7 +50,7 @@ class SearchArgs(ctypes.Structure):
         ("norms", c_vp), ("nb", c_i64), ("metric", c_i32), ("k", c_i32),
         ("label_base", c_i64), ("out_dist", c_vp), ("out_labels", c_vp),
         ("scratch", c_vp), ("scratch_bytes", c_sz), ("status", c_vp), ("stream", c_vp),
-        ("path", c_i32), ("norm_cols", c_i32),
+        ("path", c_i32), ("norm_cols", c_i32), ("plane_format", c_i32), ("plane_scale_log2", c_i32),
     ]
 
 
@@ -66,6 +67,9 @@ SIGNATURES = {
     "b200f_device_caps": (c_int, [c_int, ctypes.POINTER(Caps)]),
     "b200f_row_norms": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_vp]),
     "b200f_store_rows": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_i64, c_vp, c_i64, c_i64, c_vp, c_int, c_vp]),
+    "b200f_store_rows_fp32": (c_int, [c_vp, c_i64, c_i64, c_int, c_vp, c_i64, c_vp, c_i64, c_i64, c_int, c_int, c_vp, c_vp,
+                                      c_int, c_vp]),
+    "b200f_rows_absmax": (c_int, [c_vp, c_i64, c_int, c_i64, c_vp, c_vp]),
     "b200f_load_rows": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_vp, c_vp]),
     "b200f_search_scratch_bytes": (c_sz, [c_i64, c_i64, c_int, c_int, c_int, c_int]),
     "b200f_search": (c_int, [ctypes.POINTER(SearchArgs)]),
@@ -110,6 +114,8 @@ SIGNATURES = {
     "b200f_index_set_label_base": (c_int, [c_vp, c_i64]),
     "b200f_index_set_growth_mode": (c_int, [c_vp, c_int]),
     "b200f_index_set_use_graphs": (c_int, [c_vp, c_int]),
+    "b200f_index_set_fp32_planes": (c_int, [c_vp, c_int]),
+    "b200f_index_fp32_planes": (c_int, [c_vp]),
     "b200f_index_device_rows": (c_vp, [c_vp]),
     "b200f_index_last_device_status": (c_int, [c_vp]),
     "b200f_index_debug_wait_expiry": (c_int, [c_vp, c_i64]),

@@ -57,9 +57,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Launchers implemented in the other translation units ------------------------
 
 // rows.cu: queries fp32 [nq][d] -> A planes (16-bit, [npl][nq][d_pad]) + squared norms.
+// FP32 storage, plane_format B200F_PLANES_FP16X2: two fp16 planes of the row scaled by its own
+// power of two, and rowscale[r] = 1 / (row scale * 2^x_scale_log2) (what turns the kernel's
+// accumulator back into key units).  Otherwise rowscale is not written.
 int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,
                            int64_t a_pitch, int64_t a_plane_stride, float* qnorm, int norm_cols,
-                           cudaStream_t stream);
+                           int plane_format, int x_scale_log2, float* rowscale, cudaStream_t stream);
 
 // scan.cu: streaming search for small nq, k <= 32.  Writes P = *out_P partial lists.
 struct ScanPlan {
@@ -91,8 +94,10 @@ struct GemmOperands {
     int64_t a_pitch, a_plane_stride;
     const uint16_t* b_planes;  // [npl][nb][b_pitch]
     int64_t b_pitch, b_plane_stride;
-    int npl;                   // 1 (fp16 / bf16 storage) or 3 (fp32 storage split)
+    int npl;                   // 1 (fp16 / bf16 storage), 3 (fp32 storage, bf16 split) or 2 (fp16 split)
     int is_bf16;               // element format of both operands
+    const float* rowscale;     // optional, per query row: keys are the accumulator times kscale * rowscale[row]
+    const int32_t* rowscale_map;  // optional: row j of A is row rowscale_map[j] of rowscale (redone rows)
     int64_t nq, nb;
     int d_pad;                 // K extent (multiple of 8), norm columns included
     const int* nq_dev;         // optional: live rows of A (<= nq) left in device memory by a kernel

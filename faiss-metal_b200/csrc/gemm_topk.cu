@@ -119,6 +119,10 @@ struct GemmParams {
     int mode;
     int k;
     float kscale;        // key = -kscale * t  (2 for L2, 1 for inner product)
+    // optional per-row factor on kscale (operands scaled per query row: fp16x2 planes); row j of
+    // this launch is row rowscale_map[j] of the array when the map is set (redone rows)
+    const float* rowscale;
+    const int32_t* rowscale_map;
     float sign;
     const float* rowadd; // per query row, may be null (0)
     float* part_key;
@@ -594,6 +598,8 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const bool row_live = grow < nq_live;
             // slot of the row's bound array this list publishes to
             uint32_t* const gslot = p.gthr ? p.gthr + grow * p.gslots + (int)((2 * xr + eh) % p.gslots) : nullptr;
+            float ksc = p.kscale;          // this row's key scale
+            if (p.rowscale && row_live) ksc *= __ldg(p.rowscale + (p.rowscale_map ? (int64_t)__ldg(p.rowscale_map + grow) : grow));
             float thr = CUDART_INF_F;      // worst key of this thread's list (k-th best of the range)
             float thr_eff = CUDART_INF_F;  // filter: min(thr, bound shared by all ranges of the row)
             float thr_pub = CUDART_INF_F;  // last value published to gthr
@@ -609,7 +615,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // (+INF, the threshold of a row whose sample was too small, stays; -INF passes nothing)
                 thr_eff = -CUDART_INF_F;
                 if (row_live) {
-                    const float t = p.fthr[grow * p.fthr_stride + p.fthr_pos] / p.kscale;
+                    const float t = p.fthr[grow * p.fthr_stride + p.fthr_pos] / ksc;
                     const uint32_t o = float_to_ordered(t);
                     thr_eff = (o >= 0xff800000u) ? t : ordered_to_float(o + 1u);
                 }
@@ -698,7 +704,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                             else
                                                 drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
                                                                 p.cand_idx + grow * p.cand_cap, p.cand_cap,
-                                                                p.kscale, stage_key, stage_idx, nstaged);
+                                                                ksc, stage_key, stage_idx, nstaged);
                                             nstaged = 0;
                                         }
                                         stage_key[nstaged * STAGE_LD] = -__uint_as_float(bits);
@@ -733,7 +739,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         float* tbuf = reinterpret_cast<float*>(smem + SM_LKEY) + (warp - 2) * (32 * 33);
 #pragma unroll
                         for (int c = 0; c < 32; c++) {
-                            const float key = -p.kscale * __uint_as_float(r[c]);
+                            const float key = -ksc * __uint_as_float(r[c]);
                             tbuf[lane * 33 + c] = fmaf(p.sign, key, radd);
                         }
                         __syncwarp();
@@ -761,7 +767,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         drain_to_list(lk, li, stage_key, stage_idx, nstaged, thr, thr_eff);
                     else
                         drain_to_buffer(p.cand_cnt + grow, p.cand_key + grow * p.cand_cap,
-                                        p.cand_idx + grow * p.cand_cap, p.cand_cap, p.kscale, stage_key,
+                                        p.cand_idx + grow * p.cand_cap, p.cand_cap, ksc, stage_key,
                                         stage_idx, nstaged);
                     nstaged = 0;
                 }
@@ -781,7 +787,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                 for (int j = 0; j < KMAX; j++) {
                     if (j >= KMAX - k) {
-                        okey[j] = p.kscale * lk[j];  // INF stays INF for empty slots
+                        okey[j] = ksc * lk[j];  // INF stays INF for empty slots
                         oidx[j] = li[j];
                     }
                 }
@@ -872,10 +878,17 @@ int launch_common(const GemmOperands& op, const GemmPlan& plan, GemmParams& p, i
     p.P = plan.P;
     p.kb_per_pass = (int)ceil_div64(op.d_pad, BK);
     p.k_extent = op.d_pad;
+    p.rowscale = op.rowscale;
+    p.rowscale_map = op.rowscale_map;
     if (op.npl == 1) {
         p.npass = 1;
         p.pass_a = 0;
         p.pass_b = 0;
+    } else if (op.npl == 2) {
+        // two fp16 planes (22 bits): (1,0) (0,1) (0,0), smallest first; (1,1) is below 2^-22
+        p.npass = 3;
+        p.pass_a = 0x001u;
+        p.pass_b = 0x010u;
     } else {
         // smallest products first: (1,1) (0,2) (2,0) (0,1) (1,0) (0,0)
         p.npass = 6;

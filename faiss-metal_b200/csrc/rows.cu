@@ -7,6 +7,8 @@
 // (src/MetalIndexFlat.mm:224-255).  One warp owns one row; lanes read 128-bit
 // vectors and reduce with shuffles.  Squares are formed in fp32 (the reference's
 // "f16" norm kernels square in half precision, which is not reproduced).
+#include <cmath>
+
 #include "common.cuh"
 
 namespace b200f {
@@ -141,26 +143,60 @@ __device__ __forceinline__ void norm_pieces(float v, int storage, uint16_t (&out
 // One warp per row.  Writes the stored row (pad columns zeroed), the squared norm of
 // the stored values, for fp32 storage the three bf16 split planes, and (norm_cols) the
 // 8 norm columns after the d8 = round_up(d, 8) data columns of the 16-bit row / plane 0.
+// FP32 storage keeps, beside the fp32 rows, split planes for the tensor path, in one of two formats:
+//   kPlanesBf16x3  x = b0 + b1 + b2, three bf16 planes (24 bits, fp32's exponent range): six plane
+//                  products reproduce the fp32 product to 2^-24
+//   kPlanesFp16x2  x * s = h0 + h1, two fp16 planes (22 bits) of the row scaled by a power of two s
+//                  chosen for the index (largest element near 2^6): three plane products, half
+//                  the tensor work and two thirds of the plane bytes.  fp16 has a narrow exponent
+//                  range, so the format only holds while every stored row fits it: an element
+//                  at or beyond 2^15 after scaling, or a row whose largest element falls below
+//                  2^-4 (1/1024 of the scale target: its low plane would go subnormal and lose
+//                  bits), raises `range_flag`, and the index re-splits itself into bf16x3.
+constexpr int kPlanesBf16x3 = 0;
+constexpr int kPlanesFp16x2 = 1;
+
 template <int STORAGE>
-__global__ void store_rows_kernel(const float* __restrict__ src, int64_t n, int d,
+__global__ void store_rows_kernel(const float* __restrict__ src, int64_t src_pitch, int64_t n, int d,
                                   void* __restrict__ dst, int64_t dst_pitch,
                                   uint16_t* __restrict__ planes, int64_t plane_pitch,
-                                  int64_t plane_stride, float* __restrict__ norms, int norm_cols) {
+                                  int64_t plane_stride, int plane_format, float plane_scale,
+                                  int32_t* __restrict__ range_flag, float* __restrict__ norms, int norm_cols) {
     const int lane = threadIdx.x & 31;
     const int d8 = (d + 7) & ~7;
     const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
          r += warps_total) {
-        const float* row = src + r * (int64_t)d;
+        const float* row = src + r * src_pitch;
         float s = 0.f;
         if (STORAGE == B200F_STORAGE_F32) {
             float* out = reinterpret_cast<float*>(dst) + r * dst_pitch;
-            for (int j = lane; j < dst_pitch; j += 32) {
-                float v = (j < d) ? row[j] : 0.f;
-                out[j] = v;
-                s = fmaf(v, v, s);
+            if (out != row) {   // a re-split reads the stored rows themselves
+                for (int j = lane; j < dst_pitch; j += 32) {
+                    float v = (j < d) ? row[j] : 0.f;
+                    out[j] = v;
+                    s = fmaf(v, v, s);
+                }
+            } else {
+                for (int j = lane; j < d; j += 32) s = fmaf(row[j], row[j], s);
             }
-            if (planes) {
+            if (planes && plane_format == kPlanesFp16x2) {
+                uint16_t* p0 = planes + r * plane_pitch;
+                uint16_t* p1 = p0 + plane_stride;
+                float amax = 0.f;
+                for (int j = lane; j < plane_pitch; j += 32) {
+                    const float v = (j < d) ? row[j] * plane_scale : 0.f;
+                    amax = fmaxf(amax, fabsf(v));
+                    const uint16_t h0 = float_to_fp16_bits(v);
+                    const float r1 = v - fp16_bits_to_float(h0);   // exact in fp32
+                    p0[j] = h0;
+                    p1[j] = float_to_fp16_bits(r1);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if (lane == 0 && range_flag && (amax >= 32768.f || (amax > 0.f && amax < 0.0625f)))
+                    atomicOr(range_flag, 1);
+            } else if (planes) {
                 uint16_t* p0 = planes + r * plane_pitch;
                 uint16_t* p1 = p0 + plane_stride;
                 uint16_t* p2 = p1 + plane_stride;
@@ -199,7 +235,11 @@ __global__ void store_rows_kernel(const float* __restrict__ src, int64_t n, int 
             __syncwarp();
             if (lane == 0) {
                 uint16_t pc[8];
-                norm_pieces(-0.5f * s, STORAGE == B200F_STORAGE_F32 ? B200F_STORAGE_BF16 : STORAGE, pc);
+                if (STORAGE == B200F_STORAGE_F32 && plane_format == kPlanesFp16x2)
+                    // in the scaled units of the planes: (s x).(s x) / 2, fp16 pieces
+                    norm_pieces(-0.5f * s * plane_scale * plane_scale, B200F_STORAGE_F16, pc);
+                else
+                    norm_pieces(-0.5f * s, STORAGE == B200F_STORAGE_F32 ? B200F_STORAGE_BF16 : STORAGE, pc);
                 uint16_t* o = (STORAGE == B200F_STORAGE_F32)
                                       ? (planes ? planes + r * plane_pitch + d8 : nullptr)
                                       : reinterpret_cast<uint16_t*>(dst) + r * dst_pitch + d8;
@@ -210,6 +250,25 @@ __global__ void store_rows_kernel(const float* __restrict__ src, int64_t n, int 
             }
         }
     }
+}
+
+// Largest |element| of a block of fp32 rows (as the bit pattern of a non-negative float, which
+// orders like an unsigned integer): what the index derives the fp16x2 plane scale from.
+__global__ void rows_absmax_kernel(const float* __restrict__ src, int64_t pitch, int64_t n, int d,
+                                   uint32_t* __restrict__ out_max_bits) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    float amax = 0.f;
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n; r += warps_total) {
+        const float* row = src + r * pitch;
+        for (int j = lane; j < d; j += 32) {
+            const float v = fabsf(row[j]);
+            if (v < CUDART_INF_F) amax = fmaxf(amax, v);   // NaN and INF do not set the scale
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0 && amax > 0.f) atomicMax(out_max_bits, __float_as_uint(amax));
 }
 
 template <int STORAGE>
@@ -231,14 +290,39 @@ __global__ void load_rows_kernel(const void* __restrict__ rows, int64_t n, int d
 __global__ void prepare_queries_kernel(const float* __restrict__ q, int64_t nq, int d, int storage,
                                        uint16_t* __restrict__ a, int64_t a_pitch,
                                        int64_t a_plane_stride, float* __restrict__ qnorm,
-                                       int norm_cols) {
+                                       int norm_cols, int plane_format, int x_scale_log2,
+                                       float* __restrict__ rowscale) {
     const int lane = threadIdx.x & 31;
     const int d8 = (d + 7) & ~7;
     const int fmt = storage == B200F_STORAGE_F16 ? B200F_STORAGE_F16 : B200F_STORAGE_BF16;
+    const bool fp16x2 = storage == B200F_STORAGE_F32 && plane_format == kPlanesFp16x2;
     const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nq;
          r += warps_total) {
         const float* row = q + r * (int64_t)d;
+        // fp16x2 planes: every query row gets its own power-of-two scale (largest element near
+        // 2^6, as the stored rows), kept at most 2^3 above the rows' scale so that the norm-column
+        // scales below stay inside fp16.  The kernel's accumulator is then (sq * sx) * t, and
+        // rowscale[r] = 1 / (sq * sx) brings a key back to its units.
+        float sq = 1.f, ratio = 1.f;
+        if (fp16x2 && a) {
+            float amax = 0.f;
+            for (int j = lane; j < d; j += 32) {
+                const float v = fabsf(row[j]);
+                if (v < CUDART_INF_F) amax = fmaxf(amax, v);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            int e = 0;
+            if (amax > 0.f) (void)frexpf(amax, &e);   // amax = m * 2^e, m in [0.5, 1)
+            int lq = amax > 0.f ? 7 - e : x_scale_log2;
+            if (lq > x_scale_log2 + 3) lq = x_scale_log2 + 3;
+            if (lq > 126) lq = 126;
+            if (lq < -126) lq = -126;
+            sq = ldexpf(1.f, lq);
+            ratio = ldexpf(1.f, lq - x_scale_log2);            // sq / sx
+            if (rowscale && lane == 0) rowscale[r] = ldexpf(1.f, -(lq + x_scale_log2));
+        }
         float s = 0.f;
         for (int j = lane; j < a_pitch || j < d; j += 32) {
             float v = (j < d) ? row[j] : 0.f;
@@ -246,6 +330,14 @@ __global__ void prepare_queries_kernel(const float* __restrict__ q, int64_t nq, 
             if (a && j < a_pitch) {
                 uint16_t* p0 = a + r * a_pitch + j;
                 const bool ncol = norm_cols && j >= d8 && j < d8 + 8;
+                if (fp16x2) {
+                    // norm columns: the stored side holds (sx x).(sx x) / 2 in fp16 pieces
+                    const float w = ncol ? norm_scale(B200F_STORAGE_F16, j - d8) * ratio : v * sq;
+                    const uint16_t h0 = float_to_fp16_bits(w);
+                    p0[0] = h0;
+                    p0[a_plane_stride] = ncol ? (uint16_t)0 : float_to_fp16_bits(w - fp16_bits_to_float(h0));
+                    continue;
+                }
                 if (ncol) v = norm_scale(fmt, j - d8);
                 if (storage == B200F_STORAGE_F16) {
                     *p0 = float_to_fp16_bits(v);
@@ -353,10 +445,11 @@ int cached_sm_count() {
 
 int launch_prepare_queries(const float* q, int64_t nq, int d, int storage, uint16_t* a_planes,
                            int64_t a_pitch, int64_t a_plane_stride, float* qnorm, int norm_cols,
-                           cudaStream_t stream) {
+                           int plane_format, int x_scale_log2, float* rowscale, cudaStream_t stream) {
     if (nq <= 0) return B200F_OK;
     prepare_queries_kernel<<<grid_for_rows(nq), ROW_THREADS, 0, stream>>>(
-            q, nq, d, storage, a_planes, a_pitch, a_plane_stride, qnorm, norm_cols);
+            q, nq, d, storage, a_planes, a_pitch, a_plane_stride, qnorm, norm_cols, plane_format, x_scale_log2,
+            rowscale);
     count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
@@ -390,12 +483,15 @@ extern "C" int b200f_row_norms(const void* rows, int storage, int64_t n, int d, 
     return B200F_OK;
 }
 
-extern "C" int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
-                                int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
-                                int64_t plane_stride, float* norms_or_null, int norm_cols,
-                                void* stream) {
-    if (n < 0 || d <= 0 || dst_pitch < d || (n > 0 && (!src || !dst_rows))) return B200F_ERR_BAD_ARG;
+namespace {
+int store_rows_impl(const float* src, int64_t src_pitch, int64_t n, int d, int storage, void* dst_rows,
+                    int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch, int64_t plane_stride,
+                    int plane_format, int plane_scale_log2, int32_t* range_flag, float* norms_or_null,
+                    int norm_cols, void* stream) {
+    if (n < 0 || d <= 0 || dst_pitch < d || src_pitch < d || (n > 0 && (!src || !dst_rows))) return B200F_ERR_BAD_ARG;
     if (planes && (plane_pitch < d || plane_stride < plane_pitch)) return B200F_ERR_BAD_ARG;
+    if (plane_format != B200F_PLANES_BF16X3 && plane_format != B200F_PLANES_FP16X2) return B200F_ERR_BAD_ARG;
+    if (plane_scale_log2 < -126 || plane_scale_log2 > 126) return B200F_ERR_BAD_ARG;
     if (norm_cols) {
         const int64_t need = ((d + 7) & ~7) + 8;
         if (storage == B200F_STORAGE_F32 ? (planes && plane_pitch < need) : dst_pitch < need)
@@ -404,22 +500,53 @@ extern "C" int b200f_store_rows(const float* src, int64_t n, int d, int storage,
     if (n == 0) return B200F_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int g = grid_for_rows(n);
+    const float scale = std::ldexp(1.f, plane_scale_log2);
     switch (storage) {
         case B200F_STORAGE_F32:
             store_rows_kernel<B200F_STORAGE_F32><<<g, ROW_THREADS, 0, st>>>(
-                    src, n, d, dst_rows, dst_pitch, planes, plane_pitch, plane_stride, norms_or_null, norm_cols);
+                    src, src_pitch, n, d, dst_rows, dst_pitch, planes, plane_pitch, plane_stride, plane_format, scale,
+                    range_flag, norms_or_null, norm_cols);
             break;
         case B200F_STORAGE_F16:
             store_rows_kernel<B200F_STORAGE_F16><<<g, ROW_THREADS, 0, st>>>(
-                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null, norm_cols);
+                    src, src_pitch, n, d, dst_rows, dst_pitch, nullptr, 0, 0, 0, 1.f, nullptr, norms_or_null, norm_cols);
             break;
         case B200F_STORAGE_BF16:
             store_rows_kernel<B200F_STORAGE_BF16><<<g, ROW_THREADS, 0, st>>>(
-                    src, n, d, dst_rows, dst_pitch, nullptr, 0, 0, norms_or_null, norm_cols);
+                    src, src_pitch, n, d, dst_rows, dst_pitch, nullptr, 0, 0, 0, 1.f, nullptr, norms_or_null, norm_cols);
             break;
         default:
             return B200F_ERR_BAD_ARG;
     }
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+}  // namespace
+
+extern "C" int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
+                                int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
+                                int64_t plane_stride, float* norms_or_null, int norm_cols,
+                                void* stream) {
+    return store_rows_impl(src, d, n, d, storage, dst_rows, dst_pitch, planes, plane_pitch, plane_stride,
+                           B200F_PLANES_BF16X3, 0, nullptr, norms_or_null, norm_cols, stream);
+}
+
+extern "C" int b200f_store_rows_fp32(const float* src, int64_t src_pitch, int64_t n, int d, float* dst_rows,
+                                     int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
+                                     int64_t plane_stride, int plane_format, int plane_scale_log2,
+                                     int32_t* range_flag, float* norms_or_null, int norm_cols, void* stream) {
+    return store_rows_impl(src, src_pitch, n, d, B200F_STORAGE_F32, dst_rows, dst_pitch, planes, plane_pitch,
+                           plane_stride, plane_format, plane_scale_log2, range_flag, norms_or_null, norm_cols, stream);
+}
+
+extern "C" int b200f_rows_absmax(const float* rows, int64_t n, int d, int64_t pitch_elems, uint32_t* max_bits,
+                                 void* stream) {
+    if (n < 0 || d <= 0 || pitch_elems < d || !max_bits || (n > 0 && !rows)) return B200F_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B200F_CUDA_TRY(cudaMemsetAsync(max_bits, 0, sizeof(uint32_t), st));
+    if (n == 0) return B200F_OK;
+    rows_absmax_kernel<<<grid_for_rows(n), ROW_THREADS, 0, st>>>(rows, pitch_elems, n, d, max_bits);
     count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;

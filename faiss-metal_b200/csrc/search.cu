@@ -68,6 +68,7 @@ struct SearchPlan {
     ScanPlan scan;
     int64_t chunk_cols;
     int64_t ngroups;  // scan path: query groups of SCAN_GROUP
+    size_t off_qscale;
     size_t off_qnorm, off_gthr, off_a, off_part_key, off_part_idx, off_matrix, off_run_key, off_run_idx;
     size_t off_dirty, off_rows, off_count, off_a2;
     size_t off_pilot_key, off_pilot_idx, off_thr, off_cand_key, off_cand_idx, off_cand_cnt;
@@ -135,6 +136,8 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         }
     };
     pl.off_qnorm = off;
+    adv((size_t)(nq > 0 ? nq : 1) * 4);
+    pl.off_qscale = off;   // per-row key scales of the fp16x2 plane format
     adv((size_t)(nq > 0 ? nq : 1) * 4);
     pl.gslots = 1;
     if (!pairwise && pl.path == B200F_PATH_TENSOR && k <= B200F_LIST_MAX_K && !filter_disabled()) {
@@ -268,6 +271,8 @@ int validate(const B200FSearchArgs* a, bool pairwise) {
     if (!pairwise && a->k > B200F_MAX_K) return B200F_ERR_UNSUPPORTED;
     if (a->nb > 0x7fffffffLL) return B200F_ERR_UNSUPPORTED;  // int32 row numbers inside a shard
     if (a->path < B200F_PATH_AUTO || a->path > B200F_PATH_TENSOR) return B200F_ERR_BAD_ARG;
+    if (a->plane_format != B200F_PLANES_BF16X3 && a->plane_format != B200F_PLANES_FP16X2) return B200F_ERR_BAD_ARG;
+    if (a->plane_scale_log2 < -126 || a->plane_scale_log2 > 126) return B200F_ERR_BAD_ARG;
     if (a->nq > 0 && !a->queries) return B200F_ERR_BAD_ARG;
     if (!pairwise && a->nq > 0 && (!a->out_dist || !a->out_labels)) return B200F_ERR_BAD_ARG;
     if (a->nb > 0) {
@@ -300,7 +305,13 @@ int fill_operands(const B200FSearchArgs& a, const SearchPlan& pl, uint8_t* scrat
         op.b_planes = a.planes;
         op.b_pitch = a.plane_pitch;
         op.b_plane_stride = a.plane_stride;
-        op.is_bf16 = 1;
+        if (a.plane_format == B200F_PLANES_FP16X2) {
+            op.npl = 2;
+            op.is_bf16 = 0;
+            op.rowscale = reinterpret_cast<const float*>(scratch + pl.off_qscale);
+        } else {
+            op.is_bf16 = 1;
+        }
     } else {
         if (a.row_pitch < op.d_pad) return B200F_ERR_BAD_ARG;
         op.b_planes = reinterpret_cast<const uint16_t*>(a.rows);
@@ -573,9 +584,10 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
         if (rc != B200F_OK) return rc;
         rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage,
                                     reinterpret_cast<uint16_t*>(scratch + pl.off_a), pl.a_pitch,
-                                    pl.a_plane_stride, qnorm, qnc, st);
+                                    pl.a_plane_stride, qnorm, qnc, a->plane_format, a->plane_scale_log2,
+                                    reinterpret_cast<float*>(scratch + pl.off_qscale), st);
     } else {
-        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, st);
+        rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, 0, 0, nullptr, st);
     }
     if (rc != B200F_OK) return rc;
 
@@ -594,6 +606,7 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
                                 a2, st);
         if (r2 != B200F_OK) return r2;
         op.a_planes = a2;
+        op.rowscale_map = rows;   // row j of the gathered operand is query rows[j]
         op.nq_dev = count;
         nq_dev = count;
         row_map = rows;
@@ -748,12 +761,13 @@ extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64
         if (rc != B200F_OK) return rc;
         rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage,
                                     reinterpret_cast<uint16_t*>(scratch + pl.off_a), pl.a_pitch,
-                                    pl.a_plane_stride, qnorm, l2 ? 1 : 0, st);
+                                    pl.a_plane_stride, qnorm, l2 ? 1 : 0, a->plane_format, a->plane_scale_log2,
+                                    reinterpret_cast<float*>(scratch + pl.off_qscale), st);
         if (rc != B200F_OK) return rc;
         return launch_gemm_store(op, pl.gemm, 0, a->nb, kscale, l2 ? 1.f : -1.f,
                                  l2 ? qnorm : nullptr, out_matrix, ld_out, a->status, st);
     }
-    rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, st);
+    rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, 0, 0, nullptr, st);
     if (rc != B200F_OK) return rc;
     for (int64_t g = 0; g < pl.ngroups; g++) {
         B200FSearchArgs sub = *a;

@@ -164,6 +164,17 @@ struct B200IndexFlat::Impl {
     int64_t planeStride() const { return inPlace ? planeStrideFixed : capacity * planePitch; }
     int growthMode = -1;           // -1: process default, 0: in place, 1: allocate-copy-free
 
+    // FP32 storage: format of the split planes (B200F_PLANES_*).  An index starts with two fp16
+    // planes (half the tensor work of three bf16 planes) unless told otherwise, takes its
+    // power-of-two scale from the first rows it sees, and re-splits itself into three bf16 planes
+    // the moment a row does not fit fp16's range (the conversion kernel raises a flag).
+    int planeFormat = B200F_PLANES_FP16X2;
+    int planeFormatWanted = B200F_PLANES_FP16X2;
+    int planeScaleLog2 = 0;
+    bool planeScaleKnown = false;
+    int planesBacked() const { return planeFormat == B200F_PLANES_FP16X2 ? 2 : 3; }
+    int32_t* rangeFlag() const { return status + 8; }   // device word beside the status words
+
     // Small searches (n <= kGraphMaxQueries, host buffers) replayed from CUDA graphs.  A graph
     // holds the whole call: host-to-device copy of the queries out of its pinned slot, the
     // search, and the copies of distances, labels and status word back into the slot.  It is
@@ -267,7 +278,7 @@ struct B200IndexFlat::Impl {
             const size_t es = elemBytes(storage);
             vRows.back(0, (size_t)want * pitch * es);
             if (planes)
-                for (int p = 0; p < 3; p++)
+                for (int p = 0; p < planesBacked(); p++)
                     vPlanes.back((size_t)p * planeStrideFixed * 2, (size_t)want * planePitch * 2);
             if (norms) vNorms.back(0, (size_t)want * 4);
             capacity = want;
@@ -317,6 +328,8 @@ struct B200IndexFlat::Impl {
         a.planes = planes;
         a.plane_pitch = planePitch;
         a.plane_stride = planeStride();
+        a.plane_format = planeFormat;
+        a.plane_scale_log2 = planeScaleLog2;
         a.norms = norms;
         a.nb = ntotal;
         a.metric = l2 ? B200F_METRIC_L2 : B200F_METRIC_INNER_PRODUCT;
@@ -377,7 +390,7 @@ B200IndexFlat::B200IndexFlat(std::shared_ptr<B200Resources> resources, int d_,
     DeviceGuard g(impl_->res->getDevice());
     impl_->status = static_cast<int32_t*>(impl_->res->allocBuffer(256));
     impl_->oneRow = static_cast<float*>(impl_->res->allocBuffer((size_t)d_ * 4));
-    impl_->hostStatus = static_cast<int32_t*>(alloc_pinned(16));
+    impl_->hostStatus = static_cast<int32_t*>(alloc_pinned(64));
     if (!impl_->hostStatus) throw B200RuntimeError(B200F_ERR_OOM, "faiss-b200: pinned allocation failed");
     cudaCheck(cudaMemsetAsync(impl_->status, 0, 256, impl_->stream()), "memset status");
     is_trained = true;
@@ -413,6 +426,16 @@ void B200IndexFlat::setGrowthMode(int mode) {
     impl_->growthMode = mode;
 }
 
+void B200IndexFlat::setFp32PlaneFormat(int format) {
+    B200_THROW_ARG_IF_NOT(B200F_ERR_BAD_ARG, format == B200F_PLANES_BF16X3 || format == B200F_PLANES_FP16X2,
+                          "plane format must be B200F_PLANES_BF16X3 or B200F_PLANES_FP16X2");
+    B200_THROW_ARG_IF_NOT(B200F_ERR_STATE, ntotal == 0 && impl_->capacity == 0,
+                          "the plane format can only be chosen on an index that holds no storage yet");
+    impl_->planeFormatWanted = format;
+    impl_->planeFormat = format;
+}
+int B200IndexFlat::getFp32PlaneFormat() const { return impl_->planeFormat; }
+
 void B200IndexFlat::setUseGraphs(bool on) {
     if (!on) {
         DeviceGuard g(impl_->res->getDevice());
@@ -438,14 +461,36 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
     }
     cudaStream_t st = impl_->stream();
     const size_t es = elemBytes(impl_->storage);
+    const bool fp32 = impl_->storage == StorageType::Float32;
+    if (fp32) cudaCheck(cudaMemsetAsync(impl_->rangeFlag(), 0, 4, st), "add: clear range flag");
     auto store = [&](const float* src, int64_t r0, int64_t nr) {
         const int64_t row = ntotal + r0;
-        abiCheck(b200f_store_rows(
-                         src, nr, d, impl_->storageCode(),
-                         static_cast<uint8_t*>(impl_->rows) + (size_t)row * impl_->pitch * es, impl_->pitch,
-                         impl_->planes ? impl_->planes + (size_t)row * impl_->planePitch : nullptr,
-                         impl_->planePitch, impl_->planeStride(),
-                         impl_->norms ? impl_->norms + row : nullptr, impl_->l2 ? 1 : 0, st),
+        if (!fp32) {
+            abiCheck(b200f_store_rows(
+                             src, nr, d, impl_->storageCode(),
+                             static_cast<uint8_t*>(impl_->rows) + (size_t)row * impl_->pitch * es, impl_->pitch, nullptr, 0,
+                             0, impl_->norms ? impl_->norms + row : nullptr, impl_->l2 ? 1 : 0, st),
+                     "add: store rows");
+            return;
+        }
+        if (impl_->planeFormat == B200F_PLANES_FP16X2 && !impl_->planeScaleKnown) {
+            // the index's scale: the largest element of the first rows it is given goes to [2^6, 2^7)
+            uint32_t* bits = reinterpret_cast<uint32_t*>(impl_->rangeFlag() + 1);
+            abiCheck(b200f_rows_absmax(src, nr, d, d, bits, st), "add: rows absmax");
+            cudaCheck(cudaMemcpyAsync(impl_->hostStatus + 8, bits, 4, cudaMemcpyDeviceToHost, st), "add: absmax copy");
+            cudaCheck(cudaStreamSynchronize(st), "add: synchronize");
+            float amax;
+            std::memcpy(&amax, impl_->hostStatus + 8, 4);
+            int e = 0;
+            if (amax > 0.f) (void)std::frexp(amax, &e);
+            impl_->planeScaleLog2 = amax > 0.f ? std::max(-120, std::min(120, 7 - e)) : 0;
+            impl_->planeScaleKnown = amax > 0.f;   // all-zero rows say nothing: ask the next block again
+        }
+        abiCheck(b200f_store_rows_fp32(src, d, nr, d, static_cast<float*>(impl_->rows) + (size_t)row * impl_->pitch,
+                                       impl_->pitch, impl_->planes + (size_t)row * impl_->planePitch, impl_->planePitch,
+                                       impl_->planeStride(), impl_->planeFormat, impl_->planeScaleLog2,
+                                       impl_->rangeFlag(), impl_->norms ? impl_->norms + row : nullptr,
+                                       impl_->l2 ? 1 : 0, st),
                  "add: store rows");
     };
     const PtrKind kind = pointerKind(x);
@@ -515,9 +560,25 @@ void B200IndexFlat::add(faiss::idx_t n, const float* x) {
         releaseEvents();
     }
     // the caller may free x as soon as add returns
+    if (fp32 && impl_->planeFormat == B200F_PLANES_FP16X2)
+        cudaCheck(cudaMemcpyAsync(impl_->hostStatus + 9, impl_->rangeFlag(), 4, cudaMemcpyDeviceToHost, st),
+                  "add: range flag copy");
     cudaCheck(cudaStreamSynchronize(st), "add: synchronize");
     ntotal = newTotal;
     impl_->mirrorValid = false;
+    if (fp32 && impl_->planeFormat == B200F_PLANES_FP16X2 && impl_->hostStatus[9] != 0) {
+        // a row of this add does not fit fp16's range at the index's scale: three bf16 planes
+        // from now on, re-split from the stored fp32 rows
+        impl_->planeFormat = B200F_PLANES_BF16X3;
+        if (impl_->inPlace)
+            impl_->vPlanes.back((size_t)2 * impl_->planeStrideFixed * 2, (size_t)impl_->capacity * impl_->planePitch * 2);
+        abiCheck(b200f_store_rows_fp32(static_cast<const float*>(impl_->rows), impl_->pitch, ntotal, d,
+                                       static_cast<float*>(impl_->rows), impl_->pitch, impl_->planes, impl_->planePitch,
+                                       impl_->planeStride(), B200F_PLANES_BF16X3, 0, nullptr, impl_->norms,
+                                       impl_->l2 ? 1 : 0, st),
+                 "add: re-split rows");
+        cudaCheck(cudaStreamSynchronize(st), "add: synchronize");
+    }
 }
 
 void B200IndexFlat::reset() {
@@ -525,6 +586,9 @@ void B200IndexFlat::reset() {
     cudaCheck(cudaStreamSynchronize(impl_->stream()), "reset: synchronize");
     impl_->invalidateGraphs();
     impl_->freeStorage();
+    impl_->planeFormat = impl_->planeFormatWanted;
+    impl_->planeScaleKnown = false;
+    impl_->planeScaleLog2 = 0;
     impl_->mirror.clear();
     impl_->mirror.shrink_to_fit();
     impl_->mirrorValid = false;

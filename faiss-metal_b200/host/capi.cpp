@@ -270,6 +270,16 @@ int b200f_index_set_growth_mode(B200FIndex* index, int mode) {
     B200F_GUARD_END
 }
 
+int b200f_index_set_fp32_planes(B200FIndex* index, int format) {
+    if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
+    B200F_GUARD_BEGIN
+    index->index->setFp32PlaneFormat(format);
+    return B200F_OK;
+    B200F_GUARD_END
+}
+
+int b200f_index_fp32_planes(const B200FIndex* index) { return index ? index->index->getFp32PlaneFormat() : -1; }
+
 int b200f_index_set_use_graphs(B200FIndex* index, int on) {
     if (!index) return fail(B200F_ERR_BAD_ARG, "null index");
     B200F_GUARD_BEGIN

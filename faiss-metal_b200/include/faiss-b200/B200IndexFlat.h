@@ -87,6 +87,13 @@ class B200IndexFlat : public faiss::Index {
     /// where the driver supports it), 1: the reference's allocate-copy-free growth
     /// (src/MetalIndexFlat.mm:196-222).  Only before the first add / reserve.
     void setGrowthMode(int mode);
+    /// FP32 storage only: which split planes the tensor path multiplies (B200F_PLANES_BF16X3: three
+    /// bf16 planes, six products; B200F_PLANES_FP16X2: two fp16 planes of the rows scaled by a power of
+    /// two the index picks from its first rows, three products).  The default is FP16X2; an index
+    /// whose rows stop fitting fp16's range re-splits itself into BF16X3 during that add().  Both
+    /// hold the 1e-4 contract.  Only on an empty index.
+    void setFp32PlaneFormat(int format);
+    int getFp32PlaneFormat() const;
     /// Searches of at most 8 queries with host buffers are replayed from a CUDA graph captured
     /// on their second occurrence (default on).  Off: every search is enqueued call by call.
     void setUseGraphs(bool on);

@@ -239,6 +239,14 @@ class B200IndexFlat:
         """0: grow in place (default where supported), 1: allocate-copy-free; empty index only."""
         abi.check(abi.lib().b200f_index_set_growth_mode(self._h, int(mode)), "set_growth_mode")
 
+    def set_fp32_planes(self, fmt: int):
+        """FP32 storage: abi.PLANES_BF16X3 or abi.PLANES_FP16X2 (default); empty index only."""
+        abi.check(abi.lib().b200f_index_set_fp32_planes(self._h, int(fmt)), "set_fp32_planes")
+
+    @property
+    def fp32_planes(self) -> int:
+        return abi.lib().b200f_index_fp32_planes(self._h)
+
     def set_use_graphs(self, on: bool):
         abi.check(abi.lib().b200f_index_set_use_graphs(self._h, 1 if on else 0), "set_use_graphs")
 

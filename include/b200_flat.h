@@ -52,6 +52,19 @@ extern "C" {
 #define B200F_ERR_DEVICE_CHECK 10 /* a device-side self-check failed: shared-memory base misaligned,
                                      candidate buffer overflow, debug canary overwritten   */
 
+/* Split planes FP32 storage keeps for the tensor path (the reference multiplies FP32 storage in
+ * half precision, shaders/simdgroup_gemm.metal:62-69, ~1e-2 relative; the contract here is 1e-4):
+ *   BF16X3  x = b0 + b1 + b2, three bf16 planes, six plane products, exact to 2^-24.
+ *   FP16X2  2^s x = h0 + h1, two fp16 planes of the row scaled by the index's power of two 2^s
+ *           (largest element near 2^6), three plane products, exact to 2^-22: half the tensor
+ *           work, two thirds of the plane bytes.  Valid while every row fits fp16's range
+ *           (elements below 2^15 after scaling, no non-zero row whose largest element is below
+ *           2^-4); b200f_store_rows_fp32 reports rows that do not through range_flag, and the
+ *           index then re-splits itself into BF16X3.  Queries are scaled per row inside
+ *           b200f_search, so their magnitude does not matter. */
+#define B200F_PLANES_BF16X3 0
+#define B200F_PLANES_FP16X2 1
+
 /* Largest k any path accepts (README.md:218-219 / src/MetalSelect.mm:65-70: 4096 on M3+). */
 #define B200F_MAX_K 4096
 /* Largest k served by the fused (no distance matrix) epilogue and scan kernels
@@ -150,6 +163,17 @@ int b200f_row_norms(const void* rows, int storage, int64_t n, int d, int64_t pit
 int b200f_store_rows(const float* src, int64_t n, int d, int storage, void* dst_rows,
                      int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch,
                      int64_t plane_stride, float* norms_or_null, int norm_cols, void* stream);
+/* The same for FP32 storage with a choice of plane format (B200F_PLANES_*) and, for FP16X2, the
+ * index's scale 2^plane_scale_log2.  src rows are src_pitch elements apart; src == dst_rows
+ * (with src_pitch == dst_pitch) re-splits rows that are stored already.  range_flag (device
+ * int32, may be NULL): bit 1 is OR-ed in when a row does not fit the FP16X2 format. */
+int b200f_store_rows_fp32(const float* src, int64_t src_pitch, int64_t n, int d, float* dst_rows,
+                          int64_t dst_pitch, uint16_t* planes, int64_t plane_pitch, int64_t plane_stride,
+                          int plane_format, int plane_scale_log2, int32_t* range_flag, float* norms_or_null,
+                          int norm_cols, void* stream);
+/* *max_bits = bit pattern of the largest finite |element| of the fp32 rows (0 when all are zero):
+ * what an index derives its FP16X2 scale from.  Device pointers.  No counterpart in the reference. */
+int b200f_rows_absmax(const float* rows, int64_t n, int d, int64_t pitch_elems, uint32_t* max_bits, void* stream);
 
 /* Stored rows -> fp32 [n][d] (pitch d).
  * Replaces the per-element conversions of MetalIndexFlat::reconstruct
@@ -184,6 +208,8 @@ typedef struct B200FSearchArgs {
     int32_t norm_cols;       /* 1: 16-bit rows / split plane 0 carry the 8 norm columns
                                 written by b200f_store_rows(norm_cols = 1); required for
                                 L2 on 16-bit storage and on the tensor path                */
+    int32_t plane_format;    /* FP32 storage: B200F_PLANES_* of `planes` (0 = three bf16 planes) */
+    int32_t plane_scale_log2; /* FP16X2: the planes hold 2^plane_scale_log2 * x                  */
 } B200FSearchArgs;
 
 /* Scratch bytes b200f_search needs for this shape (0 on bad arguments).
@@ -366,6 +392,11 @@ int b200f_index_reserve(B200FIndex* index, int64_t n);
  * allocate-copy-free (src/MetalIndexFlat.mm:196-222).  Only on an empty index.  The default
  * comes from the environment variable B200F_NO_VMM=1 (read once per process). */
 int b200f_index_set_growth_mode(B200FIndex* index, int mode);
+/* FP32 storage: plane format of the tensor path's operands (B200F_PLANES_*; default FP16X2, see
+ * there).  The setter works on an empty index only; the getter tells what the index uses now (an
+ * FP16X2 index falls back to BF16X3 by itself when a row leaves fp16's range). */
+int b200f_index_set_fp32_planes(B200FIndex* index, int format);
+int b200f_index_fp32_planes(const B200FIndex* index);
 /* Searches of at most 8 queries whose three arrays are host memory are replayed from a CUDA
  * graph (query upload, every kernel of the search, result download in one launch), captured
  * the second time a (n, k) shape is seen and dropped whenever the index changes.  on = 0

@@ -35,7 +35,7 @@ def test_ctypes_table_matches_header(fm):
 def test_search_args_layout(fm):
     # struct layout must match the C declaration (all 8-byte fields naturally aligned)
     a = fm.abi.SearchArgs
-    assert ctypes.sizeof(a) == 152
+    assert ctypes.sizeof(a) == 160
     assert a.nb.offset == 72 and a.scratch.offset == 112 and a.path.offset == 144
 
 
