@@ -493,6 +493,15 @@ def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_labe
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step = float(t.item()) / steps
+        # the dominant kernel's time per step on every rank: a step ends when the slowest shard
+        # has been searched (the exchange waits for it), so the spread between the GPUs (clocks
+        # under the power cap) shows up as waiting time on the faster ranks
+        kernel_ms_by_rank = None
+        if world > 1:
+            km = torch.zeros(world, dtype=torch.float64, device="cuda")
+            km[rank] = main_ms.value / max(1, steps)
+            dist.all_reduce(km, op=dist.ReduceOp.SUM)
+            kernel_ms_by_rank = [round(v, 4) for v in km.cpu().tolist()]
 
         # ---- end-to-end timing -------------------------------------------------------------
         e2e = None
@@ -657,7 +666,8 @@ def run_workload(ctx, name, w, steps, warmup, headline, with_e2e=True, with_labe
                                 % (nb_local * d * ELEM_BYTES[w["storage"]] / 1e9),
                    "seeds": {"database": 1, "queries": 2},
                    "headline": headline},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches.value),
+        "roofline": dict(roofline, kernel_ms_per_step_by_rank=kernel_ms_by_rank), "e2e": e2e,
+        "gpu_launches": int(launches.value),
         "latency": latency, "clocks": clocks, "check": check, "step_ms": [round(x, 3) for x in step_ms],
     }
 
