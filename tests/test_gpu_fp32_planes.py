@@ -127,3 +127,74 @@ def test_format_can_only_be_chosen_on_an_empty_index(fm, res):
         fm.B200IndexFlat(res, 16, O.METRIC_L2, 0).set_fp32_planes(7)
     assert e.value.status == fm.abi.ERR_BAD_ARG
     idx.close()
+
+
+@pytest.mark.parametrize("metric", [O.METRIC_L2, O.METRIC_INNER_PRODUCT])
+def test_op_level_fp16_planes_pairwise_and_search(fm, res, metric):
+    """The op-level entry points with the FP16X2 plane format: b200f_rows_absmax gives the scale,
+    b200f_store_rows_fp32 writes the planes, b200f_pairwise (keys scaled back per query row in the
+    store epilogue) and b200f_search multiply them."""
+    import ctypes
+
+    import torch
+    from test_gpu_ops import Stored, cur_stream, vp
+    L = fm.lib()
+    nb, nq, d = 3000, 150, 72
+    xb = (H.gaussian(nb, d, 21) * np.float32(37.0)).astype(np.float32)
+    xq = (H.gaussian(nq, d, 22) * np.float32(0.02)).astype(np.float32)
+    xq[::2] *= np.float32(500.0)
+    st = Stored(fm, xb, 0)                                  # allocates rows / planes / norms (bf16x3 content)
+    src = torch.from_numpy(xb).cuda()
+    bits = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    fm.abi.check_op(L.b200f_rows_absmax(vp(src), nb, d, d, vp(bits), cur_stream()), "rows_absmax")
+    amax = np.array([int(bits.cpu()[0])], dtype=np.uint32).view(np.float32)[0]
+    assert amax == np.abs(xb).max()
+    lg = 7 - int(np.frexp(amax)[1])
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    fm.abi.check_op(L.b200f_store_rows_fp32(vp(src), d, nb, d, vp(st.rows), st.pitch, vp(st.planes), st.ppitch,
+                                            max(1, nb) * st.ppitch, fm.abi.PLANES_FP16X2, lg, vp(flag), vp(st.norms), 1,
+                                            cur_stream()), "store_rows_fp32")
+    torch.cuda.synchronize()
+    assert int(flag.cpu()[0]) == 0
+    # plane 0 + plane 1 reproduce 2^lg * x to 22 bits
+    planes = st.planes.view(torch.float16).reshape(3, nb, st.ppitch).to(torch.float64)
+    back = (planes[0, :, :d] + planes[1, :, :d]).cpu().numpy() / 2.0 ** lg
+    np.testing.assert_allclose(back, xb.astype(np.float64), rtol=2.0 ** -21, atol=2.0 ** (-25 - lg))
+    xq_dev = torch.from_numpy(xq).cuda()
+    out = torch.full((nq, nb), float("nan"), dtype=torch.float32, device="cuda:0")
+    a = st.args(fm, xq_dev, metric, 1, 2)
+    a.plane_format = fm.abi.PLANES_FP16X2
+    a.plane_scale_log2 = lg
+    fm.abi.check_op(L.b200f_pairwise(ctypes.byref(a), vp(out), nb), "pairwise")
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().astype(np.float64)
+    want = O.pairwise(metric, xb, xq)
+    if metric == O.METRIC_L2:
+        assert (np.abs(got - want) <= 1e-4 * np.maximum(want, 1e-3 * want.max())).all()
+    else:
+        # relative to |q| |x| of each pair's query row (rows differ by 500x in magnitude)
+        bound = 1e-5 * np.linalg.norm(xq, axis=1)[:, None] * np.linalg.norm(xb, axis=1)[None, :]
+        assert (np.abs(got - want) <= bound).all()
+    k = 40
+    out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda:0")
+    out_l = torch.empty((nq, k), dtype=torch.int64, device="cuda:0")
+    a = st.args(fm, xq_dev, metric, k, 2, out_d, out_l)
+    a.plane_format = fm.abi.PLANES_FP16X2
+    a.plane_scale_log2 = lg
+    fm.abi.check_op(L.b200f_search(ctypes.byref(a)), "search")
+    torch.cuda.synchronize()
+    assert int(st.status[0]) == 0
+    H.check_against_oracle(metric, 0, True, xb, xq, k, out_d.cpu().numpy(), out_l.cpu().numpy())
+    # a row that does not fit raises the flag
+    xb2 = xb.copy()
+    xb2[7] *= np.float32(1e4)
+    src2 = torch.from_numpy(xb2).cuda()
+    fm.abi.check_op(L.b200f_store_rows_fp32(vp(src2), d, nb, d, vp(st.rows), st.pitch, vp(st.planes), st.ppitch,
+                                            max(1, nb) * st.ppitch, fm.abi.PLANES_FP16X2, lg, vp(flag), vp(st.norms), 1,
+                                            cur_stream()), "store_rows_fp32")
+    torch.cuda.synchronize()
+    assert int(flag.cpu()[0]) == 1
+    # bad arguments
+    assert L.b200f_store_rows_fp32(vp(src), d, nb, d, vp(st.rows), st.pitch, vp(st.planes), st.ppitch,
+                                   max(1, nb) * st.ppitch, 5, lg, None, None, 1, cur_stream()) == fm.abi.ERR_BAD_ARG
+    assert L.b200f_rows_absmax(vp(src), nb, d, d, None, cur_stream()) == fm.abi.ERR_BAD_ARG
