@@ -214,11 +214,18 @@ def run_reference(args, w, rank, world):
         "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
+        # the same keys and values as the B200 arm's config for this N: it names the workload, not the arm
         "config": {"workload": args.workload, "desc": w["desc"], "nb": w["nb"], "nq": w["nq"], "d": w["d"],
-                   "k": w["k"], "seeds": {"database": 1, "queries": 2}, "headline": not (args.nb or args.nq or args.storage >= 0),
-                   "note": "the reference's own CPU comparison is CPU FAISS, which is not installed and whose "
-                           "Metal shaders cannot run here; this arm times the oracle's sgemm + partial-select "
-                           "port (the algorithm CPU FAISS uses for query batches) on all host cores"},
+                   "k": w["k"], "rows_per_gpu": (w["nb"] + world - 1) // world,
+                   "parallelism": "row-sharded x%d, NCCL all-gather + k-way merge" % world,
+                   "l2_policy": "inputs larger than L2 (database shard %.1f GB streams every step)"
+                                % ((w["nb"] + world - 1) // world * w["d"] * ELEM_BYTES[w["storage"]] / 1e9),
+                   "seeds": {"database": 1, "queries": 2},
+                   "headline": not (args.nb or args.nq or args.storage >= 0)},
+        "note": "the reference's own CPU comparison is CPU FAISS, which is not installed and whose "
+                "Metal shaders cannot run here; this arm times the oracle's sgemm + partial-select "
+                "port (the algorithm CPU FAISS uses for query batches) on all host cores of this box, "
+                "whatever the number of GPUs",
         "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
