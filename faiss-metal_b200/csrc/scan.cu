@@ -129,8 +129,9 @@ __device__ __forceinline__ void warp_insert(float& lk, int& li, float s, int id,
 
 template <int STORAGE, int NQ, bool STORE>
 // Three CTAs per SM where 80 registers suffice; four queries, and two queries on fp32 rows (paired
-// accumulators), take 128 registers and two CTAs.  Measured on 12.5 M fp32 rows of d = 128:
-// 5.43 / 5.41 / 3.81 TB/s for one / two / four queries (4.98 / 4.58 / 3.53 with plain FMAs).
+// accumulators), take 128 registers and two CTAs; the grid is exactly one such wave.  Measured on
+// 12.5 M fp32 rows of d = 128: 6.90 / 5.64 / 4.06 TB/s for one / two / four queries (4.98 / 4.58 /
+// 3.53 with plain FMAs and a grid of four CTAs per SM, whose last wave ran a third full).
 __global__ void __launch_bounds__(SCAN_THREADS, (NQ == 4 || (NQ == 2 && STORAGE == B200F_STORAGE_F32 && !STORE)) ? 2 : 3)
 scan_kernel(const ScanParams p) {
     constexpr int E = Piece<STORAGE>::E;
@@ -688,13 +689,23 @@ bool plan_stream(ScanParams& p, int storage, int d, int norm_cols) {
 
 int lanes_per_row_cap(int64_t nq) { (void)nq; return 8; }
 
-int scan_grid(int64_t nrows, int d, int storage, int sm_count, int lpr_cap) {
+// CTAs of scan_kernel that are resident per SM (its launch bounds): the grid is one full wave of
+// them.  A grid of 4 per SM with 3 resident ran a second, third-empty wave: measured 66 % of the
+// DRAM peak in the profile of one fp32 query where one wave reaches more.
+int resident_ctas(int64_t nq, int storage, bool store) {
+    const int64_t group = nq < 4 ? nq : 4;   // queries per launch: 1, 2 or 4 (three run as four)
+    if (group >= 3) return 2;
+    if (group == 2 && storage == B200F_STORAGE_F32 && !store) return 2;
+    return 3;
+}
+
+int scan_grid(int64_t nrows, int d, int storage, int sm_count, int lpr_cap, int per_sm) {
     ScanParams t{};
     fill_geometry(t, storage, d, d, 0, lpr_cap);
     const int rows_per_block = (32 / t.lpr) * SCAN_U;
     const int64_t nblocks = ceil_div64(nrows, rows_per_block);
     int64_t g = ceil_div64(nblocks, SCAN_WARPS);
-    const int64_t cap = (int64_t)sm_count * 4;
+    const int64_t cap = (int64_t)sm_count * per_sm;
     if (g > cap) g = cap;
     if (g < 1) g = 1;
     return (int)g;
@@ -705,7 +716,7 @@ int scan_grid(int64_t nrows, int d, int storage, int sm_count, int lpr_cap) {
 ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count) {
     ScanPlan s;
     s.lpr_cap = lanes_per_row_cap(nq);  // of the whole search: every query group uses the same geometry
-    s.grid = scan_grid(nb, d, storage, sm_count, s.lpr_cap);
+    s.grid = scan_grid(nb, d, storage, sm_count, s.lpr_cap, resident_ctas(nq, storage, false));
     s.threads = SCAN_THREADS;
     return s;
 }
@@ -782,7 +793,9 @@ int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, flo
     p.metric = a.metric;
     p.out = out;
     p.ld = ld;
-    return launch_storage<true>(p, a.storage, scan_grid(ncols, a.d, a.storage, sm_count, lanes_per_row_cap(a.nq)),
+    return launch_storage<true>(p, a.storage,
+                                scan_grid(ncols, a.d, a.storage, sm_count, lanes_per_row_cap(a.nq),
+                                          resident_ctas(a.nq, a.storage, true)),
                                 stream);
 }
 
