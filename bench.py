@@ -753,9 +753,8 @@ def run_b200(args, w, rank, world, local_rank):
                 extras[name] = run_workload(ctx, name, dict(WORKLOADS[name]), max(3, min(args.steps, 10)), 3, False,
                                             with_e2e=not args.no_e2e, with_label_check=not args.no_label_check)
             except Exception as e:   # an extra must never take the headline down with it
+                # (checks raise after a workload's last collective call, so the ranks stay in step)
                 extras[name] = {"error": "%s: %s" % (type(e).__name__, e)}
-                if world > 1:
-                    raise
         if world == 1:
             try:
                 extras["ingest"] = run_ingest(ctx, w)
