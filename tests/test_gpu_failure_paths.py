@@ -144,3 +144,27 @@ def test_ingest_pipeline_pinned_and_pageable(fm, res):
         idx.reconstruct_n(5, n - 5, out_pin.numpy())
         assert np.array_equal(out_pin.numpy(), want[5:])
         idx.close()
+
+
+def test_many_async_tokens_in_flight(fm, res):
+    # sixteen tokens of different sizes queued back to back: uploads, kernels and downloads of
+    # neighbouring tokens overlap on the three streams; every token must hold exactly what the
+    # synchronous search gives for its queries, whatever the order they are waited for in
+    nb, d = 120_000, 128
+    xb = H.gaussian(nb, d, 3, scale=0.05)
+    idx = fm.B200IndexFlat(res, d, O.METRIC_L2, 2)
+    idx.add(xb)
+    sizes = [1, 700, 3, 2000, 64, 9, 1500, 2, 300, 5000, 1, 17, 1024, 8, 256, 33]
+    k = 10
+    queries = [H.gaussian(n, d, 100 + i, scale=0.05) for i, n in enumerate(sizes)]
+    outs = [(np.full((n, k), np.nan, np.float32), np.full((n, k), -7, np.int64)) for n in sizes]
+    for rounds in range(2):                      # the second round runs entirely on recycled buffers
+        tokens = [idx.search_async(q, k, o[0], o[1]) for q, o in zip(queries, outs)]
+        for t in reversed(tokens):
+            t.wait()
+        for q, (D, I) in zip(queries, outs):
+            Ds, Is = idx.search(q, k)
+            assert np.array_equal(I, Is) and np.array_equal(D, Ds)
+            D.fill(np.nan)
+            I.fill(-7)
+    idx.close()
