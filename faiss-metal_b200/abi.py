@@ -60,6 +60,7 @@ SIGNATURES = {
     "b200f_set_selection_mode": (c_int, [c_int]),
     "b200f_get_selection_mode": (c_int, []),
     "b200f_set_gemm_shape": (c_int, [c_int]),
+    "b200f_set_rank_select": (c_int, [c_int]),
     "b200f_set_debug_canaries": (c_int, [c_int]),
     "b200f_debug_wait_expiry": (c_int, [c_vp, c_i64, c_vp]),
     "b200f_debug_canary_selftest": (c_int, [c_vp, c_sz, c_int, c_vp, c_vp]),

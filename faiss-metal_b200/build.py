@@ -22,7 +22,7 @@ NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 HOST_CXX = shutil.which("g++") or "g++"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-CU_SOURCES = ["csrc/rows.cu", "csrc/scan.cu", "csrc/select.cu", "csrc/gemm_topk.cu", "csrc/search.cu"]
+CU_SOURCES = ["csrc/rows.cu", "csrc/scan.cu", "csrc/select.cu", "csrc/select_rank.cu", "csrc/gemm_topk.cu", "csrc/search.cu"]
 CPP_SOURCES = ["host/Resources.cpp", "host/GrowableArray.cpp", "host/IndexFlat.cpp", "host/Sharded.cpp", "host/capi.cpp",
                "faiss_compat/compat_impl.cpp"]
 def _headers():

@@ -159,6 +159,17 @@ int launch_select_candidates(const float* cand_key, const int32_t* cand_idx, con
                              int cap, int64_t nb, int64_t nq, int k, int metric, const float* qnorm,
                              int64_t label_base, float* out_dist, int64_t* out_labels, int32_t* dirty,
                              cudaStream_t stream);
+// select_rank.cu: the same selection / merge for inputs of at most 8192 entries per row, sorted in
+// registers and placed by binary search; results identical to the kernels of select.cu.
+bool rank_select_enabled();
+bool rank_select_fits(int cap, int k);
+int launch_rank_select(const float* cand_key, const int32_t* cand_idx, const int32_t* cand_cnt, int cap,
+                       int64_t nb, int64_t nq, int k, int metric, const float* qnorm, int64_t label_base,
+                       float* out_dist, int64_t* out_labels, int32_t* dirty, cudaStream_t stream);
+bool rank_merge_fits(int P, int k);
+int launch_rank_merge(const float* dist, const int64_t* labels, int64_t stride_d, int64_t stride_l, int P,
+                      int64_t nq, int k, int metric, float* out_dist, int64_t* out_labels,
+                      cudaStream_t stream);
 // rows[0 .. *count) = ascending indices q with dirty[q] != 0; *count also goes to *count_copy.
 int launch_compact_rows(const int32_t* dirty, int64_t nq, int32_t* rows, int32_t* count,
                         int32_t* count_copy, cudaStream_t stream);

@@ -774,6 +774,9 @@ int launch_select_candidates(const float* cand_key, const int32_t* cand_idx, con
                              int64_t label_base, float* out_dist, int64_t* out_labels, int32_t* dirty,
                              cudaStream_t stream) {
     if (cap < 1 || !cand_cnt) return B200F_ERR_BAD_ARG;
+    if (rank_select_enabled() && rank_select_fits(cap, k) && dirty)
+        return launch_rank_select(cand_key, cand_idx, cand_cnt, cap, nb, nq, k, metric, qnorm, label_base,
+                                  out_dist, out_labels, dirty, stream);
     const bool l2 = metric == B200F_METRIC_L2;
     SortSelectParams p{};
     p.keys = cand_key;
@@ -949,6 +952,9 @@ extern "C" int b200f_merge_lists_strided(const float* dist, const int64_t* label
         B200F_LAUNCH_CHECK();
         return B200F_OK;
     }
+    if (rank_select_enabled() && rank_merge_fits(P, k))
+        return launch_rank_merge(dist, labels, list_stride_dist, list_stride_labels, P, nq, k, metric, out_dist,
+                                 out_labels, st);
     SortSelectParams p{};
     p.keys = dist;
     p.labels = labels;

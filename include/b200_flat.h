@@ -102,6 +102,12 @@ int b200f_get_selection_mode(void);
 #define B200F_GEMM_SHAPE_SINGLE 0
 #define B200F_GEMM_SHAPE_PAIR 1
 int b200f_set_gemm_shape(int shape);
+/* Selection of more than 32 results from at most 8192 entries per row (a row's threshold-filtered
+ * candidates; the sorted lists of up to 8192 / k shards): with on != 0 (the default) the kernels
+ * that sort in registers and place every entry by binary search, else the shared-memory sorting
+ * kernel that also serves larger inputs.  Results are identical; a testing aid.  No counterpart
+ * in the reference (its block_select, shaders/block_select.metal:111-274, is the one kernel). */
+int b200f_set_rank_select(int on);
 /* Debug canaries, the stand-in for a memory checker on the scratch arena: with on != 0 every
  * slice of a search's scratch region is followed by a 256-byte guard that is filled before the
  * search and compared after it; a kernel that wrote past its slice sets bit 8 of status[0]
