@@ -118,8 +118,10 @@ int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscal
                        int32_t* cand_cnt, int cand_cap, int few_hits, int32_t* status,
                        cudaStream_t stream);
 // Store mode: out[row*ld + (col-col0)] = sign*(-kscale*t) + rowadd[row], t = q.x (- ||x||^2/2).
+// tile_stride > 1 visits only every tile_stride-th column tile (plan made for that many tiles);
+// the visited tiles lie side by side in out.
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                      float kscale, float sign, const float* rowadd, float* out,
+                      int64_t tile_stride, float kscale, float sign, const float* rowadd, float* out,
                       int64_t ld, int32_t* status, cudaStream_t stream);
 
 // select.cu
@@ -136,6 +138,10 @@ int launch_merge_partials(const float* part_key, const int32_t* part_idx, int P,
 // Merged raw keys only: out_key[q][k], best first, +INF where fewer than k entries exist.
 int launch_merge_keys(const float* part_key, const int32_t* part_idx, int P, int64_t nq, int k,
                       float* out_key, cudaStream_t stream);
+// The r <= 32 smallest keys of every row of a key matrix (no ids): out_key[q][r], best first,
+// +INF where the row has fewer.  One warp per row.
+int launch_select_keys(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int r, float* out_key,
+                       cudaStream_t stream);
 // nq_dev (optional): number of live rows, read on the device.
 int launch_select_chunk(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int64_t col0,
                         int k, int has_prev, float* run_key, int32_t* run_idx, const int* nq_dev,

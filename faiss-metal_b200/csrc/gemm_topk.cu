@@ -745,7 +745,7 @@ gemm_topk_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         __syncwarp();
                         const int64_t grow0 = grow - lane;  // first row of this warp's 32 rows
                         const bool col_ok = cbase + lane < p.ncols_end;
-                        float* obase = p.out + (cbase - p.col0) + lane;
+                        float* obase = p.out + (t * TILE_N + ch * 32) + lane;   // tiles lie side by side, whatever the stride
 #pragma unroll 8
                         for (int rr = 0; rr < 32; rr++) {
                             const float v = tbuf[rr * 33 + lane];
@@ -1078,10 +1078,11 @@ int launch_gemm_filter(const GemmOperands& op, const GemmPlan& plan, float kscal
 }
 
 int launch_gemm_store(const GemmOperands& op, const GemmPlan& plan, int64_t col0, int64_t ncols,
-                      float kscale, float sign, const float* rowadd, float* out,
+                      int64_t tile_stride, float kscale, float sign, const float* rowadd, float* out,
                       int64_t ld, int32_t* status, cudaStream_t stream) {
     GemmParams p{};
     p.mode = MODE_STORE;
+    p.tile_stride = tile_stride;
     p.k = 0;
     p.kscale = kscale;
     p.sign = sign;

@@ -62,6 +62,7 @@ struct SearchPlan {
     int frank;        // threshold = frank-th best key of the pilot sample
     int fcap;         // candidate buffer entries per query
     GemmPlan pilot;
+    bool pilot_matrix; // pilot sample as a key matrix (store mode + key selection) instead of lists
     int npl;
     int64_t a_pitch, a_plane_stride;
     GemmPlan gemm;    // tensor path (fused: whole shard; chunked: per chunk)
@@ -230,6 +231,11 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
         if (cols > nb_pad) cols = nb_pad;
         pl.chunk_cols = cols;
         if (!pl.lists && !pl.filter) pl.gemm = plan_gemm(nq, cols, sm);
+        // A list starts empty and takes every key of its first tile: ~0.1 ms per work item, and a
+        // small shard's pilot is all first tiles.  Where the sample's keys fit the matrix slice
+        // they are written out instead and the frank best picked by a selection kernel.
+        pl.pilot_matrix = pl.filter && rank_select_enabled() &&
+                          pl.pilot.ntiles * pl.pilot.tile_n <= cols;
         pl.off_matrix = off;
         adv((size_t)(nq > 0 ? nq : 1) * cols * 4);
         pl.off_run_key = off;
@@ -621,11 +627,26 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
         int32_t* cidx = reinterpret_cast<int32_t*>(scratch + pl.off_cand_idx);
         int32_t* ccnt = reinterpret_cast<int32_t*>(scratch + pl.off_cand_cnt);
         int32_t* dirty = reinterpret_cast<int32_t*>(scratch + pl.off_dirty);
-        rc = launch_gemm_topk(op, pl.pilot, 0, a->nb, pl.fstride, kscale, pl.frank, 1, pkey, pidx, gthr,
-                              a->status, st);
-        if (rc != B200F_OK) return rc;
-        rc = launch_merge_keys(pkey, pidx, 2 * pl.pilot.P, a->nq, pl.frank, thr, st);
-        if (rc != B200F_OK) return rc;
+        if (pl.pilot_matrix) {
+            // every fstride-th column tile, side by side in the matrix slice; the last one may be partial
+            float* matrix = reinterpret_cast<float*>(scratch + pl.off_matrix);
+            const int64_t pcols = pl.pilot.ntiles * pl.pilot.tile_n;
+            const int64_t last0 = (pl.pilot.ntiles - 1) * pl.fstride * pl.pilot.tile_n;
+            int64_t last_valid = a->nb - last0;
+            if (last_valid > pl.pilot.tile_n) last_valid = pl.pilot.tile_n;
+            const int64_t valid = (pl.pilot.ntiles - 1) * pl.pilot.tile_n + last_valid;
+            rc = launch_gemm_store(op, pl.pilot, 0, a->nb, pl.fstride, kscale, 1.f, nullptr, matrix, pcols,
+                                   a->status, st);
+            if (rc != B200F_OK) return rc;
+            rc = launch_select_keys(matrix, a->nq, valid, pcols, pl.frank, thr, st);
+            if (rc != B200F_OK) return rc;
+        } else {
+            rc = launch_gemm_topk(op, pl.pilot, 0, a->nb, pl.fstride, kscale, pl.frank, 1, pkey, pidx, gthr,
+                                  a->status, st);
+            if (rc != B200F_OK) return rc;
+            rc = launch_merge_keys(pkey, pidx, 2 * pl.pilot.P, a->nq, pl.frank, thr, st);
+            if (rc != B200F_OK) return rc;
+        }
         // candidates per row ~ frank * fstride: a few hundred for k <= 128, thousands beyond
         rc = launch_gemm_filter(op, pl.gemm, kscale, thr, pl.frank, pl.frank - 1, ckey, cidx, ccnt,
                                 pl.fcap, pl.fstride == 64 ? 1 : 0, a->status, st);
@@ -697,7 +718,7 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
         const int64_t nc = (a->nb - c0) < pl.chunk_cols ? (a->nb - c0) : pl.chunk_cols;
         if (pl.path == B200F_PATH_TENSOR) {
             GemmPlan g = plan_gemm(a->nq, nc, sm);
-            rc = launch_gemm_store(op, g, c0, nc, kscale, 1.f, nullptr, matrix, pl.chunk_cols,
+            rc = launch_gemm_store(op, g, c0, nc, 1, kscale, 1.f, nullptr, matrix, pl.chunk_cols,
                                    a->status, st);
             if (rc != B200F_OK) return rc;
         } else {
@@ -764,7 +785,7 @@ extern "C" int b200f_pairwise(const B200FSearchArgs* a, float* out_matrix, int64
                                     pl.a_plane_stride, qnorm, l2 ? 1 : 0, a->plane_format, a->plane_scale_log2,
                                     reinterpret_cast<float*>(scratch + pl.off_qscale), st);
         if (rc != B200F_OK) return rc;
-        return launch_gemm_store(op, pl.gemm, 0, a->nb, kscale, l2 ? 1.f : -1.f,
+        return launch_gemm_store(op, pl.gemm, 0, a->nb, 1, kscale, l2 ? 1.f : -1.f,
                                  l2 ? qnorm : nullptr, out_matrix, ld_out, a->status, st);
     }
     rc = launch_prepare_queries(a->queries, a->nq, a->d, a->storage, nullptr, 0, 0, qnorm, 0, 0, 0, nullptr, st);

@@ -566,6 +566,51 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_small_kernel(const Sort
     }
 }
 
+// The r <= 32 smallest keys of a matrix row (the pilot sample of the threshold filter): one warp
+// per row reads 128 columns at a time; a key under the current r-th best is inserted into the
+// warp's sorted list (lane j = rank j).  About r ln(n / r) + r insertions per row.
+__global__ void __launch_bounds__(SEL_WARPS * 32) select_keys_kernel(const float* __restrict__ keys, int64_t nq,
+                                                                     int64_t ncols, int64_t ld, int r,
+                                                                     float* __restrict__ out_key) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * SEL_WARPS + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * SEL_WARPS;
+    const bool vec = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(keys) & 15) == 0);
+    for (int64_t q = warp0; q < nq; q += nwarps) {
+        const float* row = keys + q * ld;
+        float lk = CUDART_INF_F;
+        float thr = CUDART_INF_F;
+        for (int64_t base = 0; base < ncols; base += 128) {
+            const int64_t c = base + lane * 4;
+            float v[4];
+            if (vec && c + 4 <= ncols) {
+                const float4 f = __ldg(reinterpret_cast<const float4*>(row + c));
+                v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) v[e] = (c + e < ncols) ? __ldg(row + c + e) : CUDART_INF_F;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                unsigned m = __ballot_sync(FULL, v[e] < thr);   // NaN never qualifies
+                while (m) {
+                    const int src = __ffs(m) - 1;
+                    m &= m - 1;
+                    const float s = __shfl_sync(FULL, v[e], src);
+                    if (s < thr) {   // the bound moved since the ballot
+                        const int pos = __popc(__ballot_sync(FULL, lk <= s));
+                        const float up = __shfl_up_sync(FULL, lk, 1);
+                        if (lane == pos) lk = s;
+                        else if (lane > pos) lk = up;
+                        thr = __shfl_sync(FULL, lk, r - 1);
+                    }
+                }
+            }
+        }
+        if (lane < r) out_key[q * r + lane] = lk;
+    }
+}
+
 // rows[0 .. n) = ascending q with flag[q] != 0, n -> *count (one CTA)
 __global__ void __launch_bounds__(1024) compact_rows_kernel(const int32_t* __restrict__ flag, int64_t nq,
                                                             int32_t* __restrict__ rows,
@@ -720,6 +765,19 @@ int launch_merge_keys(const float* part_key, const int32_t* part_idx, int P, int
     const int64_t cap = (int64_t)cached_sm_count() * 32;
     if (g > cap) g = cap;
     merge_small_kernel<int32_t><<<(int)g, MS_THREADS, 0, stream>>>(p);
+    count_launch();
+    B200F_LAUNCH_CHECK();
+    return B200F_OK;
+}
+
+int launch_select_keys(const float* keys, int64_t nq, int64_t ncols, int64_t ld, int r, float* out_key,
+                       cudaStream_t stream) {
+    if (r < 1 || r > 32 || ncols < 0 || ld < ncols || !keys || !out_key) return B200F_ERR_BAD_ARG;
+    if (nq <= 0) return B200F_OK;
+    int64_t g = ceil_div64(nq, SEL_WARPS);
+    const int64_t gcap = (int64_t)cached_sm_count() * 8;
+    if (g > gcap) g = gcap;
+    select_keys_kernel<<<(int)g, SEL_WARPS * 32, 0, stream>>>(keys, nq, ncols, ld, r, out_key);
     count_launch();
     B200F_LAUNCH_CHECK();
     return B200F_OK;
