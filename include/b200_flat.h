@@ -90,7 +90,7 @@ const char* b200f_status_string(int status);
  * Until the setter is called the default comes from the environment variable
  * B200F_SELECT_MODE (auto | filter | no_filter | matrix), which is read once, at the first
  * search; nothing else in the search path reads the environment. */
-#define B200F_SELECT_AUTO 0       /* threshold filter from 2^27 (query, row) pairs, 32-entry lists below */
+#define B200F_SELECT_AUTO 0       /* threshold filter from 2^27 (query, row) pairs (2^22 where the pilot sample fits a key matrix), 32-entry lists below */
 #define B200F_SELECT_FILTER 1     /* threshold filter wherever the shard allows a pilot sample */
 #define B200F_SELECT_NO_FILTER 2  /* never the threshold filter                                */
 #define B200F_SELECT_MATRIX 3     /* neither filter nor lists: fused lists (k <= 32), key matrix beyond */
