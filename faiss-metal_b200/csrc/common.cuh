@@ -72,8 +72,10 @@ struct ScanPlan {
 };
 ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count);
 // *out_P receives the number of partial lists per query actually written (<= plan.grid).
+// stream_f32: FP32 rows may take the streaming tf32 kernel (up to 8 queries); the caller must pass
+// the same value for every query group of a search, since the kernels write different list counts.
 int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part_key,
-                     int32_t* part_idx, int* out_P, cudaStream_t stream);
+                     int32_t* part_idx, int* out_P, bool stream_f32, cudaStream_t stream);
 // Scan that stores keys (smaller = better) to a matrix [nq][ld] for columns [col0, col0+ncols).
 int launch_scan_store(const B200FSearchArgs& a, int64_t col0, int64_t ncols, float* out,
                       int64_t ld, int sm_count, cudaStream_t stream);

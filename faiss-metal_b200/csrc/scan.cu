@@ -604,6 +604,294 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same streaming pipeline for FP32 rows: mma.sync m16n8k8 on a tf32 split.  A value is
+// x = hi + lo with hi = tf32(x), lo = tf32(x - hi) (21 mantissa bits between them); the three
+// products hi*hi, lo*hi, hi*lo accumulate in fp32 and leave about 2^-21 of the result out, as an
+// fp32 FMA chain would.  The rows are split on the fly (two conversions and a subtraction per
+// element), the queries once into two matrices.  K is permuted as in the 16-bit kernel: per
+// 16-column chunk a lane takes the 16 bytes at column 16c + 4t of rows g and g+8, floats 0 / 1 feed
+// k-slots t / t+4 of the first MMA, floats 2 / 3 those of the second, and the query matrices are read
+// with the same pattern.  ||x||^2 comes from the norm array (FP32 rows carry no norm columns).
+// Up to 8 queries per pass, one dot product per (row, query) on the tensor pipe instead of d FMAs
+// and a shuffle reduction: what held the FMA kernel to 86 % / 62 % of the copy bandwidth at 2 / 4
+// queries.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ void mma1688_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+            "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int ST_QPAD = 16;   // floats between query rows beyond kq: rows 64 bytes apart in bank space
+
+__global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanParams p) {
+    extern __shared__ __align__(128) uint8_t sm[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t sbase = smem_u32(sm);
+    const int ring_bytes = p.nstage * p.stage_stride;
+    const int nchunk = p.iters;          // 16-column chunks per row
+    const int kq = nchunk * 16;
+    const int qpitch = kq + ST_QPAD;     // floats
+    float* sqh = reinterpret_cast<float*>(sm + ring_bytes);      // [8][qpitch] hi parts
+    float* sql = sqh + SM_NQ * qpitch;                           // [8][qpitch] lo parts
+    const int qbytes = 2 * SM_NQ * qpitch * 4;
+    const uint32_t bar_full = sbase + ring_bytes + qbytes;
+    const uint32_t bar_empty = bar_full + SM_MAX_STAGES * 8;
+    volatile int* abort_flag =
+            reinterpret_cast<volatile int*>(sm + ring_bytes + qbytes + 2 * SM_MAX_STAGES * 8);
+    const int kext = (p.d + 3) & ~3;     // floats of a row that are read (zero padded by the store)
+
+    for (int i = threadIdx.x; i < SM_NQ * qpitch; i += SM_THREADS) {
+        const int qi = i / qpitch;
+        const int j = i - qi * qpitch;
+        float v = 0.f;
+        if (qi < p.nq && j < p.d) v = p.queries[(int64_t)qi * p.d + j];
+        const float hi = __uint_as_float(to_tf32(v));
+        sqh[i] = hi;
+        sql[i] = __uint_as_float(to_tf32(v - hi));
+    }
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < p.nstage; s++) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, SM_NW);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int64_t nrows_total = p.col1 - p.col0;
+    const int64_t nchunks = ceil_div64(nrows_total, p.stage_rows);
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(p.rows);
+    const bool l2 = p.metric == B200F_METRIC_L2;
+
+    float lk[SM_NQ];
+    int li[SM_NQ];
+    float thr[SM_NQ];
+    int thr_id[SM_NQ];
+#pragma unroll
+    for (int qi = 0; qi < SM_NQ; qi++) {
+        lk[qi] = CUDART_INF_F;
+        li[qi] = -1;
+        thr[qi] = CUDART_INF_F;
+        thr_id[qi] = -1;
+    }
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+                if (!mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status,
+                                       kDevErrBarrierWait)) {
+                    ok = false;
+                    break;
+                }
+                const int64_t row0 = p.col0 + c * p.stage_rows;
+                const int64_t nr = min((int64_t)p.stage_rows, p.col1 - row0);
+                const uint32_t bytes = (uint32_t)(nr * p.pitch_bytes);
+                mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
+                bulk_load(sbase + stage * p.stage_stride, base + row0 * p.pitch_bytes, bytes,
+                          bar_full + stage * 8);
+                if (++stage == p.nstage) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) {  // let copies already issued land before shared memory goes away
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000LL) {
+                }
+            }
+        }
+    } else {
+        const int wc = warp - 1;
+        const int g = lane >> 2;
+        const int t = lane & 3;
+        int stage = 0;
+        uint32_t phase = 0;
+        float mta, mtb;
+        int mia, mib;
+        auto refresh_bounds = [&]() {
+            mta = t == 0 ? thr[0] : t == 1 ? thr[2] : t == 2 ? thr[4] : thr[6];
+            mtb = t == 0 ? thr[1] : t == 1 ? thr[3] : t == 2 ? thr[5] : thr[7];
+            mia = t == 0 ? thr_id[0] : t == 1 ? thr_id[2] : t == 2 ? thr_id[4] : thr_id[6];
+            mib = t == 0 ? thr_id[1] : t == 1 ? thr_id[3] : t == 2 ? thr_id[5] : thr_id[7];
+            if (2 * t >= p.nq) mta = -CUDART_INF_F;
+            if (2 * t + 1 >= p.nq) mtb = -CUDART_INF_F;
+        };
+        refresh_bounds();
+        const uint32_t bh_row = sbase + ring_bytes + (uint32_t)(g * qpitch * 4) + t * 16;
+        const uint32_t bl_row = bh_row + (uint32_t)(SM_NQ * qpitch * 4);
+        for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+            const bool w = mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status,
+                                             kDevErrBarrierWait);
+            if (!__all_sync(FULL, w)) break;
+            const int64_t row0 = p.col0 + c * p.stage_rows;
+            const int nr = (int)min((int64_t)p.stage_rows, p.col1 - row0);
+            const uint32_t sstage = sbase + stage * p.stage_stride;
+            const int ntiles = (nr + 15) >> 4;
+            for (int tile = wc; tile < ntiles; tile += SM_NW) {
+                const int r0 = tile * 16 + g;      // local rows of this lane
+                const int r1 = r0 + 8;
+                const bool v0 = r0 < nr, v1 = r1 < nr;
+                float n0 = 0.f, n1 = 0.f;
+                if (l2) {
+                    if (v0) n0 = __ldg(p.norms + row0 + r0);
+                    if (v1) n1 = __ldg(p.norms + row0 + r1);
+                }
+                const uint32_t a_row0 = sstage + (uint32_t)r0 * (uint32_t)p.pitch_bytes + t * 16;
+                const uint32_t a_row1 = sstage + (uint32_t)r1 * (uint32_t)p.pitch_bytes + t * 16;
+                // one accumulator per product kind: three short dependent MMA chains, not one long
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                float acc_lh[4] = {0.f, 0.f, 0.f, 0.f};
+                float acc_hl[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+                for (int ch = 0; ch < nchunk; ch++) {
+                    const bool kv = ch * 16 + t * 4 < kext;  // beyond the row: the next row's bytes
+                    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+                    if (kv && v0) x0 = lds128(a_row0 + ch * 64);
+                    if (kv && v1) x1 = lds128(a_row1 + ch * 64);
+                    const uint4 qh = lds128(bh_row + ch * 64);
+                    const uint4 ql = lds128(bl_row + ch * 64);
+                    const uint32_t xs0[4] = {x0.x, x0.y, x0.z, x0.w};
+                    const uint32_t xs1[4] = {x1.x, x1.y, x1.z, x1.w};
+                    uint32_t h0[4], l0[4], h1[4], l1[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float f0 = __uint_as_float(xs0[e]), f1 = __uint_as_float(xs1[e]);
+                        h0[e] = to_tf32(f0);
+                        h1[e] = to_tf32(f1);
+                        l0[e] = to_tf32(f0 - __uint_as_float(h0[e]));
+                        l1[e] = to_tf32(f1 - __uint_as_float(h1[e]));
+                    }
+                    // A fragment: a0 = row g slot t, a1 = row g+8 slot t, a2 = row g slot t+4,
+                    // a3 = row g+8 slot t+4
+                    mma1688_tf32(acc_lh, l0[0], l1[0], l0[1], l1[1], qh.x, qh.y);
+                    mma1688_tf32(acc_hl, h0[0], h1[0], h0[1], h1[1], ql.x, ql.y);
+                    mma1688_tf32(acc, h0[0], h1[0], h0[1], h1[1], qh.x, qh.y);
+                    mma1688_tf32(acc_lh, l0[2], l1[2], l0[3], l1[3], qh.z, qh.w);
+                    mma1688_tf32(acc_hl, h0[2], h1[2], h0[3], h1[3], ql.z, ql.w);
+                    mma1688_tf32(acc, h0[2], h1[2], h0[3], h1[3], qh.z, qh.w);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[e] += acc_lh[e] + acc_hl[e];
+                // acc[0]: (row r0, query 2t)  acc[1]: (r0, 2t+1)  acc[2]: (r1, 2t)  acc[3]: (r1, 2t+1)
+                float key[4];
+                key[0] = l2 ? fmaf(-2.f, acc[0], n0) : -acc[0];
+                key[1] = l2 ? fmaf(-2.f, acc[1], n0) : -acc[1];
+                key[2] = l2 ? fmaf(-2.f, acc[2], n1) : -acc[2];
+                key[3] = l2 ? fmaf(-2.f, acc[3], n1) : -acc[3];
+                {
+                    const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
+                    const bool any_hit =
+                            (v0 && (before(key[0], row_a, mta, mia) || before(key[1], row_a, mtb, mib))) ||
+                            (v1 && (before(key[2], row_b, mta, mia) || before(key[3], row_b, mtb, mib)));
+                    if (!__any_sync(FULL, any_hit)) continue;  // the usual case: nothing for any query
+                }
+#pragma unroll
+                for (int qi = 0; qi < SM_NQ; qi++) {
+                    if (qi >= p.nq) break;
+                    const bool mine = (qi >> 1) == t;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const float kk = (qi & 1) ? key[2 * h + 1] : key[2 * h];
+                        const int row = (int)(row0 + (h ? r1 : r0));
+                        const bool hit = mine && (h ? v1 : v0) && before(kk, row, thr[qi], thr_id[qi]);
+                        unsigned m = __ballot_sync(FULL, hit);
+                        while (m) {
+                            const int src = __ffs(m) - 1;
+                            m &= m - 1;
+                            const float s = __shfl_sync(FULL, kk, src);
+                            const int id = __shfl_sync(FULL, row, src);
+                            if (before(s, id, thr[qi], thr_id[qi])) {
+                                warp_insert(lk[qi], li[qi], s, id, lane);
+                                thr[qi] = __shfl_sync(FULL, lk[qi], p.k - 1);
+                                thr_id[qi] = __shfl_sync(FULL, li[qi], p.k - 1);
+                            }
+                        }
+                    }
+                }
+                refresh_bounds();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+            if (++stage == p.nstage) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+    }
+
+    // CTA merge in the (now idle) ring memory, as in scan_mma_kernel
+    __syncthreads();
+    float* mk = reinterpret_cast<float*>(sm);                        // [SM_NW][SM_NQ][32]
+    int* mi = reinterpret_cast<int*>(sm) + SM_NW * SM_NQ * 32;
+    if (warp > 0) {
+#pragma unroll
+        for (int qi = 0; qi < SM_NQ; qi++) {
+            mk[((warp - 1) * SM_NQ + qi) * 32 + lane] = lk[qi];
+            mi[((warp - 1) * SM_NQ + qi) * 32 + lane] = li[qi];
+        }
+    }
+    __syncthreads();
+    if (warp >= 1 && warp - 1 < p.nq) {
+        const int qi = warp - 1;
+        float k0 = mk[qi * 32 + lane];
+        int i0 = mi[qi * 32 + lane];
+        float tk = __shfl_sync(FULL, k0, p.k - 1);
+        int tid = __shfl_sync(FULL, i0, p.k - 1);
+        for (int w2 = 1; w2 < SM_NW; w2++) {
+            for (int j = 0; j < p.k; j++) {
+                const float s = mk[(w2 * SM_NQ + qi) * 32 + j];
+                const int id = mi[(w2 * SM_NQ + qi) * 32 + j];
+                if (id < 0 || !before(s, id, tk, tid)) break;
+                warp_insert(k0, i0, s, id, lane);
+                tk = __shfl_sync(FULL, k0, p.k - 1);
+                tid = __shfl_sync(FULL, i0, p.k - 1);
+            }
+        }
+        if (lane < p.k) {
+            const int64_t o = ((int64_t)qi * gridDim.x + blockIdx.x) * p.k + lane;
+            p.part_key[o] = k0;
+            p.part_idx[o] = i0;
+        }
+    }
+}
+
+// Stage geometry of the FP32 streaming pipeline; false when it does not apply.
+bool plan_stream_f32(ScanParams& p, int d) {
+    if ((p.pitch_bytes % 16) != 0 || (reinterpret_cast<uintptr_t>(p.rows) & 15) != 0) return false;
+    if ((int64_t)((d + 3) & ~3) * 4 > p.pitch_bytes) return false;
+    p.norm_cols = 0;
+    p.iters = (d + 15) / 16;                    // 16-column chunks
+    int64_t rows = (36 * 1024) / p.pitch_bytes; // ~36 KiB per stage
+    rows = rows / 16 * 16;
+    if (rows < 16) rows = 16;
+    if (rows > 16 * SM_NW * 2) rows = 16 * SM_NW * 2;
+    p.stage_rows = (int)rows;
+    p.rb = 16;
+    p.stage_stride = (int)round_up64((int64_t)p.stage_rows * p.pitch_bytes + 64, 128);
+    const int64_t fixed = (int64_t)2 * SM_NQ * (p.iters * 16 + ST_QPAD) * 4 + 2 * SM_MAX_STAGES * 8 + 16;
+    int64_t ns = (220 * 1024 - fixed) / p.stage_stride;
+    if (ns > SM_MAX_STAGES) ns = SM_MAX_STAGES;
+    p.nstage = (int)ns;
+    // the CTA merge reuses the ring: SM_NW * SM_NQ * 32 (key, id) pairs
+    return ns >= 3 && (int64_t)p.nstage * p.stage_stride >= (int64_t)SM_NW * SM_NQ * 32 * 8;
+}
+
 size_t scan_smem_bytes(int nq_t, int qstride) {
     size_t a = (size_t)nq_t * qstride * 4;
     size_t b = (size_t)SCAN_WARPS * nq_t * 32 * 8;
@@ -722,7 +1010,7 @@ ScanPlan plan_scan(int64_t nq, int64_t nb, int d, int storage, int sm_count) {
 }
 
 int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part_key,
-                     int32_t* part_idx, int* out_P, cudaStream_t stream) {
+                     int32_t* part_idx, int* out_P, bool stream_f32, cudaStream_t stream) {
     if (a.nq < 1 || a.nq > 8 || a.k < 1 || a.k > 32) return B200F_ERR_UNSUPPORTED;
     ScanParams p{};
     fill_geometry(p, a.storage, a.d, a.row_pitch, a.metric == B200F_METRIC_L2 ? a.norm_cols : 0,
@@ -763,6 +1051,24 @@ int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part
                 main_kernel_begin(stream);
                 scan_mma_kernel<false><<<grid, SM_THREADS, smem, stream>>>(ps);
             }
+            main_kernel_end(stream);
+            count_launch();
+            B200F_LAUNCH_CHECK();
+            return B200F_OK;
+        }
+    }
+    if (a.storage == B200F_STORAGE_F32 && stream_f32 && (a.metric != B200F_METRIC_L2 || a.norms)) {
+        ScanParams ps = p;
+        if (plan_stream_f32(ps, a.d) && a.nb >= (int64_t)ps.stage_rows * sm) {
+            const int64_t nchunks = ceil_div64(a.nb, ps.stage_rows);
+            const int grid = (int)(nchunks < sm ? nchunks : sm);
+            const size_t smem = (size_t)ps.nstage * ps.stage_stride +
+                                (size_t)2 * SM_NQ * (ps.iters * 16 + ST_QPAD) * 4 + 2 * SM_MAX_STAGES * 8 + 16;
+            *out_P = grid;
+            B200F_CUDA_TRY(cudaFuncSetAttribute(scan_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)smem));
+            main_kernel_begin(stream);
+            scan_tf32_kernel<<<grid, SM_THREADS, smem, stream>>>(ps);
             main_kernel_end(stream);
             count_launch();
             B200F_LAUNCH_CHECK();

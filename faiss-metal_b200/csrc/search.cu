@@ -107,6 +107,7 @@ bool lists_disabled() { return select_mode() == B200F_SELECT_MATRIX; }
 // its lists on a single tile).  Measured: at 2.6e8 (query, row) pairs the filter path is 19 - 47 %
 // faster than the lists (d = 768 / 1536, 16-bit rows), at 1e8 - 4e8 pairs of fp32 rows with
 // d = 128 the two are level; below this many pairs the lists are used.
+constexpr int64_t F32_STREAM_MIN_ROWS = 65536;   // fp32 rows: from here the tf32 streaming scan applies
 constexpr int64_t FILTER_MIN_PAIRS = 1ll << 27;
 constexpr int64_t FILTER_MIN_PAIRS_MATRIX = 1ll << 22;
 constexpr int64_t PILOT_MATRIX_BYTES = 256ll << 20;   // k <= 32: largest pilot sample kept as a key matrix
@@ -128,10 +129,11 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     const int sm = cached_sm_count();
     pl = SearchPlan{};
     pl.path = path;
-    // 16-bit rows: the streaming scan takes up to 8 queries per pass at HBM speed, which beats a
-    // 128-row tensor tile that is mostly padding; fp32 rows: 4 per pass (the reference's limit,
+    // the streaming scans take up to 8 queries per pass, which beats a 128-row tensor tile that is
+    // mostly padding (measured on 12.5 M fp32 rows of d = 128, 8 queries: 1.7 against 4.1 ms); fp32
+    // shards too small for the streaming kernel: 4 per pass (the reference's limit,
     // src/MetalDistance.mm:346-354)
-    const int64_t scan_limit = (storage == B200F_STORAGE_F32) ? SCAN_GROUP : 2 * SCAN_GROUP;
+    const int64_t scan_limit = (storage == B200F_STORAGE_F32 && nb < F32_STREAM_MIN_ROWS) ? SCAN_GROUP : 2 * SCAN_GROUP;
     if (path == B200F_PATH_AUTO) pl.path = (nq <= scan_limit) ? B200F_PATH_SCAN : B200F_PATH_TENSOR;
     pl.fused = (k <= B200F_FUSED_MAX_K) && !pairwise;
     pl.npl = (storage == B200F_STORAGE_F32) ? 3 : 1;
@@ -699,17 +701,20 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
             if (rc != B200F_OK) return rc;
         } else {
             // every group of queries writes the same number of lists (same shard, same
-            // geometry); the first launch reports it.  Groups of 8 where the streaming kernel
-            // applies (16-bit rows, shard large enough), else of 4.
+            // geometry); the first launch reports it.  Groups of 8 where a streaming kernel
+            // applies (shard large enough), else of 4.
             P = pl.scan.grid;
-            int64_t group = (a->storage != B200F_STORAGE_F32 && a->nq > SCAN_GROUP) ? 2 * SCAN_GROUP : SCAN_GROUP;
+            // FP32 rows: the streaming tf32 kernel takes up to 8 queries per pass at 3.8 TB/s whatever
+            // their number; the FMA kernel is faster up to four (6.9 / 5.6 / 4.1 TB/s for 1 / 2 / 4)
+            const bool stream_f32 = a->nq > SCAN_GROUP;
+            int64_t group = a->nq > SCAN_GROUP ? 2 * SCAN_GROUP : SCAN_GROUP;
             for (int64_t q0 = 0; q0 < a->nq;) {
                 B200FSearchArgs sub = *a;
                 sub.queries = a->queries + q0 * (int64_t)a->d;
                 sub.nq = (a->nq - q0) < group ? (a->nq - q0) : group;
                 int Pg = P;
                 rc = launch_scan_topk(sub, pl.scan, part_key + q0 * (int64_t)P * a->k,
-                                      part_idx + q0 * (int64_t)P * a->k, &Pg, st);
+                                      part_idx + q0 * (int64_t)P * a->k, &Pg, stream_f32, st);
                 if (rc == B200F_ERR_UNSUPPORTED && q0 == 0 && group > SCAN_GROUP) {
                     group = SCAN_GROUP;  // no streaming kernel for this shape: nothing was launched
                     continue;
