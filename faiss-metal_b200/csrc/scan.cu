@@ -633,8 +633,10 @@ __device__ __forceinline__ void mma1688_tf32(float (&c)[4], uint32_t a0, uint32_
 }
 
 constexpr int ST_QPAD = 16;   // floats between query rows beyond kq: rows 64 bytes apart in bank space
+constexpr int ST_NW = 15;     // consumer warps: the split and the three MMA chains of a tile are latency, not issue, bound
+constexpr int ST_THREADS = 32 * (1 + ST_NW);
 
-__global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(ST_THREADS, 1) scan_tf32_kernel(const ScanParams p) {
     extern __shared__ __align__(128) uint8_t sm[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -652,7 +654,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
             reinterpret_cast<volatile int*>(sm + ring_bytes + qbytes + 2 * SM_MAX_STAGES * 8);
     const int kext = (p.d + 3) & ~3;     // floats of a row that are read (zero padded by the store)
 
-    for (int i = threadIdx.x; i < SM_NQ * qpitch; i += SM_THREADS) {
+    for (int i = threadIdx.x; i < SM_NQ * qpitch; i += ST_THREADS) {
         const int qi = i / qpitch;
         const int j = i - qi * qpitch;
         float v = 0.f;
@@ -665,7 +667,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
         *abort_flag = 0;
         for (int s = 0; s < p.nstage; s++) {
             mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, SM_NW);
+            mbar_init(bar_empty + s * 8, ST_NW);
         }
         mbar_fence_init();
     }
@@ -675,6 +677,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
     const int64_t nchunks = ceil_div64(nrows_total, p.stage_rows);
     const uint8_t* base = reinterpret_cast<const uint8_t*>(p.rows);
     const bool l2 = p.metric == B200F_METRIC_L2;
+    const uint32_t norm_off = (uint32_t)p.stage_rows * (uint32_t)p.pitch_bytes;   // norms of a stage, behind its rows
 
     float lk[SM_NQ];
     int li[SM_NQ];
@@ -702,9 +705,20 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
                 const int64_t row0 = p.col0 + c * p.stage_rows;
                 const int64_t nr = min((int64_t)p.stage_rows, p.col1 - row0);
                 const uint32_t bytes = (uint32_t)(nr * p.pitch_bytes);
-                mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
+                // the stage's norms ride behind its rows: whole 16-byte pieces by bulk copy, the
+                // up to three floats left of a last, ragged stage by plain stores (made visible
+                // by the arrive that follows them)
+                const uint32_t nbytes = l2 ? (uint32_t)(nr * 4) & ~15u : 0u;
+                if (l2) {
+                    float* sn = reinterpret_cast<float*>(sm + stage * p.stage_stride + norm_off);
+                    for (int64_t r = nbytes / 4; r < nr; r++) sn[r] = __ldg(p.norms + row0 + r);
+                }
+                mbar_arrive_expect_tx(bar_full + stage * 8, bytes + nbytes);
                 bulk_load(sbase + stage * p.stage_stride, base + row0 * p.pitch_bytes, bytes,
                           bar_full + stage * 8);
+                if (nbytes)
+                    bulk_load(sbase + stage * p.stage_stride + norm_off, p.norms + row0, nbytes,
+                              bar_full + stage * 8);
                 if (++stage == p.nstage) {
                     stage = 0;
                     phase ^= 1;
@@ -735,6 +749,10 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
         refresh_bounds();
         const uint32_t bh_row = sbase + ring_bytes + (uint32_t)(g * qpitch * 4) + t * 16;
         const uint32_t bl_row = bh_row + (uint32_t)(SM_NQ * qpitch * 4);
+        // A stage of wide rows holds fewer 16-row tiles than there are consumer warps: the first
+        // tile's owner moves on by that many warps from stage to stage, so all of them work.
+        const int tiles_full = p.stage_rows >> 4;
+        int shift = 0;
         for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
             const bool w = mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status,
                                              kDevErrBarrierWait);
@@ -742,15 +760,16 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
             const int64_t row0 = p.col0 + c * p.stage_rows;
             const int nr = (int)min((int64_t)p.stage_rows, p.col1 - row0);
             const uint32_t sstage = sbase + stage * p.stage_stride;
+            const float* snorm = reinterpret_cast<const float*>(sm + stage * p.stage_stride + norm_off);
             const int ntiles = (nr + 15) >> 4;
-            for (int tile = wc; tile < ntiles; tile += SM_NW) {
+            for (int tile = (wc - shift + ST_NW) % ST_NW; tile < ntiles; tile += ST_NW) {
                 const int r0 = tile * 16 + g;      // local rows of this lane
                 const int r1 = r0 + 8;
                 const bool v0 = r0 < nr, v1 = r1 < nr;
                 float n0 = 0.f, n1 = 0.f;
                 if (l2) {
-                    if (v0) n0 = __ldg(p.norms + row0 + r0);
-                    if (v1) n1 = __ldg(p.norms + row0 + r1);
+                    if (v0) n0 = snorm[r0];
+                    if (v1) n1 = snorm[r1];
                 }
                 const uint32_t a_row0 = sstage + (uint32_t)r0 * (uint32_t)p.pitch_bytes + t * 16;
                 const uint32_t a_row1 = sstage + (uint32_t)r1 * (uint32_t)p.pitch_bytes + t * 16;
@@ -758,7 +777,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 float acc_lh[4] = {0.f, 0.f, 0.f, 0.f};
                 float acc_hl[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
+#pragma unroll 4
                 for (int ch = 0; ch < nchunk; ch++) {
                     const bool kv = ch * 16 + t * 4 < kext;  // beyond the row: the next row's bytes
                     uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
@@ -794,23 +813,24 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
                 key[1] = l2 ? fmaf(-2.f, acc[1], n0) : -acc[1];
                 key[2] = l2 ? fmaf(-2.f, acc[2], n1) : -acc[2];
                 key[3] = l2 ? fmaf(-2.f, acc[3], n1) : -acc[3];
-                {
-                    const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
-                    const bool any_hit =
-                            (v0 && (before(key[0], row_a, mta, mia) || before(key[1], row_a, mtb, mib))) ||
-                            (v1 && (before(key[2], row_b, mta, mia) || before(key[3], row_b, mtb, mib)));
-                    if (!__any_sync(FULL, any_hit)) continue;  // the usual case: nothing for any query
-                }
+                // one vote per accumulator register: bit l of mj[j] = lane l's key j is a candidate
+                // (lane 4g + t holds query 2t in keys 0 / 2 and query 2t + 1 in keys 1 / 3)
+                const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
+                unsigned mj[4];
+                mj[0] = __ballot_sync(FULL, v0 && before(key[0], row_a, mta, mia));
+                mj[1] = __ballot_sync(FULL, v0 && before(key[1], row_a, mtb, mib));
+                mj[2] = __ballot_sync(FULL, v1 && before(key[2], row_b, mta, mia));
+                mj[3] = __ballot_sync(FULL, v1 && before(key[3], row_b, mtb, mib));
+                if (!(mj[0] | mj[1] | mj[2] | mj[3])) continue;  // the usual case: nothing for any query
 #pragma unroll
                 for (int qi = 0; qi < SM_NQ; qi++) {
                     if (qi >= p.nq) break;
-                    const bool mine = (qi >> 1) == t;
+                    const unsigned lanes_q = 0x11111111u << (qi >> 1);   // the lanes with t = qi / 2
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        const float kk = (qi & 1) ? key[2 * h + 1] : key[2 * h];
-                        const int row = (int)(row0 + (h ? r1 : r0));
-                        const bool hit = mine && (h ? v1 : v0) && before(kk, row, thr[qi], thr_id[qi]);
-                        unsigned m = __ballot_sync(FULL, hit);
+                        const float kk = key[2 * h + (qi & 1)];
+                        const int row = h ? row_b : row_a;
+                        unsigned m = mj[2 * h + (qi & 1)] & lanes_q;
                         while (m) {
                             const int src = __ffs(m) - 1;
                             m &= m - 1;
@@ -828,6 +848,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+            shift = (shift + tiles_full) % ST_NW;
             if (++stage == p.nstage) {
                 stage = 0;
                 phase ^= 1;
@@ -837,8 +858,8 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
 
     // CTA merge in the (now idle) ring memory, as in scan_mma_kernel
     __syncthreads();
-    float* mk = reinterpret_cast<float*>(sm);                        // [SM_NW][SM_NQ][32]
-    int* mi = reinterpret_cast<int*>(sm) + SM_NW * SM_NQ * 32;
+    float* mk = reinterpret_cast<float*>(sm);                        // [ST_NW][SM_NQ][32]
+    int* mi = reinterpret_cast<int*>(sm) + ST_NW * SM_NQ * 32;
     if (warp > 0) {
 #pragma unroll
         for (int qi = 0; qi < SM_NQ; qi++) {
@@ -853,7 +874,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
         int i0 = mi[qi * 32 + lane];
         float tk = __shfl_sync(FULL, k0, p.k - 1);
         int tid = __shfl_sync(FULL, i0, p.k - 1);
-        for (int w2 = 1; w2 < SM_NW; w2++) {
+        for (int w2 = 1; w2 < ST_NW; w2++) {
             for (int j = 0; j < p.k; j++) {
                 const float s = mk[(w2 * SM_NQ + qi) * 32 + j];
                 const int id = mi[(w2 * SM_NQ + qi) * 32 + j];
@@ -874,22 +895,23 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_tf32_kernel(const ScanPara
 // Stage geometry of the FP32 streaming pipeline; false when it does not apply.
 bool plan_stream_f32(ScanParams& p, int d) {
     if ((p.pitch_bytes % 16) != 0 || (reinterpret_cast<uintptr_t>(p.rows) & 15) != 0) return false;
+    if (p.norms && (reinterpret_cast<uintptr_t>(p.norms) & 15) != 0) return false;
     if ((int64_t)((d + 3) & ~3) * 4 > p.pitch_bytes) return false;
     p.norm_cols = 0;
     p.iters = (d + 15) / 16;                    // 16-column chunks
     int64_t rows = (36 * 1024) / p.pitch_bytes; // ~36 KiB per stage
     rows = rows / 16 * 16;
     if (rows < 16) rows = 16;
-    if (rows > 16 * SM_NW * 2) rows = 16 * SM_NW * 2;
+    if (rows > 16 * ST_NW * 2) rows = 16 * ST_NW * 2;
     p.stage_rows = (int)rows;
     p.rb = 16;
-    p.stage_stride = (int)round_up64((int64_t)p.stage_rows * p.pitch_bytes + 64, 128);
+    p.stage_stride = (int)round_up64((int64_t)p.stage_rows * (p.pitch_bytes + 4) + 64, 128);   // rows, then their norms
     const int64_t fixed = (int64_t)2 * SM_NQ * (p.iters * 16 + ST_QPAD) * 4 + 2 * SM_MAX_STAGES * 8 + 16;
     int64_t ns = (220 * 1024 - fixed) / p.stage_stride;
     if (ns > SM_MAX_STAGES) ns = SM_MAX_STAGES;
     p.nstage = (int)ns;
     // the CTA merge reuses the ring: SM_NW * SM_NQ * 32 (key, id) pairs
-    return ns >= 3 && (int64_t)p.nstage * p.stage_stride >= (int64_t)SM_NW * SM_NQ * 32 * 8;
+    return ns >= 3 && (int64_t)p.nstage * p.stage_stride >= (int64_t)ST_NW * SM_NQ * 32 * 8;
 }
 
 size_t scan_smem_bytes(int nq_t, int qstride) {
@@ -1059,7 +1081,9 @@ int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part
     }
     if (a.storage == B200F_STORAGE_F32 && stream_f32 && (a.metric != B200F_METRIC_L2 || a.norms)) {
         ScanParams ps = p;
-        if (plan_stream_f32(ps, a.d) && a.nb >= (int64_t)ps.stage_rows * sm) {
+        // no minimum shard size: a row's distance must not depend on how the rows are sharded,
+        // and this kernel and the FMA kernel round differently
+        if (plan_stream_f32(ps, a.d)) {
             const int64_t nchunks = ceil_div64(a.nb, ps.stage_rows);
             const int grid = (int)(nchunks < sm ? nchunks : sm);
             const size_t smem = (size_t)ps.nstage * ps.stage_stride +
@@ -1068,7 +1092,7 @@ int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part
             B200F_CUDA_TRY(cudaFuncSetAttribute(scan_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 (int)smem));
             main_kernel_begin(stream);
-            scan_tf32_kernel<<<grid, SM_THREADS, smem, stream>>>(ps);
+            scan_tf32_kernel<<<grid, ST_THREADS, smem, stream>>>(ps);
             main_kernel_end(stream);
             count_launch();
             B200F_LAUNCH_CHECK();

@@ -704,9 +704,9 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
             // geometry); the first launch reports it.  Groups of 8 where a streaming kernel
             // applies (shard large enough), else of 4.
             P = pl.scan.grid;
-            // FP32 rows: the streaming tf32 kernel takes up to 8 queries per pass at 3.8 TB/s whatever
-            // their number; the FMA kernel is faster up to four (6.9 / 5.6 / 4.1 TB/s for 1 / 2 / 4)
-            const bool stream_f32 = a->nq > SCAN_GROUP;
+            // FP32 rows: the streaming tf32 kernel for two queries and more (6.0 - 5.25 TB/s for 2 - 8
+            // per pass; the FMA kernel: 6.9 / 5.6 / 4.1 TB/s for 1 / 2 / 4)
+            const bool stream_f32 = a->nq >= 2;
             int64_t group = a->nq > SCAN_GROUP ? 2 * SCAN_GROUP : SCAN_GROUP;
             for (int64_t q0 = 0; q0 < a->nq;) {
                 B200FSearchArgs sub = *a;
