@@ -526,27 +526,34 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
                     mma16816<BF16>(acc, x0.z, x1.z, x0.w, x1.w, q.z, q.w);
                 }
                 // acc[0]: (row r0, query 2t)  acc[1]: (r0, 2t+1)  acc[2]: (r1, 2t)  acc[3]: (r1, 2t+1)
-                {
-                    const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
-                    const bool any_hit =
-                            (v0 && (before(kmul * acc[0], row_a, mta, mia) || before(kmul * acc[1], row_a, mtb, mib))) ||
-                            (v1 && (before(kmul * acc[2], row_b, mta, mia) || before(kmul * acc[3], row_b, mtb, mib)));
-                    if (!__any_sync(FULL, any_hit)) continue;  // the usual case: nothing for any query
-                }
+                // One vote tells whether the tile has a candidate at all; if so, one vote per accumulator
+                // register: bit l of mj[j] = lane l's key j is a candidate (lane 4g + t holds query 2t
+                // in keys 0 / 2 and query 2t + 1 in keys 1 / 3).
+                const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
+                float key[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) key[j] = kmul * acc[j];
+                const bool h0 = v0 && before(key[0], row_a, mta, mia), h1 = v0 && before(key[1], row_a, mtb, mib);
+                const bool h2 = v1 && before(key[2], row_b, mta, mia), h3 = v1 && before(key[3], row_b, mtb, mib);
+                if (!__any_sync(FULL, h0 || h1 || h2 || h3)) continue;  // the usual case: nothing for any query
+                unsigned mj[4];
+                mj[0] = __ballot_sync(FULL, h0);
+                mj[1] = __ballot_sync(FULL, h1);
+                mj[2] = __ballot_sync(FULL, h2);
+                mj[3] = __ballot_sync(FULL, h3);
 #pragma unroll
                 for (int qi = 0; qi < SM_NQ; qi++) {
                     if (qi >= p.nq) break;
-                    const bool mine = (qi >> 1) == t;
+                    const unsigned lanes_q = 0x11111111u << (qi >> 1);   // the lanes with t = qi / 2
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        const float key = kmul * ((qi & 1) ? acc[2 * h + 1] : acc[2 * h]);
-                        const int row = (int)(row0 + (h ? r1 : r0));
-                        const bool hit = mine && (h ? v1 : v0) && before(key, row, thr[qi], thr_id[qi]);
-                        unsigned m = __ballot_sync(FULL, hit);
+                        const float kk = key[2 * h + (qi & 1)];
+                        const int row = h ? row_b : row_a;
+                        unsigned m = mj[2 * h + (qi & 1)] & lanes_q;
                         while (m) {
                             const int src = __ffs(m) - 1;
                             m &= m - 1;
-                            const float s = __shfl_sync(FULL, key, src);
+                            const float s = __shfl_sync(FULL, kk, src);
                             const int id = __shfl_sync(FULL, row, src);
                             if (before(s, id, thr[qi], thr_id[qi])) {
                                 warp_insert(lk[qi], li[qi], s, id, lane);
@@ -813,15 +820,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) scan_tf32_kernel(const ScanPara
                 key[1] = l2 ? fmaf(-2.f, acc[1], n0) : -acc[1];
                 key[2] = l2 ? fmaf(-2.f, acc[2], n1) : -acc[2];
                 key[3] = l2 ? fmaf(-2.f, acc[3], n1) : -acc[3];
-                // one vote per accumulator register: bit l of mj[j] = lane l's key j is a candidate
-                // (lane 4g + t holds query 2t in keys 0 / 2 and query 2t + 1 in keys 1 / 3)
+                // one vote tells whether the tile has a candidate at all; if so, one vote per accumulator
+                // register: bit l of mj[j] = lane l's key j is a candidate (lane 4g + t holds query 2t
+                // in keys 0 / 2 and query 2t + 1 in keys 1 / 3)
                 const int row_a = (int)(row0 + r0), row_b = (int)(row0 + r1);
+                const bool h0 = v0 && before(key[0], row_a, mta, mia), h1 = v0 && before(key[1], row_a, mtb, mib);
+                const bool h2 = v1 && before(key[2], row_b, mta, mia), h3 = v1 && before(key[3], row_b, mtb, mib);
+                if (!__any_sync(FULL, h0 || h1 || h2 || h3)) continue;  // the usual case: nothing for any query
                 unsigned mj[4];
-                mj[0] = __ballot_sync(FULL, v0 && before(key[0], row_a, mta, mia));
-                mj[1] = __ballot_sync(FULL, v0 && before(key[1], row_a, mtb, mib));
-                mj[2] = __ballot_sync(FULL, v1 && before(key[2], row_b, mta, mia));
-                mj[3] = __ballot_sync(FULL, v1 && before(key[3], row_b, mtb, mib));
-                if (!(mj[0] | mj[1] | mj[2] | mj[3])) continue;  // the usual case: nothing for any query
+                mj[0] = __ballot_sync(FULL, h0);
+                mj[1] = __ballot_sync(FULL, h1);
+                mj[2] = __ballot_sync(FULL, h2);
+                mj[3] = __ballot_sync(FULL, h3);
 #pragma unroll
                 for (int qi = 0; qi < SM_NQ; qi++) {
                     if (qi >= p.nq) break;
