@@ -105,8 +105,11 @@ int b200f_set_gemm_shape(int shape);
 /* Selection of more than 32 results from at most 8192 entries per row (a row's threshold-filtered
  * candidates; the sorted lists of up to 8192 / k shards): with on != 0 (the default) the kernels
  * that sort in registers and place every entry by binary search, else the shared-memory sorting
- * kernel that also serves larger inputs.  Results are identical; a testing aid.  No counterpart
- * in the reference (its block_select, shaders/block_select.metal:111-274, is the one kernel). */
+ * kernel that also serves larger inputs.  The same switch decides how the threshold filter takes
+ * its pilot sample: on, as a key matrix picked over by a selection kernel wherever it fits (and the
+ * filter is then used from 2^22 pairs); off, always as 32-entry lists.  Results are identical
+ * either way; a testing aid.  No counterpart in the reference (its block_select,
+ * shaders/block_select.metal:111-274, is the one kernel). */
 int b200f_set_rank_select(int on);
 /* Debug canaries, the stand-in for a memory checker on the scratch arena: with on != 0 every
  * slice of a search's scratch region is followed by a 256-byte guard that is filled before the
