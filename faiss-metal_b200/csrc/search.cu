@@ -107,7 +107,10 @@ bool lists_disabled() { return select_mode() == B200F_SELECT_MATRIX; }
 // its lists on a single tile).  Measured: at 2.6e8 (query, row) pairs the filter path is 19 - 47 %
 // faster than the lists (d = 768 / 1536, 16-bit rows), at 1e8 - 4e8 pairs of fp32 rows with
 // d = 128 the two are level; below this many pairs the lists are used.
-constexpr int64_t F32_STREAM_MIN_ROWS = 65536;   // fp32 rows: from here the tf32 streaming scan applies
+// fp32 rows: five to eight queries take the scan path where the tf32 streaming scan pays and fits (three
+// stages of 16 rows and two query matrices in shared memory: d up to 768)
+constexpr int64_t F32_STREAM_MIN_ROWS = 65536;
+constexpr int F32_STREAM_MAX_D = 768;
 constexpr int64_t FILTER_MIN_PAIRS = 1ll << 27;
 constexpr int64_t FILTER_MIN_PAIRS_MATRIX = 1ll << 22;
 constexpr int64_t PILOT_MATRIX_BYTES = 256ll << 20;   // k <= 32: largest pilot sample kept as a key matrix
@@ -130,10 +133,11 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     pl = SearchPlan{};
     pl.path = path;
     // the streaming scans take up to 8 queries per pass, which beats a 128-row tensor tile that is
-    // mostly padding (measured on 12.5 M fp32 rows of d = 128, 8 queries: 1.7 against 4.1 ms); fp32
-    // shards too small for the streaming kernel: 4 per pass (the reference's limit,
-    // src/MetalDistance.mm:346-354)
-    const int64_t scan_limit = (storage == B200F_STORAGE_F32 && nb < F32_STREAM_MIN_ROWS) ? SCAN_GROUP : 2 * SCAN_GROUP;
+    // mostly padding (measured on 12.5 M fp32 rows of d = 128, 8 queries: 1.3 against 4.1 ms); fp32
+    // shards under 64 Ki rows or wider than the streaming kernel takes: 4 per pass (the reference's
+    // limit, src/MetalDistance.mm:346-354)
+    const bool f32_stream = nb >= F32_STREAM_MIN_ROWS && d <= F32_STREAM_MAX_D;
+    const int64_t scan_limit = (storage == B200F_STORAGE_F32 && !f32_stream) ? SCAN_GROUP : 2 * SCAN_GROUP;
     if (path == B200F_PATH_AUTO) pl.path = (nq <= scan_limit) ? B200F_PATH_SCAN : B200F_PATH_TENSOR;
     pl.fused = (k <= B200F_FUSED_MAX_K) && !pairwise;
     pl.npl = (storage == B200F_STORAGE_F32) ? 3 : 1;

@@ -19,6 +19,9 @@ pytestmark = pytest.mark.gpu
     (131_077, 7, 33, 7, False),       # padded row pitch, partial last stage
     (90_000, 13, 48, 10, True),       # groups of 8 and 5
     (200_000, 8, 16, 32, False),      # a single chunk per row
+    (66_000, 8, 768, 10, False),      # the widest rows the kernel takes: three stages of 16 rows
+    (66_000, 6, 1024, 5, False),      # wider: these queries go to the tensor path
+    (5_000, 3, 64, 10, False),        # a shard of a few stages: fewer CTAs than SMs
 ])
 def test_tf32_scan_against_oracle(fm, res, metric, nb, nq, d, k, force_scan):
     rng = np.random.default_rng(nb + nq + d)
@@ -26,7 +29,10 @@ def test_tf32_scan_against_oracle(fm, res, metric, nb, nq, d, k, force_scan):
     xb[1000:1040] = xb[17]                 # exact ties: lower label first
     xb[nb - 5:] = xb[17]                   # in the last (partial) stage too
     xq = rng.standard_normal((nq, d), dtype=np.float32)
-    xq[0] = xb[17] + 0.01
+    if d <= 128:
+        # a near copy of a stored row (at large d the fp32 cancellation in ||q||^2 + ||x||^2 - 2 q.x,
+        # terms of ~d each, is all such a distance consists of, on any kernel)
+        xq[0] = xb[17] + 0.01
     idx = fm.B200IndexFlat(res, d, metric, fm.abi.STORAGE_F32)
     idx.add(xb)
     if force_scan:
