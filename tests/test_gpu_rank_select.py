@@ -176,3 +176,34 @@ def test_candidate_selection_matches_sorting_kernel(fm, res, nb, nq, d, k, stora
     assert np.array_equal(I1, I0), int((I1 != I0).sum())
     assert np.array_equal(D1, D0)
     idx.close()
+
+
+@pytest.mark.parametrize("k,storage", [(100, 1), (600, 0)])
+def test_more_ties_than_the_selection_holds(fm, res, k, storage):
+    # thousands of exact copies tie at the k-th key: more candidates at or under it than the
+    # register-sorting kernel holds (2048 / 4096), so the row goes to the exact redo pass; the k
+    # lowest labels of the tie win
+    nb, d, nq = 70_000, 32, 40
+    rng = np.random.default_rng(9)
+    xb = rng.standard_normal((nb, d), dtype=np.float32)
+    xb[5000:10_000] = xb[17]
+    xq = rng.standard_normal((nq, d), dtype=np.float32)
+    xq[3] = xb[17] + 0.001
+    xq[11] = xb[17]
+    L = fm.lib()
+    idx = fm.B200IndexFlat(res, d, O.METRIC_L2, storage)
+    idx.add(xb)
+    idx.set_path(2)
+    old_mode = L.b200f_get_selection_mode()
+    assert L.b200f_set_selection_mode(1) == 0
+    try:
+        D1, I1 = idx.search(xq, k)
+        assert L.b200f_set_rank_select(0) == 0
+        D0, I0 = idx.search(xq, k)
+    finally:
+        L.b200f_set_rank_select(1)
+        L.b200f_set_selection_mode(old_mode)
+    assert np.array_equal(I1, I0) and np.array_equal(D1, D0)
+    want = np.concatenate(([17], np.arange(5000, 5000 + k - 1)))
+    assert np.array_equal(I1[3], want) and np.array_equal(I1[11], want)
+    idx.close()
