@@ -371,7 +371,8 @@ scan_kernel(const ScanParams p) {
 // 32c + 8t) and the query matrix in shared memory is read with the same pattern.  With
 // norm columns in the rows the L2 term -||x||^2/2 is part of the same dot product.
 // ---------------------------------------------------------------------------------------
-constexpr int SM_NW = 8;
+constexpr int SM_NW = 8;            // consumer warps of the ring kernels (scan_mma_kernel: for one or two queries)
+constexpr int SM_NW_MANY = 12;      // scan_mma_kernel with three to eight queries
 constexpr int SM_THREADS = 32 * (1 + SM_NW);
 constexpr int SM_MAX_STAGES = 8;
 constexpr int SM_NQ = 8;
@@ -394,8 +395,10 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
     }
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParams p) {
+// NW consumer warps: 8 for one or two queries (6.80 / 6.62 TB/s on 25 M fp16 rows; 12 warps: 6.55 at
+// one), 12 beyond (four queries 6.24 -> 6.53 TB/s, eight 5.44 -> 6.08).
+template <bool BF16, int NW>
+__global__ void __launch_bounds__(32 * (1 + NW), 1) scan_mma_kernel(const ScanParams p) {
     extern __shared__ __align__(128) uint8_t sm[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -413,7 +416,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
     const int d8 = (p.d + 7) & ~7;
     const int kext = d8 + (p.norm_cols ? 8 : 0);  // valid columns of a stored row
 
-    for (int i = threadIdx.x; i < SM_NQ * kq; i += SM_THREADS) {
+    for (int i = threadIdx.x; i < SM_NQ * kq; i += 32 * (1 + NW)) {
         const int qi = i / kq;
         const int j = i - qi * kq;
         float v = 0.f;
@@ -427,7 +430,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
         *abort_flag = 0;
         for (int s = 0; s < p.nstage; s++) {
             mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, SM_NW);
+            mbar_init(bar_empty + s * 8, NW);
         }
         mbar_fence_init();
     }
@@ -498,6 +501,10 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
             if (2 * t + 1 >= p.nq) mtb = -CUDART_INF_F;
         };
         refresh_bounds();
+        // a stage may hold fewer 16-row tiles than there are consumer warps: the first tile's owner
+        // moves on by that many warps from stage to stage, so all of them work
+        const int tiles_full = p.stage_rows >> 4;
+        int shift = 0;
         for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
             const bool w = mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, p.status,
                                              kDevErrBarrierWait);
@@ -506,7 +513,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
             const int nr = (int)min((int64_t)p.stage_rows, p.col1 - row0);
             const uint32_t sstage = sbase + stage * p.stage_stride;
             const int ntiles = (nr + 15) >> 4;
-            for (int tile = wc; tile < ntiles; tile += SM_NW) {
+            for (int tile = (wc - shift + NW) % NW; tile < ntiles; tile += NW) {
                 const int r0 = tile * 16 + g;      // local rows of this lane
                 const int r1 = r0 + 8;
                 const bool v0 = r0 < nr, v1 = r1 < nr;
@@ -567,6 +574,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+            shift = (shift + tiles_full) % NW;
             if (++stage == p.nstage) {
                 stage = 0;
                 phase ^= 1;
@@ -577,8 +585,8 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
     // CTA merge in the (now idle) ring memory: consumer warp wc publishes its lists,
     // warp 1 + qi folds them for query qi.
     __syncthreads();
-    float* mk = reinterpret_cast<float*>(sm);                        // [SM_NW][SM_NQ][32]
-    int* mi = reinterpret_cast<int*>(sm) + SM_NW * SM_NQ * 32;
+    float* mk = reinterpret_cast<float*>(sm);                        // [NW][SM_NQ][32]
+    int* mi = reinterpret_cast<int*>(sm) + NW * SM_NQ * 32;
     if (warp > 0) {
 #pragma unroll
         for (int qi = 0; qi < SM_NQ; qi++) {
@@ -593,7 +601,7 @@ __global__ void __launch_bounds__(SM_THREADS, 1) scan_mma_kernel(const ScanParam
         int i0 = mi[qi * 32 + lane];
         float tk = __shfl_sync(FULL, k0, p.k - 1);
         int tid = __shfl_sync(FULL, i0, p.k - 1);
-        for (int w2 = 1; w2 < SM_NW; w2++) {
+        for (int w2 = 1; w2 < NW; w2++) {
             for (int j = 0; j < p.k; j++) {
                 const float s = mk[(w2 * SM_NQ + qi) * 32 + j];
                 const int id = mi[(w2 * SM_NQ + qi) * 32 + j];
@@ -996,7 +1004,7 @@ bool plan_stream(ScanParams& p, int storage, int d, int norm_cols) {
     int64_t rows = (36 * 1024) / p.pitch_bytes; // ~36 KiB per stage
     rows = rows / 16 * 16;
     if (rows < 16) rows = 16;
-    if (rows > 16 * SM_NW * 2) rows = 16 * SM_NW * 2;
+    if (rows > 256) rows = 256;
     p.stage_rows = (int)rows;
     p.rb = 16;
     p.stage_stride = (int)round_up64((int64_t)p.stage_rows * p.pitch_bytes + 64, 128);
@@ -1072,17 +1080,21 @@ int launch_scan_topk(const B200FSearchArgs& a, const ScanPlan& plan, float* part
             const size_t smem = (size_t)ps.nstage * ps.stage_stride + (size_t)SM_NQ * ps.iters * 32 * 2 +
                                 2 * SM_MAX_STAGES * 8 + 16;
             *out_P = grid;
-            if (a.storage == B200F_STORAGE_BF16) {
-                B200F_CUDA_TRY(cudaFuncSetAttribute(scan_mma_kernel<true>,
-                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                main_kernel_begin(stream);
-                scan_mma_kernel<true><<<grid, SM_THREADS, smem, stream>>>(ps);
+            // macro: the kernel is a template over (format, consumer warps)
+#define B200F_SCAN_MMA(BF, NW)                                                                            \
+    {                                                                                                     \
+        B200F_CUDA_TRY(cudaFuncSetAttribute(scan_mma_kernel<BF, NW>,                                      \
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
+        main_kernel_begin(stream);                                                                        \
+        scan_mma_kernel<BF, NW><<<grid, 32 * (1 + NW), smem, stream>>>(ps);                               \
+    }
+            const bool bf = a.storage == B200F_STORAGE_BF16;
+            if (a.nq <= 2) {
+                if (bf) B200F_SCAN_MMA(true, 8) else B200F_SCAN_MMA(false, 8)
             } else {
-                B200F_CUDA_TRY(cudaFuncSetAttribute(scan_mma_kernel<false>,
-                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                main_kernel_begin(stream);
-                scan_mma_kernel<false><<<grid, SM_THREADS, smem, stream>>>(ps);
+                if (bf) B200F_SCAN_MMA(true, SM_NW_MANY) else B200F_SCAN_MMA(false, SM_NW_MANY)
             }
+#undef B200F_SCAN_MMA
             main_kernel_end(stream);
             count_launch();
             B200F_LAUNCH_CHECK();
