@@ -502,7 +502,9 @@ __global__ void __launch_bounds__(32 * (1 + NW), 1) scan_mma_kernel(const ScanPa
         };
         refresh_bounds();
         // a stage may hold fewer 16-row tiles than there are consumer warps: the first tile's owner
-        // moves on by that many warps from stage to stage, so all of them work
+        // moves on by that many warps from stage to stage, so all of them work (eight warps: stages of
+        // 128 or 256 rows are the rule, and the single-query stream keeps its measured loop)
+        constexpr bool ROTATE = NW != 8;
         const int tiles_full = p.stage_rows >> 4;
         int shift = 0;
         for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
@@ -513,7 +515,7 @@ __global__ void __launch_bounds__(32 * (1 + NW), 1) scan_mma_kernel(const ScanPa
             const int nr = (int)min((int64_t)p.stage_rows, p.col1 - row0);
             const uint32_t sstage = sbase + stage * p.stage_stride;
             const int ntiles = (nr + 15) >> 4;
-            for (int tile = (wc - shift + NW) % NW; tile < ntiles; tile += NW) {
+            for (int tile = ROTATE ? (wc - shift + NW) % NW : wc; tile < ntiles; tile += NW) {
                 const int r0 = tile * 16 + g;      // local rows of this lane
                 const int r1 = r0 + 8;
                 const bool v0 = r0 < nr, v1 = r1 < nr;
@@ -574,7 +576,7 @@ __global__ void __launch_bounds__(32 * (1 + NW), 1) scan_mma_kernel(const ScanPa
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + stage * 8);
-            shift = (shift + tiles_full) % NW;
+            if (ROTATE) shift = (shift + tiles_full) % NW;
             if (++stage == p.nstage) {
                 stage = 0;
                 phase ^= 1;
