@@ -623,16 +623,16 @@ __global__ void __launch_bounds__(32 * (1 + NW), 1) scan_mma_kernel(const ScanPa
 
 // ---------------------------------------------------------------------------------------
 // The same streaming pipeline for FP32 rows: mma.sync m16n8k8 on a tf32 split.  A value is
-// x = hi + lo with hi = tf32(x), lo = tf32(x - hi) (21 mantissa bits between them); the three
-// products hi*hi, lo*hi, hi*lo accumulate in fp32 and leave about 2^-21 of the result out, as an
-// fp32 FMA chain would.  The rows are split on the fly (two conversions and a subtraction per
-// element), the queries once into two matrices.  K is permuted as in the 16-bit kernel: per
+// x = hi + lo with hi = x cut to tf32's bits, lo = x - hi (of which the MMA reads the top bits: 21
+// mantissa bits between them); the three products hi*hi, lo*hi, hi*lo accumulate in fp32 and leave
+// about 2^-21 of the result out, as an fp32 FMA chain would.  The rows are split on the fly (a
+// mask and a subtraction per element), the queries once into two matrices.  K is permuted as in the 16-bit kernel: per
 // 16-column chunk a lane takes the 16 bytes at column 16c + 4t of rows g and g+8, floats 0 / 1 feed
 // k-slots t / t+4 of the first MMA, floats 2 / 3 those of the second, and the query matrices are read
 // with the same pattern.  ||x||^2 comes from the norm array (FP32 rows carry no norm columns).
 // Up to 8 queries per pass, one dot product per (row, query) on the tensor pipe instead of d FMAs
 // and a shuffle reduction: what held the FMA kernel to 86 % / 62 % of the copy bandwidth at 2 / 4
-// queries.
+// queries (this kernel: 108 / 103 / 94 % at 2 / 4 / 8).
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t to_tf32(float x) {
     uint32_t r;

@@ -133,7 +133,7 @@ bool make_plan(int64_t nq, int64_t nb, int d, int k, int storage, int path, bool
     pl = SearchPlan{};
     pl.path = path;
     // the streaming scans take up to 8 queries per pass, which beats a 128-row tensor tile that is
-    // mostly padding (measured on 12.5 M fp32 rows of d = 128, 8 queries: 1.3 against 4.1 ms); fp32
+    // mostly padding (measured on 12.5 M fp32 rows of d = 128, 8 queries: 1.1 against 4.1 ms); fp32
     // shards under 64 Ki rows or wider than the streaming kernel takes: 4 per pass (the reference's
     // limit, src/MetalDistance.mm:346-354)
     const bool f32_stream = nb >= F32_STREAM_MIN_ROWS && d <= F32_STREAM_MAX_D;
@@ -708,7 +708,7 @@ static int run_search(const B200FSearchArgs* a, const SearchPlan& pl) {
             // geometry); the first launch reports it.  Groups of 8 where a streaming kernel
             // applies (shard large enough), else of 4.
             P = pl.scan.grid;
-            // FP32 rows: the streaming tf32 kernel for two queries and more (6.0 - 5.25 TB/s for 2 - 8
+            // FP32 rows: the streaming tf32 kernel for two queries and more (7.1 - 6.1 TB/s for 2 - 8
             // per pass; the FMA kernel: 6.9 / 5.6 / 4.1 TB/s for 1 / 2 / 4)
             const bool stream_f32 = a->nq >= 2;
             int64_t group = a->nq > SCAN_GROUP ? 2 * SCAN_GROUP : SCAN_GROUP;
